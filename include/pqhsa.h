@@ -1,0 +1,230 @@
+/*
+ * pqhsa.h -- C ABI of the B200 (sm_100a) PQ-HSA per-step decode operator.
+ *
+ * Plain pointers and sizes only: no torch types, no exceptions, no allocation
+ * and no host synchronisation inside any entry point.  Every function returns
+ * 0 on success or a negative PQHSA_E_* code; pqhsa_last_error_string() gives
+ * the text of the calling thread's last failure.  All work is enqueued on the
+ * cudaStream_t handed in (passed as void* so that this header needs no CUDA
+ * include), so a sequence of calls can be captured in a CUDA graph.
+ *
+ * The entry points replace the reference's torch-pybind FFI
+ * (pq_hsa/kernels/cuda/pq_fused_h20.cu:3826-3839) and its Triton launchers for
+ * the decode hot path.  Each declaration cites what it stands in for.
+ */
+#ifndef PQHSA_H_
+#define PQHSA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PQHSA_ABI_VERSION 1
+
+/* fixed shape of the index (pq_hsa/kernels/cuda/pq_fused_h20.cu:26-35 fixes the
+ * same: 8 subspaces x 4 bits, at most 512 lists, head_dim 128) */
+#define PQHSA_SUBSPACES 8
+#define PQHSA_CODES 16
+#define PQHSA_HEAD_DIM 128
+#define PQHSA_MAX_LISTS 512
+#define PQHSA_UNIT_KEYS 256  /* a scan unit = at most this many slots of one list */
+#define PQHSA_HIST_BINS 4096 /* selection histogram resolution per query row */
+
+enum pqhsa_status {
+  PQHSA_OK = 0,
+  PQHSA_E_NULL = -1,        /* a required pointer is null */
+  PQHSA_E_SHAPE = -2,       /* unsupported or inconsistent size */
+  PQHSA_E_DTYPE = -3,       /* unknown element type */
+  PQHSA_E_WORKSPACE = -4,   /* workspace missing, misaligned or too small */
+  PQHSA_E_CUDA = -5,        /* a CUDA runtime call failed */
+  PQHSA_E_CAPACITY = -6     /* index slots / tail / static scratch exhausted */
+};
+
+enum pqhsa_dtype { PQHSA_F32 = 0, PQHSA_BF16 = 1, PQHSA_F16 = 2 };
+
+/* Per-stream counters kept ON THE DEVICE (int32[PQHSA_STATE_INTS] per stream),
+ * so that append/encode and the decode step need no host round trip. */
+enum pqhsa_state_slot {
+  PQHSA_ST_N_SORTED = 0, /* slots in the list-sorted region                     */
+  PQHSA_ST_N_TAIL = 1,   /* slots appended after it, in arrival order           */
+  PQHSA_ST_SEQ_LEN = 2,  /* tokens of this request present in the KV cache      */
+  PQHSA_ST_N_UNITS = 3,  /* scan units covering the sorted region               */
+  PQHSA_ST_N_LISTS = 4,  /* IVF lists in use (min(num_lists, keys at build))    */
+  PQHSA_ST_REQ = 5,      /* request index: row of block_table / batch index     */
+  PQHSA_ST_KV_HEAD = 6,  /* KV head index inside the cache                      */
+  PQHSA_ST_RESERVED = 7,
+  PQHSA_STATE_INTS = 8
+};
+
+/*
+ * One POD describes a batch of independent streams (stream = one request x one
+ * KV head; its G query heads share the index).  E is the element type `dtype`
+ * of q, K/V rows, output and of the float tensors of the index, as in the
+ * reference where centroids, code words and norms take the key dtype
+ * (pq_hsa/index/ivfpq.py:1052-1059, pq_hsa/index/kmeans.py:225).
+ *
+ * Index pool, S = num_streams, cap = slot_capacity (IVF-PQ layout of
+ * pq_hsa/index/ivfpq.py:160-173 in the list-sorted snapshot form of
+ * benchmarks/e2e_pq_param_sweep.py:4182-4305):
+ *   codes     uint32 [S, cap]      8 nibbles, subspace s in bits 4s..4s+3
+ *   norms     E      [S, cap]      |k|, clamped at 1e-12
+ *   list_ids  uint16 [S, cap]
+ *   slot_pos  int32  [S, cap]      token position of the slot's key
+ *   unit_off  int32  [S, unit_capacity + 1]   slot ranges of the scan units
+ *   unit_list uint16 [S, unit_capacity]       list of each unit
+ *   coarse    E      [S, num_lists, 128]      list centroids (unit-direction space)
+ *   codebooks E      [S, 8, 16, 16]           residual code words
+ *   vmeans    E      [S, num_lists, 128]      per-list mean value row
+ *   vsum      float  [S, num_lists, 128]      running value sums   (append only)
+ *   vcnt      int32  [S, num_lists]           running list counts  (append only)
+ *   state     int32  [S, PQHSA_STATE_INTS]
+ *
+ * KV cache addressing for token t of request r, KV head h
+ * (pq_hsa/kernels/cuda/pq_fused_h20.cu:879-903 supports the same two page
+ * layouts; a contiguous [B, Hkv, S, D] cache is the block_table == NULL case):
+ *   blk = block_table ? block_table[r * max_blocks + t / block_size] : r
+ *   row = block_table ? t % block_size : t
+ *   K   = k_base + blk * stride_block + h * stride_head + row * stride_row   (elements)
+ *   V   = v_base + the same offset
+ */
+typedef struct pqhsa_params {
+  int32_t abi_version;     /* PQHSA_ABI_VERSION */
+  int32_t dtype;           /* enum pqhsa_dtype */
+  int32_t num_streams;     /* S = requests x local KV heads */
+  int32_t group;           /* G = query heads per KV head: 1, 2, 4 or 8 */
+  int32_t head_dim;        /* 128 */
+  int32_t num_lists;       /* row count of coarse / vmeans, <= 512 */
+  int32_t slot_capacity;   /* cap, multiple of 8 */
+  int32_t unit_capacity;   /* >= lists + cap / PQHSA_UNIT_KEYS */
+  int32_t sink_tokens;
+  int32_t local_window;
+  int32_t max_slots;       /* host upper bound of n_sorted + n_tail over streams (grid sizing) */
+  int32_t max_full;        /* capacity: sink + local rows of any stream never exceed it (fixes the layout) */
+  int32_t topk_fixed;      /* used when top_fraction < 0 */
+  int32_t tail_capacity;   /* most slots the unsorted tail may hold (fixes the workspace layout) */
+  double top_fraction;     /* K = min(max(ceil(N * f), 0), N) in double, as
+                              pq_hsa/attention/sparse_attention.py:1779-1783 */
+  float scale;             /* softmax scale, 1/sqrt(D) unless the model says otherwise */
+  float hist_lo;           /* selection histogram: bin = (logit - lo) * inv_width, clamped */
+  float hist_inv_width;
+  float reserved1;
+
+  const void *codes, *norms, *list_ids, *slot_pos, *unit_off, *unit_list;
+  const void *coarse, *codebooks, *vmeans;
+  void *vsum, *vcnt, *state;
+
+  const void *k_base, *v_base;
+  const int32_t *block_table;
+  int32_t max_blocks;
+  int32_t block_size;
+  int64_t stride_block, stride_head, stride_row;
+
+  const void *q;           /* E [S, G, 128]: query heads h*G .. h*G+G-1 of KV head h */
+  void *out;               /* E [S, G, 128] */
+  void *workspace;         /* >= pqhsa_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+} pqhsa_params;
+
+/* Byte offsets of the intermediate results inside the workspace, so that a
+ * caller (or a parity test) can read them after the stream has been synchronised.
+ * R = S * G query rows. */
+typedef struct pqhsa_ws_layout {
+  size_t total_bytes;
+  size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>            */
+  size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>               */
+  size_t bins;         /* uint16 [R, cap]        histogram bin of every slot's logit  */
+  size_t hist;         /* uint32 [R, 4096]                                            */
+  size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit              */
+  size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max)   */
+  size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail     */
+  size_t row_info;     /* int32  [R, 8]: K, threshold bin, #above, #selected, #candidates, tail_cap */
+  size_t row_amax;     /* float  [R]   max approximate logit                          */
+  size_t sel_slot;     /* int32  [R, kcap]  selected slots (unordered)                */
+  size_t sel_logit;    /* float  [R, kcap]  their approximate logits                  */
+  size_t sel_list;     /* uint16 [R, kcap]  their lists                               */
+  size_t cand_slot;    /* int32  [R, cap]   slots inside the threshold bin            */
+  size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)   */
+  int32_t kcap;        /* row stride of sel_* */
+  int32_t tail_cap;    /* row stride of tail_logit */
+  int32_t chunks;      /* split-K partials per row */
+  int32_t reserved;
+} pqhsa_ws_layout;
+
+enum pqhsa_row_info_slot {
+  PQHSA_RI_K = 0, PQHSA_RI_THR_BIN = 1, PQHSA_RI_ABOVE = 2, PQHSA_RI_NSEL = 3,
+  PQHSA_RI_NCAND = 4, PQHSA_RI_N = 5, PQHSA_RI_INTS = 8
+};
+
+int pqhsa_abi_version(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* pqhsa_last_error_string(void);
+
+/* Workspace size for `p` (ignores p->workspace*).  Replaces the function-static
+ * scratch tensors of pq_fused_h20.cu:2610-2618; here the caller owns the memory. */
+size_t pqhsa_workspace_bytes(const pqhsa_params* p);
+int pqhsa_workspace_layout(const pqhsa_params* p, pqhsa_ws_layout* out);
+
+/* (1) Per-query, per-head table construction: lut and list_scores in the
+ * workspace.  Replaces pq_lut_prep (pq_fused_h20.cu:2975-3051) and
+ * ProductQuantizer.compute_lut + the coarse bias (pq_hsa/index/pq.py:190-217,
+ * pq_hsa/index/ivfpq.py:1179-1190).  Also clears the per-step counters. */
+int pqhsa_lut_build(const pqhsa_params* p, void* stream);
+
+/* (2)+(3)+(5a) Code scan with per-unit log-sum-exp and exact top-K selection.
+ * Needs pqhsa_lut_build first.  Leaves sel_slot / row_info / unit_* in the
+ * workspace.  Replaces the pair-fused Triton scan
+ * (pq_hsa/kernels/triton_lut_scan_h20.py:1197-1291), list_exp_sums_sorted
+ * (pq_hsa/kernels/triton_lut_scan.py:424-514), pq_block_reduce
+ * (pq_fused_h20.cu:3094) and aten topk + pq_cast_topk
+ * (benchmarks/e2e_pq_param_sweep.py:212-217, pq_fused_h20.cu:3148). */
+int pqhsa_scan_select(const pqhsa_params* p, void* stream);
+
+/* (4)+(5b) Exact attention over sink, local window and the selected keys read in
+ * place from the (paged) cache, background = per-list mass x list mean value,
+ * one softmax; writes p->out.  Needs pqhsa_scan_select first.  Replaces
+ * pq_attend_partial_nw(_paged) / pq_attend_bg / pq_attend_reduce_mw
+ * (pq_fused_h20.cu:1225-1753, :2150-2402). */
+int pqhsa_attend_merge(const pqhsa_params* p, void* stream);
+
+/* The whole step: the three calls above in order.  Stands in for one replay of
+ * the reference's per-layer CUDA graph body
+ * (benchmarks/e2e_pq_param_sweep.py:6308-6969). */
+int pqhsa_decode_step(const pqhsa_params* p, void* stream);
+
+/* Write one new K/V row per stream into the cache at position seq_len and bump
+ * seq_len (contiguous or paged addressing as above).  new_k/new_v: E [S, 128].
+ * Replaces pq_append_prep (pq_fused_h20.cu:2888-2922). */
+int pqhsa_append_kv(const pqhsa_params* p, const void* new_k, const void* new_v, void* stream);
+
+/* Incremental encode with fixed codebooks: for every stream, the next
+ * enc_count[s] tokens after the indexed region (positions sink_end + N ...) are
+ * read from the cache, split into norm and direction, assigned to the nearest
+ * list, residual-encoded to 8 nibbles and appended to the tail; the list's
+ * value sum / count / mean are updated.  enc_count: device int32 [S], or NULL
+ * for `uniform_count` on every stream.  Mirrors IVFPQIndex.add
+ * (pq_hsa/index/ivfpq.py:598-645) and the value-summary update
+ * (pq_hsa/attention/kv_cache.py:730-764).  p->vsum / p->vcnt must be valid. */
+int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t uniform_count,
+                        void* stream);
+
+/* Test / inspection entry: approximate logits (scale * estimated q.k) of every
+ * slot, float [R, cap], same arithmetic as the scan.  Counterpart of
+ * score_packed_4bit_lut_multihead_list_bias
+ * (pq_hsa/kernels/triton_lut_scan.py:1027-1104).  Needs pqhsa_lut_build first. */
+int pqhsa_scan_scores(const pqhsa_params* p, float* scores, void* stream);
+
+/* Stand-alone exact top-k of float rows: scores [rows, row_stride] (first n
+ * valid) -> out_idx int32 [rows, k] (unordered) and out_val float [rows, k].
+ * Ties at the k-th value are resolved towards the lower index.  Counterpart of
+ * pq_topk_radix (pq_fused_h20.cu:3624-3688) / torch.topk. */
+int pqhsa_topk_radix(const float* scores, int32_t rows, int32_t n, int64_t row_stride, int32_t k,
+                     int32_t* out_idx, float* out_val, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PQHSA_H_ */

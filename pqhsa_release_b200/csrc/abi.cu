@@ -1,0 +1,207 @@
+// extern "C" entry points of libpqhsa_b200: validation, workspace layout and
+// the launch sequences.  No allocation, no synchronisation, no exceptions.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace pqhsa {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(PQHSA_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return PQHSA_OK;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int topk_capacity(const pqhsa_params* p) {
+  long long k = p->topk_fixed > 0 ? p->topk_fixed : 0;
+  if (p->top_fraction >= 0.0) k = (long long)((double)p->slot_capacity * p->top_fraction) + 8;
+  if (k > p->slot_capacity) k = p->slot_capacity;
+  if (k < 8) k = 8;
+  return (int)align_up((size_t)k, 8);
+}
+
+void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
+  memset(o, 0, sizeof(*o));
+  const size_t S = (size_t)p->num_streams, G = (size_t)p->group, R = S * G;
+  const size_t cap = (size_t)p->slot_capacity;
+  o->kcap = topk_capacity(p);
+  o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
+  o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  o->lut = take(S * G * kM * kC * sizeof(float));
+  o->list_scores = take(S * G * kLMax * sizeof(float));
+  o->bins = take(R * cap * sizeof(uint16_t));
+  o->hist = take(R * kBins * sizeof(uint32_t));
+  o->unit_max = take(R * (size_t)p->unit_capacity * sizeof(float));
+  o->unit_sum = take(R * (size_t)p->unit_capacity * sizeof(float));
+  o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
+  o->row_info = take(R * kRI * sizeof(int32_t));
+  o->row_amax = take(R * sizeof(float));
+  o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
+  o->sel_logit = take(R * (size_t)o->kcap * sizeof(float));
+  o->sel_list = take(R * (size_t)o->kcap * sizeof(uint16_t));
+  o->cand_slot = take(R * cap * sizeof(int32_t));
+  o->partial = take(R * (size_t)o->chunks * kPartial * sizeof(float));
+  o->total_bytes = off;
+}
+
+int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io) {
+  if (p == nullptr) return set_error(PQHSA_E_NULL, "params is null");
+  if (p->abi_version != PQHSA_ABI_VERSION)
+    return set_error(PQHSA_E_SHAPE, "abi_version %d, library speaks %d", p->abi_version, PQHSA_ABI_VERSION);
+  if (p->dtype < PQHSA_F32 || p->dtype > PQHSA_F16) return set_error(PQHSA_E_DTYPE, "unknown dtype %d", p->dtype);
+  if (p->head_dim != kD) return set_error(PQHSA_E_SHAPE, "head_dim must be %d, got %d", kD, p->head_dim);
+  if (p->group != 1 && p->group != 2 && p->group != 4 && p->group != 8)
+    return set_error(PQHSA_E_SHAPE, "group must be 1, 2, 4 or 8, got %d", p->group);
+  if (p->num_streams <= 0) return set_error(PQHSA_E_SHAPE, "num_streams must be positive");
+  if (p->num_lists <= 0 || p->num_lists > kLMax)
+    return set_error(PQHSA_E_SHAPE, "num_lists must be in 1..%d, got %d", kLMax, p->num_lists);
+  if (p->slot_capacity <= 0 || p->slot_capacity % 8 != 0)
+    return set_error(PQHSA_E_SHAPE, "slot_capacity must be a positive multiple of 8, got %d", p->slot_capacity);
+  if (p->unit_capacity < p->num_lists + p->slot_capacity / kUnit)
+    return set_error(PQHSA_E_SHAPE, "unit_capacity %d < num_lists + slot_capacity/%d", p->unit_capacity, kUnit);
+  if (p->max_slots < 0 || p->max_slots > p->slot_capacity)
+    return set_error(PQHSA_E_SHAPE, "max_slots %d outside 0..slot_capacity", p->max_slots);
+  if (p->sink_tokens < 0 || p->local_window < 0 || p->max_full < 0)
+    return set_error(PQHSA_E_SHAPE, "sink_tokens, local_window and max_full must be non-negative");
+  if (p->tail_capacity < 0 || p->tail_capacity > p->slot_capacity)
+    return set_error(PQHSA_E_SHAPE, "tail_capacity %d outside 0..slot_capacity", p->tail_capacity);
+  if (!(p->hist_inv_width > 0.f)) return set_error(PQHSA_E_SHAPE, "hist_inv_width must be positive");
+  if (!p->codes || !p->norms || !p->list_ids || !p->slot_pos || !p->unit_off || !p->unit_list || !p->coarse ||
+      !p->codebooks || !p->vmeans || !p->state)
+    return set_error(PQHSA_E_NULL, "an index pool pointer is null");
+  if (need_kv) {
+    if (!p->k_base || !p->v_base) return set_error(PQHSA_E_NULL, "k_base / v_base is null");
+    if (p->block_table != nullptr && (p->block_size <= 0 || p->max_blocks <= 0))
+      return set_error(PQHSA_E_SHAPE, "paged cache needs positive block_size and max_blocks");
+    const int64_t row_align = p->dtype == PQHSA_F32 ? 4 : 8;
+    if (p->stride_block % row_align || p->stride_head % row_align || p->stride_row % row_align)
+      return set_error(PQHSA_E_SHAPE, "KV strides must keep rows 16-byte aligned");
+    if (((uintptr_t)p->k_base | (uintptr_t)p->v_base) & 15)
+      return set_error(PQHSA_E_SHAPE, "k_base / v_base must be 16-byte aligned");
+  }
+  if (need_io) {
+    if (!p->q || !p->out) return set_error(PQHSA_E_NULL, "q / out is null");
+    if (((uintptr_t)p->q | (uintptr_t)p->out) & 15) return set_error(PQHSA_E_SHAPE, "q / out must be 16-byte aligned");
+  }
+  if (need_ws) {
+    if (!p->workspace) return set_error(PQHSA_E_WORKSPACE, "workspace is null");
+    if ((uintptr_t)p->workspace & 255) return set_error(PQHSA_E_WORKSPACE, "workspace must be 256-byte aligned");
+    pqhsa_ws_layout w;
+    layout_of(p, &w);
+    if (p->workspace_bytes < w.total_bytes)
+      return set_error(PQHSA_E_WORKSPACE, "workspace has %zu bytes, %zu needed", p->workspace_bytes, w.total_bytes);
+  }
+  return PQHSA_OK;
+}
+
+}  // namespace pqhsa
+
+using namespace pqhsa;
+
+extern "C" {
+
+int pqhsa_abi_version(void) { return PQHSA_ABI_VERSION; }
+
+const char* pqhsa_last_error_string(void) { return g_err; }
+
+size_t pqhsa_workspace_bytes(const pqhsa_params* p) {
+  if (p == nullptr) return 0;
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  return w.total_bytes;
+}
+
+int pqhsa_workspace_layout(const pqhsa_params* p, pqhsa_ws_layout* out) {
+  if (p == nullptr || out == nullptr) return set_error(PQHSA_E_NULL, "null argument");
+  layout_of(p, out);
+  return PQHSA_OK;
+}
+
+int pqhsa_lut_build(const pqhsa_params* p, void* stream) {
+  if (int rc = check_params(p, true, false, false)) return rc;
+  if (!p->q) return set_error(PQHSA_E_NULL, "q is null");
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  return launch_lut_build(*p, w, (cudaStream_t)stream);
+}
+
+int pqhsa_scan_select(const pqhsa_params* p, void* stream) {
+  if (int rc = check_params(p, true, false, false)) return rc;
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  if (int rc = launch_scan(*p, w, nullptr, (cudaStream_t)stream)) return rc;
+  return launch_select(*p, w, (cudaStream_t)stream);
+}
+
+int pqhsa_attend_merge(const pqhsa_params* p, void* stream) {
+  if (int rc = check_params(p, true, true, true)) return rc;
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  if (int rc = launch_attend(*p, w, (cudaStream_t)stream)) return rc;
+  return launch_merge(*p, w, (cudaStream_t)stream);
+}
+
+int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
+  if (int rc = check_params(p, true, true, true)) return rc;
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int rc = launch_lut_build(*p, w, st)) return rc;
+  if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
+  if (int rc = launch_select(*p, w, st)) return rc;
+  if (int rc = launch_attend(*p, w, st)) return rc;
+  return launch_merge(*p, w, st);
+}
+
+int pqhsa_append_kv(const pqhsa_params* p, const void* new_k, const void* new_v, void* stream) {
+  if (int rc = check_params(p, false, true, false)) return rc;
+  if (!new_k || !new_v) return set_error(PQHSA_E_NULL, "new_k / new_v is null");
+  return launch_append_kv(*p, new_k, new_v, (cudaStream_t)stream);
+}
+
+int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t uniform_count, void* stream) {
+  if (int rc = check_params(p, false, true, false)) return rc;
+  if (!p->vsum || !p->vcnt) return set_error(PQHSA_E_NULL, "vsum / vcnt is null");
+  if (enc_count == nullptr && uniform_count < 0) return set_error(PQHSA_E_SHAPE, "uniform_count must be >= 0");
+  if (enc_count == nullptr && uniform_count == 0) return PQHSA_OK;
+  return launch_append_encode(*p, enc_count, uniform_count, (cudaStream_t)stream);
+}
+
+int pqhsa_scan_scores(const pqhsa_params* p, float* scores, void* stream) {
+  if (int rc = check_params(p, true, false, false)) return rc;
+  if (!scores) return set_error(PQHSA_E_NULL, "scores is null");
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  return launch_scan(*p, w, scores, (cudaStream_t)stream);
+}
+
+int pqhsa_topk_radix(const float* scores, int32_t rows, int32_t n, int64_t row_stride, int32_t k, int32_t* out_idx,
+                     float* out_val, void* stream) {
+  if (!scores || !out_idx || !out_val) return set_error(PQHSA_E_NULL, "null argument");
+  if (rows <= 0 || n < 0 || k < 0 || k > n || row_stride < n)
+    return set_error(PQHSA_E_SHAPE, "need rows > 0, 0 <= k <= n <= row_stride");
+  if (k == 0) return PQHSA_OK;
+  return launch_topk(scores, rows, n, row_stride, k, out_idx, out_val, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,213 @@
+// Appending decoded tokens: the raw K/V row write and the incremental encode
+// of keys that have left the local window into the IVF-PQ index.
+//
+// append_kv      replaces pq_append_prep (pq_hsa/kernels/cuda/pq_fused_h20.cu:2888-2922).
+// append_encode  mirrors IVFPQIndex.add with fixed codebooks
+//                (pq_hsa/index/ivfpq.py:598-645): |k| and direction
+//                (:1052-1059), nearest list by Euclidean distance (:1001-1005),
+//                residual (:1012-1016), nearest code word per subspace
+//                (pq_hsa/index/pq.py:97-115), nibble packing
+//                (pq_hsa/index/packing.py:6-34); and the running per-list value
+//                mean of pq_hsa/attention/kv_cache.py:730-776.
+// All arithmetic is fp32 on the stored element values; ties go to the lower
+// index as torch.argmin does.
+#include "common.cuh"
+
+namespace pqhsa {
+
+constexpr int kEncThreads = 256;
+
+template <typename E>
+__global__ void __launch_bounds__(kD) append_kv_kernel(E* __restrict__ kb, E* __restrict__ vb, KvAddr kv,
+                                                       int32_t* __restrict__ state, const E* __restrict__ nk,
+                                                       const E* __restrict__ nv) {
+  const int s = blockIdx.x;
+  int32_t* st = state + (size_t)s * kST;
+  const int pos = st[PQHSA_ST_SEQ_LEN];
+  const long long off = kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], pos);
+  kb[off + threadIdx.x] = nk[(size_t)s * kD + threadIdx.x];
+  vb[off + threadIdx.x] = nv[(size_t)s * kD + threadIdx.x];
+  __syncthreads();
+  if (threadIdx.x == 0) st[PQHSA_ST_SEQ_LEN] = pos + 1;
+}
+
+struct EncodeArgs {
+  uint32_t* codes;
+  void* norms;
+  uint16_t* list_ids;
+  int32_t* slot_pos;
+  const void* coarse;
+  const void* codebooks;
+  void* vmeans;
+  float* vsum;
+  int32_t* vcnt;
+  int32_t* state;
+  const void* k_base;
+  const void* v_base;
+  KvAddr kv;
+  const int32_t* enc_count;
+  int uniform_count, cap, tail_cap, num_lists, sink;
+};
+
+template <typename E>
+__global__ void __launch_bounds__(kEncThreads) append_encode_kernel(const EncodeArgs a) {
+  __shared__ float unit[kD];
+  __shared__ float resid[kD];
+  __shared__ float red[kEncThreads / 32];
+  __shared__ float best_d[kEncThreads / 32];
+  __shared__ int best_l[kEncThreads / 32];
+  __shared__ uint32_t code_sh;
+  __shared__ int list_sh;
+  const int s = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int32_t* st = a.state + (size_t)s * kST;
+  const int count = a.enc_count ? a.enc_count[s] : a.uniform_count;
+  const int n_sorted = st[PQHSA_ST_N_SORTED];
+  int n_tail = st[PQHSA_ST_N_TAIL];
+  const int seq_len = st[PQHSA_ST_SEQ_LEN];
+  const int nl = st[PQHSA_ST_N_LISTS];
+  const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
+  const int sink_end = min(a.sink, seq_len);
+  const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
+  const E* books = static_cast<const E*>(a.codebooks) + (size_t)s * kM * kC * kSub;
+  const E* kb = static_cast<const E*>(a.k_base);
+  const E* vb = static_cast<const E*>(a.v_base);
+
+  for (int it = 0; it < count; ++it) {
+    const int pos = sink_end + n_sorted + n_tail;
+    const int slot = n_sorted + n_tail;
+    // never index a token that is not in the cache, never overrun the pool
+    if (pos >= seq_len || slot >= a.cap || n_tail >= a.tail_cap) break;
+    const long long off = a.kv.offset(req, head, pos);
+
+    // |k| and the unit direction
+    float kval = 0.f;
+    if (tid < kD) kval = to_f(kb[off + tid]);
+    const float sq = warp_sum(kval * kval);
+    __syncthreads();
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kEncThreads / 32; ++i) tot += red[i];
+    const float nrm = fmaxf(sqrtf(tot), 1e-12f);
+    if (tid < kD) unit[tid] = kval / nrm;
+    __syncthreads();
+
+    // nearest list: argmin_l |u - c_l|^2 = |c_l|^2 - 2 u.c_l (+ |u|^2, constant)
+    float bd = __builtin_huge_valf();
+    int bl = 0x7fffffff;
+    for (int l = warp; l < nl; l += kEncThreads / 32) {
+      float c[4];
+      load4(coarse + (size_t)l * kD + lane * 4, c);
+      float dist = 0.f;
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const float df = unit[lane * 4 + d] - c[d];
+        dist = fmaf(df, df, dist);
+      }
+      dist = warp_sum(dist);
+      if (dist < bd) {  // l ascends, so strict < keeps the lowest index on ties
+        bd = dist;
+        bl = l;
+      }
+    }
+    if (lane == 0) {
+      best_d[warp] = bd;
+      best_l[warp] = bl;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float d0 = best_d[0];
+      int l0 = best_l[0];
+      for (int i = 1; i < kEncThreads / 32; ++i)
+        if (best_d[i] < d0 || (best_d[i] == d0 && best_l[i] < l0)) {
+          d0 = best_d[i];
+          l0 = best_l[i];
+        }
+      list_sh = l0;
+      code_sh = 0u;
+    }
+    __syncthreads();
+    const int lid = list_sh;
+    if (tid < kD) resid[tid] = unit[tid] - to_f(coarse[(size_t)lid * kD + tid]);
+    __syncthreads();
+
+    // nearest code word per subspace: thread (m, c) for tid < 128, 16 lanes per subspace
+    if (tid < kM * kC) {
+      const int m = tid / kC, c = tid % kC;
+      const E* cw = books + (size_t)tid * kSub;
+      float dist = 0.f;
+#pragma unroll
+      for (int d = 0; d < kSub; ++d) {
+        const float df = resid[m * kSub + d] - to_f(cw[d]);
+        dist = fmaf(df, df, dist);
+      }
+      int bc = c;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        const float od = __shfl_xor_sync(0xffffffffu, dist, o);
+        const int oc = __shfl_xor_sync(0xffffffffu, bc, o);
+        if (od < dist || (od == dist && oc < bc)) {
+          dist = od;
+          bc = oc;
+        }
+      }
+      if (c == 0) atomicOr(&code_sh, (uint32_t)bc << (4 * m));
+    }
+    __syncthreads();
+
+    if (tid == 0) {
+      a.codes[(size_t)s * a.cap + slot] = code_sh;
+      static_cast<E*>(a.norms)[(size_t)s * a.cap + slot] = from_f<E>(nrm);
+      a.list_ids[(size_t)s * a.cap + slot] = (uint16_t)lid;
+      a.slot_pos[(size_t)s * a.cap + slot] = pos;
+    }
+    // running value mean of the list
+    if (tid < kD) {
+      const size_t vi = ((size_t)s * a.num_lists + lid) * kD + tid;
+      const float nsum = a.vsum[vi] + to_f(vb[off + tid]);
+      const int ncnt = a.vcnt[(size_t)s * a.num_lists + lid] + 1;
+      a.vsum[vi] = nsum;
+      static_cast<E*>(a.vmeans)[vi] = from_f<E>(nsum / (float)ncnt);
+    }
+    __syncthreads();
+    if (tid == 0) a.vcnt[(size_t)s * a.num_lists + lid] += 1;
+    ++n_tail;
+    __syncthreads();
+  }
+  if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail;
+}
+
+int launch_append_kv(const pqhsa_params& p, const void* k, const void* v, cudaStream_t st) {
+  PQHSA_DISPATCH_E(p.dtype, append_kv_kernel<E><<<p.num_streams, kD, 0, st>>>(
+      static_cast<E*>(const_cast<void*>(p.k_base)), static_cast<E*>(const_cast<void*>(p.v_base)), make_kvaddr(p),
+      static_cast<int32_t*>(p.state), static_cast<const E*>(k), static_cast<const E*>(v)));
+  return check_launch("append_kv");
+}
+
+int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni, cudaStream_t st) {
+  EncodeArgs a;
+  a.codes = static_cast<uint32_t*>(const_cast<void*>(p.codes));
+  a.norms = const_cast<void*>(p.norms);
+  a.list_ids = static_cast<uint16_t*>(const_cast<void*>(p.list_ids));
+  a.slot_pos = static_cast<int32_t*>(const_cast<void*>(p.slot_pos));
+  a.coarse = p.coarse;
+  a.codebooks = p.codebooks;
+  a.vmeans = const_cast<void*>(p.vmeans);
+  a.vsum = static_cast<float*>(p.vsum);
+  a.vcnt = static_cast<int32_t*>(p.vcnt);
+  a.state = static_cast<int32_t*>(p.state);
+  a.k_base = p.k_base;
+  a.v_base = p.v_base;
+  a.kv = make_kvaddr(p);
+  a.enc_count = cnt;
+  a.uniform_count = uni;
+  a.cap = p.slot_capacity;
+  a.tail_cap = p.tail_capacity;
+  a.num_lists = p.num_lists;
+  a.sink = p.sink_tokens;
+  PQHSA_DISPATCH_E(p.dtype, append_encode_kernel<E><<<p.num_streams, kEncThreads, 0, st>>>(a));
+  return check_launch("append_encode");
+}
+
+}  // namespace pqhsa

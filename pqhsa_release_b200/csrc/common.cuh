@@ -1,0 +1,203 @@
+// Shared device/host helpers of the PQ-HSA sm_100a decode kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "pqhsa.h"
+
+namespace pqhsa {
+
+constexpr int kD = PQHSA_HEAD_DIM;      // head dimension
+constexpr int kM = PQHSA_SUBSPACES;     // PQ subspaces
+constexpr int kC = PQHSA_CODES;         // code words per subspace
+constexpr int kSub = kD / kM;           // dims per subspace
+constexpr int kLMax = PQHSA_MAX_LISTS;  // IVF lists
+constexpr int kUnit = PQHSA_UNIT_KEYS;  // slots per scan unit
+constexpr int kBins = PQHSA_HIST_BINS;  // selection histogram bins
+constexpr int kRI = PQHSA_RI_INTS;      // ints of row_info per row
+constexpr int kST = PQHSA_STATE_INTS;   // ints of state per stream
+constexpr int kChunk = 256;             // attend entries per split-K chunk
+constexpr int kPartial = kD + 2;        // floats per split-K partial (max, sum, acc[D])
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kNegInf = -__builtin_huge_valf();
+
+// host-side error plumbing (abi.cu)
+int set_error(int code, const char* fmt, ...);
+int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io);
+int check_launch(const char* what);
+void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o);
+
+// kernel launchers, one translation unit each; all return a pqhsa_status
+int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cudaStream_t st);
+int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+int launch_append_kv(const pqhsa_params& p, const void* k, const void* v, cudaStream_t st);
+int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni, cudaStream_t st);
+int launch_topk(const float* scores, int rows, int n, int64_t stride, int k, int32_t* oi, float* ov,
+                cudaStream_t st);
+
+#define PQHSA_DISPATCH_E(dtype, ...)                                   \
+  switch (dtype) {                                                     \
+    case PQHSA_F32: { using E = float; __VA_ARGS__; break; }           \
+    case PQHSA_BF16: { using E = __nv_bfloat16; __VA_ARGS__; break; }  \
+    case PQHSA_F16: { using E = __half; __VA_ARGS__; break; }          \
+    default: return set_error(PQHSA_E_DTYPE, "unknown dtype %d", (int)(dtype)); \
+  }
+
+#define PQHSA_DISPATCH_G(group, ...)                                   \
+  switch (group) {                                                     \
+    case 1: { constexpr int G = 1; __VA_ARGS__; break; }               \
+    case 2: { constexpr int G = 2; __VA_ARGS__; break; }               \
+    case 4: { constexpr int G = 4; __VA_ARGS__; break; }               \
+    case 8: { constexpr int G = 8; __VA_ARGS__; break; }               \
+    default: return set_error(PQHSA_E_SHAPE, "unsupported group size %d", (int)(group)); \
+  }
+
+#ifdef __CUDACC__
+
+// ---- element access ---------------------------------------------------
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+
+template <typename E> __device__ __forceinline__ E from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// 8 consecutive elements, 16-byte (2-byte types) or 32-byte (float) aligned
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+// 4 consecutive elements, 8-byte (2-byte types) or 16-byte (float) aligned
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 r = __ldg(reinterpret_cast<const uint2*>(p));
+  v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+  v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+__device__ __forceinline__ void load4(const __half* p, float (&v)[4]) {
+  const uint2 r = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- the approximate logit --------------------------------------------
+// logit = (sum_{m=0..7} lut[m][nibble_m] + list_score) * |k|, with the adds in
+// subspace order from zero, as pq_hsa/kernels/lut_scan.py:101-114 accumulates,
+// then the list bias, then the norm (pq_hsa/index/ivfpq.py:1093-1118).  The
+// scale and |q| are folded into lut and list_score.  Written with explicit
+// rounding intrinsics so that every kernel that re-scores a slot reproduces
+// the scan's value bit for bit.
+__device__ __forceinline__ float finish_logit(float pq, float list_score, float knorm) {
+  return __fmul_rn(__fadd_rn(pq, list_score), knorm);
+}
+// lut: 128 floats [m][c] of one query row
+__device__ __forceinline__ float pq_sum_row(const float* lut, uint32_t code) {
+  float acc = lut[code & 15u];
+#pragma unroll
+  for (int m = 1; m < kM; ++m) acc = __fadd_rn(acc, lut[m * kC + ((code >> (4 * m)) & 15u)]);
+  return acc;
+}
+
+// histogram bin of a logit: monotone non-decreasing in the logit, so a larger
+// bin implies a strictly larger logit.
+__device__ __forceinline__ int logit_bin(float logit, float lo, float inv_w) {
+  const float t = __fmul_rn(__fsub_rn(logit, lo), inv_w);
+  int b = __float2int_rd(t);
+  b = b < 0 ? 0 : b;
+  return b > kBins - 1 ? kBins - 1 : b;
+}
+
+// order-preserving 32-bit key of a float (larger float <=> larger key)
+__device__ __forceinline__ uint32_t float_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// K = min(max(ceil(N * fraction), 0), N) in double precision
+// (pq_hsa/attention/sparse_attention.py:1779-1783); fraction < 0 selects the fixed count.
+__device__ __forceinline__ int resolve_topk(int n, double fraction, int fixed) {
+  if (n <= 0) return 0;
+  long long k = fixed;
+  if (fraction >= 0.0) k = (long long)ceil((double)n * fraction);
+  if (k < 0) k = 0;
+  if (k > n) k = n;
+  return (int)k;
+}
+
+// address (in elements) of token `t` of request `req`, KV head `head`
+struct KvAddr {
+  const int32_t* block_table;
+  int32_t max_blocks, block_size;
+  int64_t stride_block, stride_head, stride_row;
+  __device__ __forceinline__ int64_t offset(int req, int head, int t) const {
+    int64_t blk = req, row = t;
+    if (block_table != nullptr) {
+      blk = __ldg(block_table + (int64_t)req * max_blocks + t / block_size);
+      row = t % block_size;
+    }
+    return blk * stride_block + (int64_t)head * stride_head + row * stride_row;
+  }
+};
+__host__ __device__ inline KvAddr make_kvaddr(const pqhsa_params& p) {
+  KvAddr a;
+  a.block_table = p.block_table;
+  a.max_blocks = p.max_blocks;
+  a.block_size = p.block_size;
+  a.stride_block = p.stride_block;
+  a.stride_head = p.stride_head;
+  a.stride_row = p.stride_row;
+  return a;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace pqhsa
