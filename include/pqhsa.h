@@ -30,7 +30,7 @@ extern "C" {
 #define PQHSA_CODES 16
 #define PQHSA_HEAD_DIM 128
 #define PQHSA_MAX_LISTS 512
-#define PQHSA_UNIT_KEYS 256  /* a scan unit = at most this many slots of one list */
+#define PQHSA_UNIT_KEYS 128  /* a scan unit = at most this many slots of one list */
 #define PQHSA_HIST_BINS 4096 /* selection histogram resolution per query row */
 
 enum pqhsa_status {
@@ -71,8 +71,10 @@ enum pqhsa_state_slot {
  * benchmarks/e2e_pq_param_sweep.py:4182-4305):
  *   codes     uint32 [S, cap]      8 nibbles, subspace s in bits 4s..4s+3
  *   norms     E      [S, cap]      |k|, clamped at 1e-12
+ *   norm_max  float  [S]           upper bound of the stream's norms (sizes the histogram)
  *   list_ids  uint16 [S, cap]
  *   slot_pos  int32  [S, cap]      token position of the slot's key
+ *   slot_unit uint16 [S, cap]      scan unit holding the slot (sorted region only)
  *   unit_off  int32  [S, unit_capacity + 1]   slot ranges of the scan units
  *   unit_list uint16 [S, unit_capacity]       list of each unit
  *   coarse    E      [S, num_lists, 128]      list centroids (unit-direction space)
@@ -108,13 +110,13 @@ typedef struct pqhsa_params {
   double top_fraction;     /* K = min(max(ceil(N * f), 0), N) in double, as
                               pq_hsa/attention/sparse_attention.py:1779-1783 */
   float scale;             /* softmax scale, 1/sqrt(D) unless the model says otherwise */
-  float hist_lo;           /* selection histogram: bin = (logit - lo) * inv_width, clamped */
-  float hist_inv_width;
-  float reserved1;
+  float hist_lo;           /* selection histogram: bin = (logit - lo) * inv_width, clamped;       */
+  float hist_inv_width;    /* inv_width <= 0 (default) sizes the bins per query row from a bound   */
+  float reserved1;         /* on |logit|; the selection is exact for any choice                    */
 
-  const void *codes, *norms, *list_ids, *slot_pos, *unit_off, *unit_list;
+  const void *codes, *norms, *list_ids, *slot_pos, *slot_unit, *unit_off, *unit_list;
   const void *coarse, *codebooks, *vmeans;
-  void *vsum, *vcnt, *state;
+  void *vsum, *vcnt, *state, *norm_max;
 
   const void *k_base, *v_base;
   const int32_t *block_table;
@@ -142,9 +144,8 @@ typedef struct pqhsa_ws_layout {
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail     */
   size_t row_info;     /* int32  [R, 8]: K, threshold bin, #above, #selected, #candidates, tail_cap */
   size_t row_amax;     /* float  [R]   max approximate logit                          */
+  size_t row_bin;      /* float  [R, 2]  histogram origin and 1 / bin width of the row */
   size_t sel_slot;     /* int32  [R, kcap]  selected slots (unordered)                */
-  size_t sel_logit;    /* float  [R, kcap]  their approximate logits                  */
-  size_t sel_list;     /* uint16 [R, kcap]  their lists                               */
   size_t cand_slot;    /* int32  [R, cap]   slots inside the threshold bin            */
   size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)   */
   int32_t kcap;        /* row stride of sel_* */
@@ -194,6 +195,17 @@ int pqhsa_attend_merge(const pqhsa_params* p, void* stream);
  * the reference's per-layer CUDA graph body
  * (benchmarks/e2e_pq_param_sweep.py:6308-6969). */
 int pqhsa_decode_step(const pqhsa_params* p, void* stream);
+
+/* One kernel group of the step on its own, for per-kernel timing and profiling:
+ * the same launches pqhsa_decode_step makes, in the same order. */
+enum pqhsa_stage {
+  PQHSA_STAGE_LUT = 0,      /* table construction                      */
+  PQHSA_STAGE_SCAN = 1,     /* code scan                               */
+  PQHSA_STAGE_SELECT = 2,   /* threshold + collect + finish            */
+  PQHSA_STAGE_ATTEND = 3,   /* exact attention partials (the gather)   */
+  PQHSA_STAGE_MERGE = 4     /* background + final merge                */
+};
+int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
 
 /* Write one new K/V row per stream into the cache at position seq_len and bump
  * seq_len (contiguous or paged addressing as above).  new_k/new_v: E [S, 128].

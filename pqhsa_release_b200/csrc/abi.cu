@@ -56,9 +56,8 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
   o->row_info = take(R * kRI * sizeof(int32_t));
   o->row_amax = take(R * sizeof(float));
+  o->row_bin = take(R * 2 * sizeof(float));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
-  o->sel_logit = take(R * (size_t)o->kcap * sizeof(float));
-  o->sel_list = take(R * (size_t)o->kcap * sizeof(uint16_t));
   o->cand_slot = take(R * cap * sizeof(int32_t));
   o->partial = take(R * (size_t)o->chunks * kPartial * sizeof(float));
   o->total_bytes = off;
@@ -85,9 +84,8 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
     return set_error(PQHSA_E_SHAPE, "sink_tokens, local_window and max_full must be non-negative");
   if (p->tail_capacity < 0 || p->tail_capacity > p->slot_capacity)
     return set_error(PQHSA_E_SHAPE, "tail_capacity %d outside 0..slot_capacity", p->tail_capacity);
-  if (!(p->hist_inv_width > 0.f)) return set_error(PQHSA_E_SHAPE, "hist_inv_width must be positive");
-  if (!p->codes || !p->norms || !p->list_ids || !p->slot_pos || !p->unit_off || !p->unit_list || !p->coarse ||
-      !p->codebooks || !p->vmeans || !p->state)
+  if (!p->codes || !p->norms || !p->list_ids || !p->slot_pos || !p->slot_unit || !p->unit_off || !p->unit_list ||
+      !p->coarse || !p->codebooks || !p->vmeans || !p->state || !p->norm_max)
     return set_error(PQHSA_E_NULL, "an index pool pointer is null");
   if (need_kv) {
     if (!p->k_base || !p->v_base) return set_error(PQHSA_E_NULL, "k_base / v_base is null");
@@ -171,6 +169,22 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
   if (int rc = launch_select(*p, w, st)) return rc;
   if (int rc = launch_attend(*p, w, st)) return rc;
   return launch_merge(*p, w, st);
+}
+
+int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
+  if (int rc = check_params(p, true, stage >= PQHSA_STAGE_ATTEND, stage >= PQHSA_STAGE_ATTEND)) return rc;
+  if (stage == PQHSA_STAGE_LUT && !p->q) return set_error(PQHSA_E_NULL, "q is null");
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (stage) {
+    case PQHSA_STAGE_LUT: return launch_lut_build(*p, w, st);
+    case PQHSA_STAGE_SCAN: return launch_scan(*p, w, nullptr, st);
+    case PQHSA_STAGE_SELECT: return launch_select(*p, w, st);
+    case PQHSA_STAGE_ATTEND: return launch_attend(*p, w, st);
+    case PQHSA_STAGE_MERGE: return launch_merge(*p, w, st);
+    default: return set_error(PQHSA_E_SHAPE, "unknown stage %d", stage);
+  }
 }
 
 int pqhsa_append_kv(const pqhsa_params* p, const void* new_k, const void* new_v, void* stream) {

@@ -42,6 +42,7 @@ struct EncodeArgs {
   float* vsum;
   int32_t* vcnt;
   int32_t* state;
+  float* norm_max;
   const void* k_base;
   const void* v_base;
   KvAddr kv;
@@ -161,6 +162,8 @@ __global__ void __launch_bounds__(kEncThreads) append_encode_kernel(const Encode
       static_cast<E*>(a.norms)[(size_t)s * a.cap + slot] = from_f<E>(nrm);
       a.list_ids[(size_t)s * a.cap + slot] = (uint16_t)lid;
       a.slot_pos[(size_t)s * a.cap + slot] = pos;
+      const float stored = to_f(from_f<E>(nrm));
+      if (stored > a.norm_max[s]) a.norm_max[s] = stored;
     }
     // running value mean of the list
     if (tid < kD) {
@@ -197,6 +200,7 @@ int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni,
   a.vsum = static_cast<float*>(p.vsum);
   a.vcnt = static_cast<int32_t*>(p.vcnt);
   a.state = static_cast<int32_t*>(p.state);
+  a.norm_max = static_cast<float*>(p.norm_max);
   a.k_base = p.k_base;
   a.v_base = p.v_base;
   a.kv = make_kvaddr(p);

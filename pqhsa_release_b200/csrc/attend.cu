@@ -9,9 +9,13 @@
 // Work item = (query row, chunk of 256 entries); entry e of a row is the e-th
 // row of [sink | local | selected].  A persistent grid strides over the items.
 // Inside a CTA each of the 8 warps owns 32 entries:
-//   1. lane-parallel: entry -> token position -> cache offset; for a selected
-//      entry also its approximate logit (re-scored from the code, bit-identical
-//      to the scan) and list id, stored for the background subtraction;
+//   1. lane-parallel: entry -> token position -> cache offset.  A selected entry
+//      also leaves the approximate side of the softmax here: its logit is
+//      re-scored from the code (bit-identical to the scan) and exactly the term
+//      the scan added for it is subtracted from its unit's exp-sum (a selected
+//      tail slot has its stored logit set to -inf).  This is the
+//      "- old_exact_exp" of pq_hsa/attention/sparse_attention.py:985-1009,
+//      done per unit so that no cancellation error is left behind;
 //   2. half-warp per K/V row: 16 lanes x 16 bytes cover one 256-byte bf16 row
 //      (2 x 16 bytes per lane for fp32), four row pairs (8 K rows + 8 V rows)
 //      are in flight per warp before the first is consumed;
@@ -33,16 +37,18 @@ struct AttendArgs {
   const uint32_t* codes;
   const void* norms;
   const uint16_t* list_ids;
+  const uint16_t* slot_unit;
   const int32_t* slot_pos;
   const int32_t* state;
   const float* lut;
   const float* list_scores;
   const int32_t* row_info;
   const int32_t* sel_slot;
-  float* sel_logit;
-  uint16_t* sel_list;
+  const float* unit_max;
+  float* unit_sum;
+  float* tail_logit;
   float* partial;
-  int R, G, cap, kcap, chunks, sink;
+  int R, G, cap, ucap, tail_cap, kcap, chunks, sink;
   float scale;
 };
 
@@ -101,7 +107,8 @@ __global__ void __launch_bounds__(kAttThreads, 2) attend_kernel(const AttendArgs
     const int row = (int)(item % a.R);
     const int s = row / a.G;
     const int32_t* st = a.state + (size_t)s * kST;
-    const int n_idx = st[PQHSA_ST_N_SORTED] + st[PQHSA_ST_N_TAIL];
+    const int n_sorted = st[PQHSA_ST_N_SORTED];
+    const int n_idx = n_sorted + st[PQHSA_ST_N_TAIL];
     const int seq_len = st[PQHSA_ST_SEQ_LEN];
     const int sink_end = min(a.sink, seq_len);
     const int retr_end = sink_end + n_idx;
@@ -123,22 +130,24 @@ __global__ void __launch_bounds__(kAttThreads, 2) attend_kernel(const AttendArgs
 
     // 1. entry metadata, one entry per lane
     const int e = c * kChunk + warp * 32 + lane;
-    const bool valid = e < total;
     long long off = 0;
-    if (valid) {
+    if (e < total) {
       int pos;
       if (e < F) {
         pos = e < sink_end ? e : retr_end + (e - sink_end);
       } else {
-        const int j = e - F;
-        const int slot = a.sel_slot[(size_t)row * a.kcap + j];
+        const int slot = a.sel_slot[(size_t)row * a.kcap + (e - F)];
         pos = a.slot_pos[(size_t)s * a.cap + slot];
-        const uint32_t code = __ldg(a.codes + (size_t)s * a.cap + slot);
-        const int lid = a.list_ids[(size_t)s * a.cap + slot];
-        const float kn = to_f(static_cast<const E*>(a.norms)[(size_t)s * a.cap + slot]);
-        const float x = finish_logit(pq_sum_row(lut_s, code), __ldg(a.list_scores + (size_t)row * kLMax + lid), kn);
-        a.sel_logit[(size_t)row * a.kcap + j] = x;
-        a.sel_list[(size_t)row * a.kcap + j] = (uint16_t)lid;
+        if (slot < n_sorted) {
+          const uint32_t code = __ldg(a.codes + (size_t)s * a.cap + slot);
+          const int lid = a.list_ids[(size_t)s * a.cap + slot];
+          const int u = a.slot_unit[(size_t)s * a.cap + slot];
+          const float kn = to_f(static_cast<const E*>(a.norms)[(size_t)s * a.cap + slot]);
+          const float x = finish_logit(pq_sum_row(lut_s, code), __ldg(a.list_scores + (size_t)row * kLMax + lid), kn);
+          atomicAdd(a.unit_sum + (size_t)row * a.ucap + u, -unit_term(x, a.unit_max[(size_t)row * a.ucap + u]));
+        } else {
+          a.tail_logit[(size_t)row * a.tail_cap + (slot - n_sorted)] = kNegInf;
+        }
       }
       off = a.kv.offset(req, head, pos);
     }
@@ -253,18 +262,22 @@ int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.codes = static_cast<const uint32_t*>(p.codes);
   a.norms = p.norms;
   a.list_ids = static_cast<const uint16_t*>(p.list_ids);
+  a.slot_unit = static_cast<const uint16_t*>(p.slot_unit);
   a.slot_pos = static_cast<const int32_t*>(p.slot_pos);
   a.state = static_cast<const int32_t*>(p.state);
   a.lut = reinterpret_cast<const float*>(ws + w.lut);
   a.list_scores = reinterpret_cast<const float*>(ws + w.list_scores);
   a.row_info = reinterpret_cast<const int32_t*>(ws + w.row_info);
   a.sel_slot = reinterpret_cast<const int32_t*>(ws + w.sel_slot);
-  a.sel_logit = reinterpret_cast<float*>(ws + w.sel_logit);
-  a.sel_list = reinterpret_cast<uint16_t*>(ws + w.sel_list);
+  a.unit_max = reinterpret_cast<const float*>(ws + w.unit_max);
+  a.unit_sum = reinterpret_cast<float*>(ws + w.unit_sum);
+  a.tail_logit = reinterpret_cast<float*>(ws + w.tail_logit);
   a.partial = reinterpret_cast<float*>(ws + w.partial);
   a.R = p.num_streams * p.group;
   a.G = p.group;
   a.cap = p.slot_capacity;
+  a.ucap = p.unit_capacity;
+  a.tail_cap = w.tail_cap;
   a.kcap = w.kcap;
   a.chunks = w.chunks;
   a.sink = p.sink_tokens;

@@ -147,6 +147,13 @@ __device__ __forceinline__ float pq_sum_row(const float* lut, uint32_t code) {
   return acc;
 }
 
+// Contribution of one key to the exp-sum of its scan unit, relative to the
+// unit's maximum logit.  The scan adds it and the attend kernel subtracts it for
+// a selected key: same inputs, same instructions, so the removal is exact.
+__device__ __forceinline__ float unit_term(float logit, float unit_max) {
+  return ex2(__fmul_rn(__fsub_rn(logit, unit_max), kLog2e));
+}
+
 // histogram bin of a logit: monotone non-decreasing in the logit, so a larger
 // bin implies a strictly larger logit.
 __device__ __forceinline__ int logit_bin(float logit, float lo, float inv_w) {

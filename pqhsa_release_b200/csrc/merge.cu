@@ -1,22 +1,24 @@
 // Per-list log-sum-exp background and the final three-source softmax merge.
 //
-//   mass[g][l] = sum_{n in list l} exp(approx[g][n] - M) - sum_{t selected, in l} exp(approx[g][t] - M)
-//   denom[g]   = sum_l (mass before the subtraction) - sum_sel exp(approx - M)
-//                + sum_{sink, local, selected} exp(exact - M)
+//   mass[g][l] = sum over the UNSELECTED keys n of list l of exp(approx[g][n] - M)
+//   denom[g]   = sum_l mass[g][l] + sum_{sink, local, selected} exp(exact - M)
 //   out[g]     = (sum exp(exact - M) v + sum_l mass[g][l] * vmean[l]) / denom[g]
 //
-// with M the maximum over all sources, exactly the centroid-mode merge of
-// pq_hsa/attention/sparse_attention.py:887-1012; it replaces pq_attend_bg and
-// pq_attend_reduce_mw (pq_hsa/kernels/cuda/pq_fused_h20.cu:2150-2402) and takes
-// the list-space form of the background argued for at :2043-2058: the value
-// means of a stream are read once for all G rows.
+// with M the maximum over all sources: the centroid-mode merge of
+// pq_hsa/attention/sparse_attention.py:887-1012 (there the selected keys'
+// approximate mass is added and subtracted again; here the attend kernel has
+// already taken each selected key out of its unit's sum).  It replaces
+// pq_attend_bg and pq_attend_reduce_mw
+// (pq_hsa/kernels/cuda/pq_fused_h20.cu:2150-2402) and takes the list-space form
+// of the background argued for at :2043-2058: the value means of a stream are
+// read once for all G rows.
 //
-// One CTA per stream.  The per-unit (max, sum) pairs from the scan are folded
-// into list masses in shared memory (a list owns a few consecutive units), the
-// tail logits and the selected keys' approximate logits are scattered with
-// shared-memory float atomics, then a [G x L] x [L x 128] product with the
-// value means and the split-K partials of the exact part finish the row.
-// Everything is in the base-2 domain (logit * log2 e).
+// One CTA per stream.  The per-unit (max, sum) pairs are folded into list
+// masses in shared memory (a list owns a few consecutive units), the tail logits
+// are scattered with shared-memory float atomics, then a [G x L] x [L x 128]
+// product with the value means and the split-K partials of the exact part
+// finish the rows.  Exponents are base 2: exp(x - M) = 2^(x * log2e - M2), the
+// fused multiply-add keeps the difference accurate for large logits.
 #include "common.cuh"
 
 namespace pqhsa {
@@ -34,10 +36,8 @@ struct MergeArgs {
   const float* unit_max;
   const float* unit_sum;
   const float* tail_logit;
-  const float* sel_logit;
-  const uint16_t* sel_list;
   const float* partial;
-  int cap, ucap, tail_cap, kcap, chunks, sink, num_lists;
+  int cap, ucap, tail_cap, chunks, sink, num_lists;
 };
 
 template <int THREADS>
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kMrgThreads) merge_kernel(const MergeArgs a) {
     const int row = s * G + g;
     const int K = a.row_info[(size_t)row * kRI + PQHSA_RI_K];
     nchunks[g] = (F + K + kChunk - 1) / kChunk;
-    // M = max(max approximate logit, max exact logit), base 2
+    // M2 = max(max approximate logit, max exact logit) in the base-2 domain
     float m = a.row_amax[row] * kLog2e;
     for (int c = 0; c < nchunks[g]; ++c) m = fmaxf(m, a.partial[((size_t)row * a.chunks + c) * kPartial]);
     if (tid == 0) sM[g] = m;
@@ -85,36 +85,28 @@ __global__ void __launch_bounds__(kMrgThreads) merge_kernel(const MergeArgs a) {
   for (int g = 0; g < G; ++g) {
     const int row = s * G + g;
     const float M = sM[g];
-    const int K = a.row_info[(size_t)row * kRI + PQHSA_RI_K];
-    // list masses from the scan units and the tail
-    float before = 0.f;
+    float approx = 0.f;
     for (int u = tid; u < n_units; u += kMrgThreads) {
-      const float v = a.unit_sum[(size_t)row * a.ucap + u] * ex2(a.unit_max[(size_t)row * a.ucap + u] * kLog2e - M);
+      const float v = a.unit_sum[(size_t)row * a.ucap + u] * ex2(fmaf(a.unit_max[(size_t)row * a.ucap + u], kLog2e, -M));
       atomicAdd(&mass[g][a.unit_list[(size_t)s * a.ucap + u]], v);
-      before += v;
+      approx += v;
     }
     for (int t = tid; t < n_tail; t += kMrgThreads) {
-      const float v = ex2(a.tail_logit[(size_t)row * a.tail_cap + t] * kLog2e - M);
-      atomicAdd(&mass[g][a.list_ids[(size_t)s * a.cap + n_sorted + t]], v);
-      before += v;
-    }
-    __syncthreads();
-    // remove the selected keys' approximate mass
-    float old = 0.f;
-    for (int j = tid; j < K; j += kMrgThreads) {
-      const float v = ex2(a.sel_logit[(size_t)row * a.kcap + j] * kLog2e - M);
-      atomicAdd(&mass[g][a.sel_list[(size_t)row * a.kcap + j]], -v);
-      old += v;
+      const float x = a.tail_logit[(size_t)row * a.tail_cap + t];
+      if (x != kNegInf) {  // -inf marks a selected tail slot
+        const float v = ex2(fmaf(x, kLog2e, -M));
+        atomicAdd(&mass[g][a.list_ids[(size_t)s * a.cap + n_sorted + t]], v);
+        approx += v;
+      }
     }
     float exact = 0.f;
     for (int c = tid; c < nchunks[g]; c += kMrgThreads) {
       const float* pp = a.partial + ((size_t)row * a.chunks + c) * kPartial;
       exact += pp[1] * ex2(pp[0] - M);
     }
-    const float tot_before = block_sum<kMrgThreads>(before, red);
-    const float tot_old = block_sum<kMrgThreads>(old, red);
+    const float tot_approx = block_sum<kMrgThreads>(approx, red);
     const float tot_exact = block_sum<kMrgThreads>(exact, red);
-    if (tid == 0) sden[g] = fmaxf(tot_before - tot_old + tot_exact, 1.17549435e-38f);
+    if (tid == 0) sden[g] = fmaxf(tot_approx + tot_exact, 1.17549435e-38f);
   }
   __syncthreads();
 
@@ -169,13 +161,10 @@ int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t s
   a.unit_max = reinterpret_cast<const float*>(ws + w.unit_max);
   a.unit_sum = reinterpret_cast<const float*>(ws + w.unit_sum);
   a.tail_logit = reinterpret_cast<const float*>(ws + w.tail_logit);
-  a.sel_logit = reinterpret_cast<const float*>(ws + w.sel_logit);
-  a.sel_list = reinterpret_cast<const uint16_t*>(ws + w.sel_list);
   a.partial = reinterpret_cast<const float*>(ws + w.partial);
   a.cap = p.slot_capacity;
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
-  a.kcap = w.kcap;
   a.chunks = w.chunks;
   a.sink = p.sink_tokens;
   a.num_lists = p.num_lists;

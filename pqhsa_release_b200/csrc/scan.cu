@@ -7,7 +7,7 @@
 // production kernel it replaces is pq_hsa/kernels/triton_lut_scan_h20.py:1197-1291.)
 //
 // Layout and work split.  The sorted region of a stream is cut into units of at
-// most 256 consecutive slots of ONE list, so the list score is a warp-uniform
+// most 128 consecutive slots of ONE list, so the list score is a warp-uniform
 // register and the per-list log-sum-exp is a warp reduction with no atomics.  A
 // warp takes one unit at a time; lanes take consecutive slots (coalesced 4-byte
 // code and 2-byte norm loads).  Slots of the unsorted tail carry their own list
@@ -22,7 +22,10 @@
 // Outputs per query row (select mode): the 12-bit histogram bin of every slot
 // (uint16, dense), the row's bin histogram (shared-memory atomics, flushed once
 // per CTA), per-unit (max, sum exp) and the tail logits.  The logits themselves
-// are never written.  Dump mode writes the fp32 logits instead (tests, and the
+// are never written.  A unit's <= 4 logits per lane stay in registers, so the sum
+// is taken against the unit's final maximum: each key contributes exactly
+// unit_term(logit, max), which the attend kernel can reproduce bit for bit when
+// it removes a selected key from its unit (no cancellation error).  Dump mode writes the fp32 logits instead (tests, and the
 // stand-alone scoring entry point).
 #include "common.cuh"
 
@@ -52,8 +55,8 @@ struct ScanArgs {
   float* unit_sum;
   float* tail_logit;
   float* dump;
+  const float* row_bin;
   int cap, ucap, tail_cap;
-  float hist_lo, hist_inv_w;
 };
 
 template <int G>
@@ -124,15 +127,20 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const ScanArgs a) {
       const int lo = a.unit_off[(size_t)s * (a.ucap + 1) + u];
       const int hi = a.unit_off[(size_t)s * (a.ucap + 1) + u + 1];
       const int l = a.unit_list[(size_t)s * a.ucap + u];
-      float ls[G], rm[G], rs[G];
+      float ls[G], lo_b[G], iw_b[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         ls[g] = __ldg(lsc + g * kLMax + l);
-        rm[g] = kNegInf;
-        rs[g] = 0.f;
+        if constexpr (!DUMP) {
+          lo_b[g] = a.row_bin[((size_t)s * G + g) * 2];
+          iw_b[g] = a.row_bin[((size_t)s * G + g) * 2 + 1];
+        }
       }
-      for (int base = lo; base < hi; base += 32) {
-        const int slot = base + lane;
+      constexpr int kIter = kUnit / 32;
+      float xs[kIter][G];
+#pragma unroll
+      for (int it = 0; it < kIter; ++it) {
+        const int slot = lo + it * 32 + lane;
         if (slot < hi) {
           const uint32_t code = __ldg(codes + slot);
           const float kn = to_f(norms[slot]);
@@ -141,31 +149,34 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const ScanArgs a) {
 #pragma unroll
           for (int g = 0; g < G; ++g) {
             const float x = finish_logit(acc[g], ls[g], kn);
+            xs[it][g] = x;
             if constexpr (DUMP) {
               a.dump[((size_t)s * G + g) * a.cap + slot] = x;
             } else {
-              const int b = logit_bin(x, a.hist_lo, a.hist_inv_w);
+              const int b = logit_bin(x, lo_b[g], iw_b[g]);
               a.bins[((size_t)s * G + g) * a.cap + slot] = (uint16_t)b;
               atomicAdd(&shist[g * kBins + b], 1u);
-              if (x <= rm[g]) {
-                rs[g] += ex2((x - rm[g]) * kLog2e);
-              } else {
-                rs[g] = rs[g] * ex2((rm[g] - x) * kLog2e) + 1.f;
-                rm[g] = x;
-              }
             }
           }
+        } else {
+#pragma unroll
+          for (int g = 0; g < G; ++g) xs[it][g] = kNegInf;
         }
       }
       if constexpr (!DUMP) {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const float mw = warp_max(rm[g]);
-          const float c = (rm[g] == kNegInf) ? 0.f : rs[g] * ex2((rm[g] - mw) * kLog2e);
-          const float sw = warp_sum(c);
+          float mx = xs[0][g];
+#pragma unroll
+          for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
+          mx = warp_max(mx);
+          float sm = 0.f;
+#pragma unroll
+          for (int it = 0; it < kIter; ++it) sm += unit_term(xs[it][g], mx);  // -inf contributes 0
+          sm = warp_sum(sm);
           if (lane == 0) {
-            a.unit_max[((size_t)s * G + g) * a.ucap + u] = mw;
-            a.unit_sum[((size_t)s * G + g) * a.ucap + u] = sw;
+            a.unit_max[((size_t)s * G + g) * a.ucap + u] = mx;
+            a.unit_sum[((size_t)s * G + g) * a.ucap + u] = sm;
           }
         }
       }
@@ -187,7 +198,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const ScanArgs a) {
           if constexpr (DUMP) {
             a.dump[((size_t)s * G + g) * a.cap + slot] = x;
           } else {
-            const int b = logit_bin(x, a.hist_lo, a.hist_inv_w);
+            const int b = logit_bin(x, a.row_bin[((size_t)s * G + g) * 2], a.row_bin[((size_t)s * G + g) * 2 + 1]);
             a.bins[((size_t)s * G + g) * a.cap + slot] = (uint16_t)b;
             atomicAdd(&shist[g * kBins + b], 1u);
             a.tail_logit[((size_t)s * G + g) * a.tail_cap + t] = x;
@@ -255,8 +266,7 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
   a.cap = p.slot_capacity;
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
-  a.hist_lo = p.hist_lo;
-  a.hist_inv_w = p.hist_inv_width;
+  a.row_bin = reinterpret_cast<const float*>(ws + w.row_bin);
   if (dump != nullptr) {
     PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G, true>(p, a, st))));
   } else {

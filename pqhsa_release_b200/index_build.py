@@ -1,0 +1,113 @@
+"""IVF-PQ index construction after prefill, batched over streams, on the GPU.
+
+Follows ``IVFPQIndex.build`` (pq_hsa/index/ivfpq.py:275-348) step for step:
+direction / norm split (:1052-1059), one seeded coarse k-means with
+``coarse_max_iter`` Lloyd steps (pq_hsa/index/kmeans.py:134-227), residuals,
+one seeded k-means per subspace (pq_hsa/index/pq.py:81-94, seed + 10000 + m),
+nearest-code-word encoding (:97-115) and the per-list value means
+(pq_hsa/attention/kv_cache.py:688-728).  The random initial rows come from a
+CPU generator with the reference's seeds, so the same rows are drawn as in the
+reference's CPU build.
+
+This is set-up work outside the per-step path and is expressed in torch tensor
+operations on the device; the per-step path never calls into it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .config import IVFPQConfig, validate_index_config
+from .device_index import StreamIndexTensors, codes_to_words, words_to_codes  # noqa: F401
+
+
+def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Tensor:
+    """x [S, N, d], cent [S, K, d] -> argmin_k (|c|^2 - 2 x.c) [S, N]
+    (pq_hsa/index/kmeans.py:108-131)."""
+    csq = (cent * cent).sum(-1)  # [S, K]
+    out = torch.empty(x.shape[0], x.shape[1], dtype=torch.long, device=x.device)
+    for lo in range(0, x.shape[1], chunk):
+        hi = min(x.shape[1], lo + chunk)
+        sc = csq.unsqueeze(1) - 2.0 * torch.bmm(x[:, lo:hi], cent.transpose(1, 2))
+        out[:, lo:hi] = sc.argmin(dim=-1)
+    return out
+
+
+def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.dtype, eps: float):
+    """Batched seeded Lloyd iterations.  x [S, N, d] fp32 -> (centroids [S, k, d]
+    holding values representable in ``store_dtype``, assignments [S, N])."""
+    s, n, d = x.shape
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed)
+    if n >= k:
+        rows = torch.randperm(n, generator=gen)[:k]
+    else:
+        rows = torch.cat([torch.arange(n), torch.randint(0, n, (k - n,), generator=gen)])
+    cent = x[:, rows.to(x.device)].to(store_dtype).float()
+    for _ in range(iters):
+        a = _assign(x, cent)
+        sums = torch.zeros(s, k, d, dtype=torch.float32, device=x.device)
+        sums.scatter_add_(1, a.unsqueeze(-1).expand(-1, -1, d), x)
+        cnt = torch.zeros(s, k, dtype=torch.float32, device=x.device)
+        cnt.scatter_add_(1, a, torch.ones_like(a, dtype=torch.float32))
+        live = cnt > 0
+        new = sums / cnt.clamp_min(eps).unsqueeze(-1)
+        dead = (~live).sum(dim=1).tolist()
+        if any(dead):
+            # the reference draws one batch of replacement rows per stream from the same generator
+            for i, nd in enumerate(dead):
+                if nd:
+                    repl = torch.randint(0, n, (nd,), generator=gen).to(x.device)
+                    new[i, ~live[i]] = x[i, repl]
+        cent = new.to(store_dtype).float()
+    return cent, _assign(x, cent)
+
+
+@torch.no_grad()
+def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig) -> list[StreamIndexTensors]:
+    """keys/values: [S, N, 128] rows of the retrieval region of S streams that share
+    N.  Returns one :class:`StreamIndexTensors` per stream (tensors stay on the
+    device of ``keys``)."""
+    validate_index_config(cfg)
+    if keys.dim() != 3 or keys.shape != values.shape:
+        raise ValueError("keys and values must both be [streams, N, dim]")
+    s, n, d = keys.shape
+    if n == 0:
+        raise ValueError("cannot build IVF-PQ index with zero keys")
+    dtype = keys.dtype
+    kf = keys.float()
+    norms = torch.linalg.vector_norm(kf, dim=-1).to(dtype).clamp_min(cfg.eps)
+    unit = kf / norms.float().unsqueeze(-1)
+    lists = min(cfg.num_lists, n)
+    coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps)
+    resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
+    m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
+    books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
+    words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
+    for j in range(m):
+        chunk = resid[:, :, j * sub : (j + 1) * sub].contiguous()
+        books[:, j], _ = _kmeans(chunk, ncodes, cfg.pq_max_iter, cfg.seed + 10_000 + j, dtype, cfg.eps)
+        # encode with true squared distances (torch.cdist's small-size path)
+        d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
+        words |= d2.argmin(dim=-1) << (4 * j)
+    vf = values.float()
+    vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
+    vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
+    vcnt = torch.zeros(s, lists, dtype=torch.float32, device=keys.device)
+    vcnt.scatter_add_(1, lid, torch.ones_like(lid, dtype=torch.float32))
+    vmean = torch.where(vcnt.unsqueeze(-1) > 0, vsum / vcnt.clamp_min(1).unsqueeze(-1), torch.zeros_like(vsum))
+    out = []
+    for i in range(s):
+        out.append(
+            StreamIndexTensors(
+                packed_codes=words_to_codes(words[i]),
+                list_ids=lid[i],
+                key_norms=norms[i],
+                coarse_centroids=coarse[i].to(dtype),
+                codebooks=books[i].to(dtype),
+                value_means=vmean[i].to(dtype),
+                value_sums=vsum[i],
+                value_counts=vcnt[i].to(torch.int32),
+            )
+        )
+    return out
