@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define PQHSA_ABI_VERSION 1
+#define PQHSA_ABI_VERSION 2
 
 /* fixed shape of the index (pq_hsa/kernels/cuda/pq_fused_h20.cu:26-35 fixes the
  * same: 8 subspaces x 4 bits, at most 512 lists, head_dim 128) */
@@ -30,8 +30,9 @@ extern "C" {
 #define PQHSA_CODES 16
 #define PQHSA_HEAD_DIM 128
 #define PQHSA_MAX_LISTS 512
-#define PQHSA_UNIT_KEYS 128  /* a scan unit = at most this many slots of one list */
-#define PQHSA_HIST_BINS 4096 /* selection histogram resolution per query row */
+#define PQHSA_UNIT_KEYS 128     /* a scan unit = at most this many slots of one list */
+#define PQHSA_SAMPLE_KEYS 4096  /* keys scored per stream to place the candidate threshold */
+#define PQHSA_HIST_BINS 4096    /* resolution of the sample histogram */
 
 enum pqhsa_status {
   PQHSA_OK = 0,
@@ -71,7 +72,7 @@ enum pqhsa_state_slot {
  * benchmarks/e2e_pq_param_sweep.py:4182-4305):
  *   codes     uint32 [S, cap]      8 nibbles, subspace s in bits 4s..4s+3
  *   norms     E      [S, cap]      |k|, clamped at 1e-12
- *   norm_max  float  [S]           upper bound of the stream's norms (sizes the histogram)
+ *   norm_max  float  [S]           upper bound of the stream's norms (sizes the sample histogram)
  *   list_ids  uint16 [S, cap]
  *   slot_pos  int32  [S, cap]      token position of the slot's key
  *   slot_unit uint16 [S, cap]      scan unit holding the slot (sorted region only)
@@ -110,9 +111,11 @@ typedef struct pqhsa_params {
   double top_fraction;     /* K = min(max(ceil(N * f), 0), N) in double, as
                               pq_hsa/attention/sparse_attention.py:1779-1783 */
   float scale;             /* softmax scale, 1/sqrt(D) unless the model says otherwise */
-  float hist_lo;           /* selection histogram: bin = (logit - lo) * inv_width, clamped;       */
+  float hist_lo;           /* sample histogram: bin = (logit - lo) * inv_width, clamped;          */
   float hist_inv_width;    /* inv_width <= 0 (default) sizes the bins per query row from a bound   */
-  float reserved1;         /* on |logit|; the selection is exact for any choice                    */
+                           /* on |logit|.  The selection is exact for any choice.                  */
+  float select_margin;     /* standard deviations of head-room of the candidate threshold;         */
+                           /* 0 = default (6).  Lower values only make the exact fallback likelier */
 
   const void *codes, *norms, *list_ids, *slot_pos, *slot_unit, *unit_off, *unit_list;
   const void *coarse, *codebooks, *vmeans;
@@ -135,28 +138,33 @@ typedef struct pqhsa_params {
  * R = S * G query rows. */
 typedef struct pqhsa_ws_layout {
   size_t total_bytes;
-  size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>            */
-  size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>               */
-  size_t bins;         /* uint16 [R, cap]        histogram bin of every slot's logit  */
-  size_t hist;         /* uint32 [R, 4096]                                            */
-  size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit              */
-  size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max)   */
-  size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail     */
-  size_t row_info;     /* int32  [R, 8]: K, threshold bin, #above, #selected, #candidates, tail_cap */
-  size_t row_amax;     /* float  [R]   max approximate logit                          */
-  size_t row_bin;      /* float  [R, 2]  histogram origin and 1 / bin width of the row */
-  size_t sel_slot;     /* int32  [R, kcap]  selected slots (unordered)                */
-  size_t cand_slot;    /* int32  [R, cap]   slots inside the threshold bin            */
-  size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)   */
+  size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>                 */
+  size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>                    */
+  size_t row_bin;      /* float  [R, 2]   sample histogram origin and 1 / bin width       */
+  size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
+  size_t ticket;       /* int32  [S]      arrival counter of the table kernel's CTAs       */
+  size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit                   */
+  size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max), selected keys removed */
+  size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */
+  size_t row_info;     /* int32  [R, 8]   see enum pqhsa_row_info_slot                     */
+  size_t cand_slot;    /* int32  [R, ccap]  slots whose logit reached the threshold        */
+  size_t cand_logit;   /* float  [R, ccap]  their logits                                   */
+  size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */
+  size_t sel_off;      /* int64  [R, kcap]  element offset of their K/V rows in the cache  */
+  size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)        */
   int32_t kcap;        /* row stride of sel_* */
+  int32_t ccap;        /* row stride of cand_* */
   int32_t tail_cap;    /* row stride of tail_logit */
   int32_t chunks;      /* split-K partials per row */
-  int32_t reserved;
 } pqhsa_ws_layout;
 
 enum pqhsa_row_info_slot {
-  PQHSA_RI_K = 0, PQHSA_RI_THR_BIN = 1, PQHSA_RI_ABOVE = 2, PQHSA_RI_NSEL = 3,
-  PQHSA_RI_NCAND = 4, PQHSA_RI_N = 5, PQHSA_RI_INTS = 8
+  PQHSA_RI_K = 0,        /* keys to select                                              */
+  PQHSA_RI_N = 1,        /* indexed keys of the stream                                  */
+  PQHSA_RI_NCAND = 2,    /* candidates found by the scan (may exceed ccap: overflow)    */
+  PQHSA_RI_NSEL = 3,     /* keys selected (== K after the finish kernel)                */
+  PQHSA_RI_FALLBACK = 4, /* 1 if the finish kernel had to select from all keys          */
+  PQHSA_RI_INTS = 8
 };
 
 int pqhsa_abi_version(void);
@@ -170,18 +178,21 @@ size_t pqhsa_workspace_bytes(const pqhsa_params* p);
 int pqhsa_workspace_layout(const pqhsa_params* p, pqhsa_ws_layout* out);
 
 /* (1) Per-query, per-head table construction: lut and list_scores in the
- * workspace.  Replaces pq_lut_prep (pq_fused_h20.cu:2975-3051) and
- * ProductQuantizer.compute_lut + the coarse bias (pq_hsa/index/pq.py:190-217,
- * pq_hsa/index/ivfpq.py:1179-1190).  Also clears the per-step counters. */
+ * workspace, plus the per-row candidate threshold estimated from a stratified
+ * sample of the stream's keys.  Replaces pq_lut_prep
+ * (pq_fused_h20.cu:2975-3051) and ProductQuantizer.compute_lut + the coarse
+ * bias (pq_hsa/index/pq.py:190-217, pq_hsa/index/ivfpq.py:1179-1190).  Also
+ * clears the per-step counters and resolves K per row. */
 int pqhsa_lut_build(const pqhsa_params* p, void* stream);
 
 /* (2)+(3)+(5a) Code scan with per-unit log-sum-exp and exact top-K selection.
- * Needs pqhsa_lut_build first.  Leaves sel_slot / row_info / unit_* in the
- * workspace.  Replaces the pair-fused Triton scan
+ * Needs pqhsa_lut_build first.  Leaves sel_slot / sel_off / row_info / unit_*
+ * in the workspace.  Replaces the pair-fused Triton scan
  * (pq_hsa/kernels/triton_lut_scan_h20.py:1197-1291), list_exp_sums_sorted
  * (pq_hsa/kernels/triton_lut_scan.py:424-514), pq_block_reduce
  * (pq_fused_h20.cu:3094) and aten topk + pq_cast_topk
- * (benchmarks/e2e_pq_param_sweep.py:212-217, pq_fused_h20.cu:3148). */
+ * (benchmarks/e2e_pq_param_sweep.py:212-217, pq_fused_h20.cu:3148).
+ * Needs the KV binding (it resolves the selected rows' cache offsets). */
 int pqhsa_scan_select(const pqhsa_params* p, void* stream);
 
 /* (4)+(5b) Exact attention over sink, local window and the selected keys read in
@@ -199,9 +210,9 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream);
 /* One kernel group of the step on its own, for per-kernel timing and profiling:
  * the same launches pqhsa_decode_step makes, in the same order. */
 enum pqhsa_stage {
-  PQHSA_STAGE_LUT = 0,      /* table construction                      */
+  PQHSA_STAGE_LUT = 0,      /* table construction + threshold estimate */
   PQHSA_STAGE_SCAN = 1,     /* code scan                               */
-  PQHSA_STAGE_SELECT = 2,   /* threshold + collect + finish            */
+  PQHSA_STAGE_SELECT = 2,   /* exact selection among the candidates    */
   PQHSA_STAGE_ATTEND = 3,   /* exact attention partials (the gather)   */
   PQHSA_STAGE_MERGE = 4     /* background + final merge                */
 };

@@ -9,11 +9,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-ABI_VERSION = 1
-SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096
+ABI_VERSION = 2
+SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 4096
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
-RI_K, RI_THR_BIN, RI_ABOVE, RI_NSEL, RI_NCAND, RI_N = range(6)
+RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK = range(5)
 F32, BF16, F16 = 0, 1, 2
 STAGE_LUT, STAGE_SCAN, STAGE_SELECT, STAGE_ATTEND, STAGE_MERGE = range(5)
 
@@ -30,7 +30,7 @@ class Params(C.Structure):
         ("max_slots", C.c_int32), ("max_full", C.c_int32), ("topk_fixed", C.c_int32),
         ("tail_capacity", C.c_int32),
         ("top_fraction", C.c_double),
-        ("scale", C.c_float), ("hist_lo", C.c_float), ("hist_inv_width", C.c_float), ("reserved1", C.c_float),
+        ("scale", C.c_float), ("hist_lo", C.c_float), ("hist_inv_width", C.c_float), ("select_margin", C.c_float),
         ("codes", C.c_void_p), ("norms", C.c_void_p), ("list_ids", C.c_void_p), ("slot_pos", C.c_void_p),
         ("slot_unit", C.c_void_p), ("unit_off", C.c_void_p), ("unit_list", C.c_void_p),
         ("coarse", C.c_void_p), ("codebooks", C.c_void_p), ("vmeans", C.c_void_p),
@@ -46,11 +46,11 @@ class WsLayout(C.Structure):
     """``pqhsa_ws_layout`` of include/pqhsa.h."""
 
     _fields_ = [
-        ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("bins", C.c_size_t),
-        ("hist", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t), ("tail_logit", C.c_size_t),
-        ("row_info", C.c_size_t), ("row_amax", C.c_size_t), ("row_bin", C.c_size_t), ("sel_slot", C.c_size_t),
-        ("cand_slot", C.c_size_t), ("partial", C.c_size_t),
-        ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32), ("reserved", C.c_int32),
+        ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("row_bin", C.c_size_t),
+        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
+        ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("cand_slot", C.c_size_t),
+        ("cand_logit", C.c_size_t), ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t),
+        ("kcap", C.c_int32), ("ccap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]
 
 

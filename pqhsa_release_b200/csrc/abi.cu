@@ -24,6 +24,18 @@ int check_launch(const char* what) {
   return PQHSA_OK;
 }
 
+static int g_sm_count = 0;
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    g_sm_count = n;
+  }
+  return g_sm_count;
+}
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int topk_capacity(const pqhsa_params* p) {
@@ -39,6 +51,10 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   const size_t S = (size_t)p->num_streams, G = (size_t)p->group, R = S * G;
   const size_t cap = (size_t)p->slot_capacity;
   o->kcap = topk_capacity(p);
+  // candidates: a few times K is the normal case, the whole stream when the context is short
+  size_t cc = 4 * (size_t)o->kcap + 2 * kSample;
+  if (cc > cap) cc = cap;
+  o->ccap = (int32_t)align_up(cc, 8);
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
   size_t off = 0;
@@ -49,16 +65,17 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   };
   o->lut = take(S * G * kM * kC * sizeof(float));
   o->list_scores = take(S * G * kLMax * sizeof(float));
-  o->bins = take(R * cap * sizeof(uint16_t));
-  o->hist = take(R * kBins * sizeof(uint32_t));
+  o->row_bin = take(R * 2 * sizeof(float));
+  o->row_tau = take(R * sizeof(float));
+  o->ticket = take(S * sizeof(int32_t));
   o->unit_max = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->unit_sum = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
   o->row_info = take(R * kRI * sizeof(int32_t));
-  o->row_amax = take(R * sizeof(float));
-  o->row_bin = take(R * 2 * sizeof(float));
+  o->cand_slot = take(R * (size_t)o->ccap * sizeof(int32_t));
+  o->cand_logit = take(R * (size_t)o->ccap * sizeof(float));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
-  o->cand_slot = take(R * cap * sizeof(int32_t));
+  o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
   o->partial = take(R * (size_t)o->chunks * kPartial * sizeof(float));
   o->total_bytes = off;
 }
@@ -78,6 +95,7 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
     return set_error(PQHSA_E_SHAPE, "slot_capacity must be a positive multiple of 8, got %d", p->slot_capacity);
   if (p->unit_capacity < p->num_lists + p->slot_capacity / kUnit)
     return set_error(PQHSA_E_SHAPE, "unit_capacity %d < num_lists + slot_capacity/%d", p->unit_capacity, kUnit);
+  if (p->unit_capacity > 65535) return set_error(PQHSA_E_SHAPE, "unit_capacity %d does not fit 16 bits", p->unit_capacity);
   if (p->max_slots < 0 || p->max_slots > p->slot_capacity)
     return set_error(PQHSA_E_SHAPE, "max_slots %d outside 0..slot_capacity", p->max_slots);
   if (p->sink_tokens < 0 || p->local_window < 0 || p->max_full < 0)
@@ -144,7 +162,7 @@ int pqhsa_lut_build(const pqhsa_params* p, void* stream) {
 }
 
 int pqhsa_scan_select(const pqhsa_params* p, void* stream) {
-  if (int rc = check_params(p, true, false, false)) return rc;
+  if (int rc = check_params(p, true, true, false)) return rc;
   pqhsa_ws_layout w;
   layout_of(p, &w);
   if (int rc = launch_scan(*p, w, nullptr, (cudaStream_t)stream)) return rc;
@@ -172,7 +190,8 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
 }
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
-  if (int rc = check_params(p, true, stage >= PQHSA_STAGE_ATTEND, stage >= PQHSA_STAGE_ATTEND)) return rc;
+  const bool kv = stage >= PQHSA_STAGE_SELECT;
+  if (int rc = check_params(p, true, kv, stage >= PQHSA_STAGE_ATTEND)) return rc;
   if (stage == PQHSA_STAGE_LUT && !p->q) return set_error(PQHSA_E_NULL, "q is null");
   pqhsa_ws_layout w;
   layout_of(p, &w);

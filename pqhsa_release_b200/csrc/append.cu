@@ -95,21 +95,59 @@ __global__ void __launch_bounds__(kEncThreads) append_encode_kernel(const Encode
     __syncthreads();
 
     // nearest list: argmin_l |u - c_l|^2 = |c_l|^2 - 2 u.c_l (+ |u|^2, constant)
+    // 4 lanes per list (32 dims each, four 16-byte loads), 64 lists per pass, two passes of
+    // loads in flight at a time: the 128 KB of centroids stream in a handful of round trips
     float bd = __builtin_huge_valf();
     int bl = 0x7fffffff;
-    for (int l = warp; l < nl; l += kEncThreads / 32) {
-      float c[4];
-      load4(coarse + (size_t)l * kD + lane * 4, c);
-      float dist = 0.f;
+    {
+      const int sub = tid & 3, grp = tid >> 2;  // 64 groups of 4 lanes
+      constexpr int kGroups = kEncThreads / 4;
+      float uq[32];
 #pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const float df = unit[lane * 4 + d] - c[d];
-        dist = fmaf(df, df, dist);
+      for (int d = 0; d < 32; ++d) uq[d] = unit[sub * 32 + d];
+      for (int l0 = 0; l0 < nl; l0 += 2 * kGroups) {
+        float c[2][32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int l = l0 + h * kGroups + grp;
+          if (l < nl) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float t[8];
+              load8(coarse + (size_t)l * kD + sub * 32 + j * 8, t);
+#pragma unroll
+              for (int d = 0; d < 8; ++d) c[h][j * 8 + d] = t[d];
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int l = l0 + h * kGroups + grp;
+          float dist = 0.f;
+          if (l < nl) {
+#pragma unroll
+            for (int d = 0; d < 32; ++d) {
+              const float df = uq[d] - c[h][d];
+              dist = fmaf(df, df, dist);
+            }
+          }
+          dist += __shfl_xor_sync(0xffffffffu, dist, 1);
+          dist += __shfl_xor_sync(0xffffffffu, dist, 2);
+          if (l < nl && dist < bd) {  // l ascends within a thread, so strict < keeps the lowest index on ties
+            bd = dist;
+            bl = l;
+          }
+        }
       }
-      dist = warp_sum(dist);
-      if (dist < bd) {  // l ascends, so strict < keeps the lowest index on ties
-        bd = dist;
-        bl = l;
+      // best over the 8 groups of a warp (distance, then lower list index)
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+        const int ol = __shfl_xor_sync(0xffffffffu, bl, o);
+        if (od < bd || (od == bd && ol < bl)) {
+          bd = od;
+          bl = ol;
+        }
       }
     }
     if (lane == 0) {

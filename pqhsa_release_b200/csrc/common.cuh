@@ -16,10 +16,11 @@ constexpr int kC = PQHSA_CODES;         // code words per subspace
 constexpr int kSub = kD / kM;           // dims per subspace
 constexpr int kLMax = PQHSA_MAX_LISTS;  // IVF lists
 constexpr int kUnit = PQHSA_UNIT_KEYS;  // slots per scan unit
-constexpr int kBins = PQHSA_HIST_BINS;  // selection histogram bins
+constexpr int kBins = PQHSA_HIST_BINS;  // sample histogram bins
+constexpr int kSample = PQHSA_SAMPLE_KEYS;
 constexpr int kRI = PQHSA_RI_INTS;      // ints of row_info per row
 constexpr int kST = PQHSA_STATE_INTS;   // ints of state per stream
-constexpr int kChunk = 256;             // attend entries per split-K chunk
+constexpr int kChunk = 128;             // attend entries per split-K chunk
 constexpr int kPartial = kD + 2;        // floats per split-K partial (max, sum, acc[D])
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kNegInf = -__builtin_huge_valf();
@@ -29,6 +30,7 @@ int set_error(int code, const char* fmt, ...);
 int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io);
 int check_launch(const char* what);
 void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o);
+int sm_count();
 
 // kernel launchers, one translation unit each; all return a pqhsa_status
 int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
@@ -70,14 +72,7 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
-// 8 consecutive elements, 16-byte (2-byte types) or 32-byte (float) aligned
-__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
-  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ void unpack8(const uint4& r, const __nv_bfloat16*, float (&v)[8]) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -85,8 +80,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
     v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
-__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
-  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ void unpack8(const uint4& r, const __half*, float (&v)[8]) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -94,6 +88,19 @@ __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
     v[2 * i] = f.x;
     v[2 * i + 1] = f.y;
   }
+}
+
+// 8 consecutive elements, 16-byte aligned
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  unpack8(__ldg(reinterpret_cast<const uint4*>(p)), p, v);
+}
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+  unpack8(__ldg(reinterpret_cast<const uint4*>(p)), p, v);
 }
 // 4 consecutive elements, 8-byte (2-byte types) or 16-byte (float) aligned
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
@@ -130,32 +137,38 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---- the approximate logit --------------------------------------------
-// logit = (sum_{m=0..7} lut[m][nibble_m] + list_score) * |k|, with the adds in
-// subspace order from zero, as pq_hsa/kernels/lut_scan.py:101-114 accumulates,
-// then the list bias, then the norm (pq_hsa/index/ivfpq.py:1093-1118).  The
-// scale and |q| are folded into lut and list_score.  Written with explicit
-// rounding intrinsics so that every kernel that re-scores a slot reproduces
-// the scan's value bit for bit.
+// logit = (pq + list_score) * |k| with
+//   pq = ((t0 + t1) + (t2 + t3)) + ... : (t_{2p} + t_{2p+1}) first, then the four
+//        pair sums left to right,  t_m = lut[m][nibble_m]
+// which is the subspace sum of pq_hsa/kernels/lut_scan.py:101-114 in the
+// association order of the byte-pair tables
+// (pq_hsa/kernels/triton_lut_scan_h20.py:127-171), then the list bias, then the
+// norm (pq_hsa/index/ivfpq.py:1093-1118).  The scale and |q| are folded into
+// lut and list_score.  Explicit rounding intrinsics (no contraction, no
+// re-association) make every kernel that re-scores a slot reproduce the scan's
+// value bit for bit.
 __device__ __forceinline__ float finish_logit(float pq, float list_score, float knorm) {
   return __fmul_rn(__fadd_rn(pq, list_score), knorm);
 }
+__device__ __forceinline__ float pair_entry(const float* lut, int pair, uint32_t byte) {
+  return __fadd_rn(lut[(2 * pair) * kC + (byte & 15u)], lut[(2 * pair + 1) * kC + (byte >> 4)]);
+}
 // lut: 128 floats [m][c] of one query row
 __device__ __forceinline__ float pq_sum_row(const float* lut, uint32_t code) {
-  float acc = lut[code & 15u];
+  float acc = pair_entry(lut, 0, code & 255u);
 #pragma unroll
-  for (int m = 1; m < kM; ++m) acc = __fadd_rn(acc, lut[m * kC + ((code >> (4 * m)) & 15u)]);
+  for (int p = 1; p < kM / 2; ++p) acc = __fadd_rn(acc, pair_entry(lut, p, (code >> (8 * p)) & 255u));
   return acc;
 }
 
 // Contribution of one key to the exp-sum of its scan unit, relative to the
-// unit's maximum logit.  The scan adds it and the attend kernel subtracts it for
-// a selected key: same inputs, same instructions, so the removal is exact.
+// unit's maximum logit.  The scan adds it and the selection subtracts it for a
+// selected key: same inputs, same instructions, so the removal is exact.
 __device__ __forceinline__ float unit_term(float logit, float unit_max) {
   return ex2(__fmul_rn(__fsub_rn(logit, unit_max), kLog2e));
 }
 
-// histogram bin of a logit: monotone non-decreasing in the logit, so a larger
-// bin implies a strictly larger logit.
+// histogram bin of a logit: monotone non-decreasing in the logit
 __device__ __forceinline__ int logit_bin(float logit, float lo, float inv_w) {
   const float t = __fmul_rn(__fsub_rn(logit, lo), inv_w);
   int b = __float2int_rd(t);
@@ -203,6 +216,22 @@ __host__ __device__ inline KvAddr make_kvaddr(const pqhsa_params& p) {
   a.stride_head = p.stride_head;
   a.stride_row = p.stride_row;
   return a;
+}
+
+// geometry of the exact part of a stream, from its device counters
+struct StreamGeom {
+  int n_sorted, n_tail, n_units, seq_len, sink_end, retr_end, full;  // full = sink + local rows
+};
+__device__ __forceinline__ StreamGeom stream_geom(const int32_t* st, int sink) {
+  StreamGeom g;
+  g.n_sorted = st[PQHSA_ST_N_SORTED];
+  g.n_tail = st[PQHSA_ST_N_TAIL];
+  g.n_units = st[PQHSA_ST_N_UNITS];
+  g.seq_len = st[PQHSA_ST_SEQ_LEN];
+  g.sink_end = min(sink, g.seq_len);
+  g.retr_end = g.sink_end + g.n_sorted + g.n_tail;
+  g.full = g.sink_end + max(g.seq_len - g.retr_end, 0);
+  return g;
 }
 
 #endif  // __CUDACC__

@@ -1,5 +1,5 @@
 // Block-wide exact radix selection over 32-bit keys (4 passes of 8 bits).
-// Shared by the finishing step of the fused selection and by the stand-alone
+// Shared by the selection kernel of the decode step and by the stand-alone
 // top-k entry point.  Counterpart of the two-pass 16-bit radix select of
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:3624-3688, widened to the fp32 key.
 #pragma once
@@ -19,14 +19,18 @@ struct RadixShared {
 // Among n items with keys key(i) (i in [0, n)), find T and t such that
 // {key > T} plus t items of {key == T} are exactly the r largest (1 <= r <= n;
 // items whose key is 0 never take part and must number at most n - r).
-// All threads of the block must call it; results are returned to every thread.
+// Returns the number of items with key == T (so t == return value means the
+// whole tie group is taken).  All threads of the block must call it; results are
+// returned to every thread.
 template <int THREADS, typename KeyFn>
-__device__ void block_radix_threshold(KeyFn key, int n, int r, RadixShared& sh, uint32_t& T, int& t) {
+__device__ int block_radix_threshold(KeyFn key, int n, int r, RadixShared& sh, uint32_t& T, int& t) {
   const int tid = threadIdx.x, lane = tid & 31;
+  __syncthreads();
   if (tid == 0) {
     sh.prefix = 0u;
     sh.mask = 0u;
     sh.remaining = r;
+    sh.count = 0;
   }
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = tid; i < 256; i += THREADS) sh.hist[i] = 0u;
@@ -61,6 +65,7 @@ __device__ void block_radix_threshold(KeyFn key, int n, int r, RadixShared& sh, 
       }
       const uint32_t excl = incl - sum;
       const uint32_t need = (uint32_t)sh.remaining;
+      __syncwarp();  // every lane has read `remaining` before one of them updates it
       if (excl < need && need <= incl) {
         uint32_t cum = excl;
 #pragma unroll
@@ -69,6 +74,7 @@ __device__ void block_radix_threshold(KeyFn key, int n, int r, RadixShared& sh, 
             sh.prefix = prefix | ((uint32_t)(255 - (lane * 8 + j)) << shift);
             sh.mask = mask | (255u << shift);
             sh.remaining = (int)(need - cum);
+            sh.count = (int)local[j];
           }
           cum += local[j];
         }
@@ -78,7 +84,9 @@ __device__ void block_radix_threshold(KeyFn key, int n, int r, RadixShared& sh, 
   }
   T = sh.prefix;
   t = sh.remaining;
+  const int ties = sh.count;
   __syncthreads();
+  return ties;
 }
 
 }  // namespace pqhsa

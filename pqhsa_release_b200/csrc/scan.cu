@@ -6,38 +6,47 @@
 // (pq_hsa/kernels/lut_scan.py:92-114 + pq_hsa/index/ivfpq.py:1084-1118; the
 // production kernel it replaces is pq_hsa/kernels/triton_lut_scan_h20.py:1197-1291.)
 //
-// Layout and work split.  The sorted region of a stream is cut into units of at
-// most 128 consecutive slots of ONE list, so the list score is a warp-uniform
-// register and the per-list log-sum-exp is a warp reduction with no atomics.  A
-// warp takes one unit at a time; lanes take consecutive slots (coalesced 4-byte
-// code and 2-byte norm loads).  Slots of the unsorted tail carry their own list
-// id and are scored in the same launch; their logits are kept individually.
+// Work split.  The sorted region of a stream is cut into units of at most 128
+// consecutive slots of ONE list, so the list score is a warp-uniform register
+// and the per-list log-sum-exp is a warp reduction with no atomics.  All units
+// of all streams form one global sequence; a persistent grid (one CTA per SM)
+// takes equal contiguous shares of it, so ragged contexts balance by
+// themselves.  A warp takes one unit at a time; lanes take consecutive slots
+// (coalesced 4-byte code and 2-byte norm loads, all of a unit in flight at once).
+// Slots of the unsorted tail carry their own list id and are scored in the same
+// launch; their logits are kept individually.
 //
-// Table lookups.  The 8x16 table of the G rows lives in shared memory as
-// vectors of W = min(G, 4) floats, replicated 32 / W times so that lane j of a
-// quarter (half, full) warp reads replica j: every LDS.128 (.64, .32) then hits
-// distinct banks whatever the codes are, i.e. the scan runs at the shared-memory
-// bandwidth of G*32 bytes per key with no bank conflicts.
+// Table lookups.  The scan is bound by shared-memory bandwidth, not HBM: a key
+// needs its G sums of 8 table entries.  The kernel therefore folds the 8 nibble
+// tables into 4 byte-pair tables (256 entries of min(G,4) floats) when it enters
+// a stream, and replicates them so that lane j of a quarter warp reads replica
+// j: every LDS.128 hits distinct banks whatever the codes are.  4 conflict-free
+// 16-byte lookups per key = 64 B of shared-memory traffic per key for 4 rows;
+// G = 8 runs two such passes.  (128 KB of tables per CTA.)
 //
-// Outputs per query row (select mode): the 12-bit histogram bin of every slot
-// (uint16, dense), the row's bin histogram (shared-memory atomics, flushed once
-// per CTA), per-unit (max, sum exp) and the tail logits.  The logits themselves
-// are never written.  A unit's <= 4 logits per lane stay in registers, so the sum
-// is taken against the unit's final maximum: each key contributes exactly
-// unit_term(logit, max), which the attend kernel can reproduce bit for bit when
-// it removes a selected key from its unit (no cancellation error).  Dump mode writes the fp32 logits instead (tests, and the
-// stand-alone scoring entry point).
+// Outputs per query row: per-unit (max, sum exp) - a unit's logits stay in
+// registers, the sum is taken against the unit's final maximum, so every key
+// contributes exactly unit_term(logit, max) and the selection kernel can remove
+// a selected key again without cancellation error - the tail logits, and the
+// candidates (slot, logit) with logit >= the row's threshold.  Candidates are
+// compacted per warp: ballot + prefix count into a warp-private shared-memory
+// buffer, written out with one global atomic per 64 candidates.  The logits
+// themselves are never written.  Dump mode writes all fp32 logits instead
+// (tests / stand-alone scoring).
 #include "common.cuh"
 
 namespace pqhsa {
 
-constexpr int kScanThreads = 512;
+constexpr int kScanThreads = 1024;
+constexpr int kScanWarps = kScanThreads / 32;
+constexpr int kWStage = 64;  // staged candidates per warp and row
+constexpr int kIter = kUnit / 32;
 
-template <int G> struct LutShape {
-  static constexpr int W = G < 4 ? G : 4;       // floats per lookup vector
-  static constexpr int P = G / W;               // planes (lookups per table entry)
-  static constexpr int REP = 32 / W;            // replicas
-  static constexpr int kFloats = P * kM * kC * 32;  // = P * 4096
+template <int G> struct PairShape {
+  static constexpr int GP = G < 4 ? G : 4;      // rows per pass = floats per lookup vector
+  static constexpr int NP = G / GP;             // passes
+  static constexpr int REP = 32 / GP;           // replicas
+  static constexpr int kFloats = 4 * 256 * 32;  // 4 pair tables x 256 entries x REP x GP = 128 KB
 };
 
 struct ScanArgs {
@@ -49,200 +58,266 @@ struct ScanArgs {
   const int32_t* state;
   const float* lut;
   const float* list_scores;
-  uint16_t* bins;
-  uint32_t* hist;
+  const float* row_tau;
+  int32_t* row_info;
+  int32_t* cand_slot;
+  float* cand_logit;
   float* unit_max;
   float* unit_sum;
   float* tail_logit;
   float* dump;
-  const float* row_bin;
-  int cap, ucap, tail_cap;
+  int S, cap, ucap, tail_cap, ccap;
 };
 
-template <int G>
-__device__ __forceinline__ void lookup_all(const float* __restrict__ lutrep, uint32_t code, int lane,
-                                           float (&acc)[G]) {
-  using S = LutShape<G>;
-  const int rep = lane & (S::REP - 1);
+// Reduce GP values across the warp: each halving step exchanges half of the
+// values, so 4 values cost 6 shuffles instead of 20.  Afterwards the lanes of
+// group j = lane / (32 / GP) hold the total of value j.
+template <int GP, bool MAX>
+__device__ __forceinline__ float warp_reduce_multi(float (&v)[GP], int lane) {
+  auto op = [](float a, float b) { return MAX ? fmaxf(a, b) : a + b; };
+  if constexpr (GP == 4) {
+    const bool hi = lane & 16;
+    float k0 = hi ? v[2] : v[0], k1 = hi ? v[3] : v[1];
+    const float s0 = hi ? v[0] : v[2], s1 = hi ? v[1] : v[3];
+    k0 = op(k0, __shfl_xor_sync(0xffffffffu, s0, 16));
+    k1 = op(k1, __shfl_xor_sync(0xffffffffu, s1, 16));
+    const bool h2 = lane & 8;
+    float k = h2 ? k1 : k0;
+    const float s = h2 ? k0 : k1;
+    k = op(k, __shfl_xor_sync(0xffffffffu, s, 8));
 #pragma unroll
-  for (int m = 0; m < kM; ++m) {
-    const int entry = m * kC + ((code >> (4 * m)) & 15u);
+    for (int o = 4; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    return k;  // lanes 0-7: value 0, 8-15: value 1, 16-23: value 2, 24-31: value 3
+  } else if constexpr (GP == 2) {
+    const bool hi = lane & 16;
+    float k = hi ? v[1] : v[0];
+    const float s = hi ? v[0] : v[1];
+    k = op(k, __shfl_xor_sync(0xffffffffu, s, 16));
 #pragma unroll
-    for (int pl = 0; pl < S::P; ++pl) {
-      const float* src = lutrep + (((pl * kM * kC + entry) * S::REP + rep) * S::W);
-      float t[S::W];
-      if constexpr (S::W == 4) {
-        const float4 v = *reinterpret_cast<const float4*>(src);
-        t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
-      } else if constexpr (S::W == 2) {
-        const float2 v = *reinterpret_cast<const float2*>(src);
-        t[0] = v.x; t[1] = v.y;
-      } else {
-        t[0] = *src;
-      }
+    for (int o = 8; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    return k;  // lanes 0-15: value 0, 16-31: value 1
+  } else {
+    float k = v[0];
 #pragma unroll
-      for (int w = 0; w < S::W; ++w) {
-        const int g = pl * S::W + w;
-        acc[g] = (m == 0) ? t[w] : __fadd_rn(acc[g], t[w]);
-      }
+    for (int o = 16; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    return k;
+  }
+}
+
+template <int GP>
+__device__ __forceinline__ void pair_lookup(const float* __restrict__ base, uint32_t code, float (&acc)[GP]) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint32_t byte = (code >> (8 * p)) & 255u;
+    const float* src = base + (p * 256 + byte) * 32;
+    float t[GP];
+    if constexpr (GP == 4) {
+      const float4 v = *reinterpret_cast<const float4*>(src);
+      t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
+    } else if constexpr (GP == 2) {
+      const float2 v = *reinterpret_cast<const float2*>(src);
+      t[0] = v.x; t[1] = v.y;
+    } else {
+      t[0] = *src;
     }
+#pragma unroll
+    for (int g = 0; g < GP; ++g) acc[g] = (p == 0) ? t[g] : __fadd_rn(acc[g], t[g]);
   }
 }
 
 template <typename E, int G, bool DUMP>
-__global__ void __launch_bounds__(kScanThreads) scan_kernel(const ScanArgs a) {
-  using S = LutShape<G>;
+__global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanArgs a) {
+  using PS = PairShape<G>;
+  constexpr int GP = PS::GP;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* lutrep = reinterpret_cast<float*>(smem_raw);
-  uint32_t* shist = reinterpret_cast<uint32_t*>(lutrep + S::kFloats);
+  float* tab = reinterpret_cast<float*>(smem_raw);                         // pair tables
+  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);                // [warps][GP][kWStage] (slot, logit bits)
+  __shared__ float lut_s[GP][kM * kC];
 
-  const int s = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int32_t* st = a.state + (size_t)s * kST;
-  const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
-  const int u_tot = n_units + (n_tail + kUnit - 1) / kUnit;
-  const int u0 = (int)((long long)u_tot * blockIdx.x / gridDim.x);
-  const int u1 = (int)((long long)u_tot * (blockIdx.x + 1) / gridDim.x);
-  if (u0 >= u1) return;
+  int2* wstage = stage + (size_t)warp * GP * kWStage;
 
-  // replicated table: [plane][entry][replica][w]
-  for (int i = tid; i < S::kFloats; i += kScanThreads) {
-    const int w = i % S::W;
-    const int entry = (i / (S::W * S::REP)) % (kM * kC);
-    const int pl = i / (S::W * S::REP * kM * kC);
-    lutrep[i] = a.lut[((size_t)s * G + pl * S::W + w) * (kM * kC) + entry];
+  // this CTA's share [g0, g1) of the global unit sequence; streams are walked in order
+  long long total = 0;
+  for (int s = 0; s < a.S; ++s) {
+    const int32_t* st = a.state + (size_t)s * kST;
+    total += st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
   }
-  if constexpr (!DUMP) {
-    uint4* h4 = reinterpret_cast<uint4*>(shist);
-    for (int i = tid; i < G * kBins / 4; i += kScanThreads) h4[i] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  __syncthreads();
+  const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
+  if (g0 >= g1) return;
 
-  const uint32_t* codes = a.codes + (size_t)s * a.cap;
-  const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
-  const float* lsc = a.list_scores + (size_t)s * G * kLMax;
+  long long sbase = 0;  // global index of the first unit of stream s
+  for (int s = 0; s < a.S && sbase < g1; ++s) {
+    const int32_t* st = a.state + (size_t)s * kST;
+    const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
+    const int u_tot = n_units + (n_tail + kUnit - 1) / kUnit;
+    const long long lo_g = sbase > g0 ? sbase : g0;
+    const long long hi_g = sbase + u_tot < g1 ? sbase + u_tot : g1;
+    const int u0 = (int)(lo_g - sbase), u1 = (int)(hi_g - sbase);
+    sbase += u_tot;
+    if (u0 >= u1) continue;
 
-  for (int u = u0 + warp; u < u1; u += kScanThreads / 32) {
-    if (u < n_units) {
-      const int lo = a.unit_off[(size_t)s * (a.ucap + 1) + u];
-      const int hi = a.unit_off[(size_t)s * (a.ucap + 1) + u + 1];
-      const int l = a.unit_list[(size_t)s * a.ucap + u];
-      float ls[G], lo_b[G], iw_b[G];
+    const uint32_t* codes = a.codes + (size_t)s * a.cap;
+    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+
+#pragma unroll 1
+    for (int pass = 0; pass < PS::NP; ++pass) {
+      const int row0 = s * G + pass * GP;  // first query row of this pass
+      __syncthreads();                     // the previous tables are no longer in use
+      for (int i = tid; i < GP * kM * kC; i += kScanThreads)
+        lut_s[i / (kM * kC)][i % (kM * kC)] = a.lut[(size_t)row0 * kM * kC + i];
+      __syncthreads();
+      // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g]
+      {
+        const int e = tid;  // 4 * 256 entries, one per thread
+        const int p = e >> 8;
+        const uint32_t byte = e & 255;
+        float v[GP];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        ls[g] = __ldg(lsc + g * kLMax + l);
-        if constexpr (!DUMP) {
-          lo_b[g] = a.row_bin[((size_t)s * G + g) * 2];
-          iw_b[g] = a.row_bin[((size_t)s * G + g) * 2 + 1];
-        }
+        for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], p, byte);
+        float* dst = tab + (size_t)e * 32;
+#pragma unroll
+        for (int rep = 0; rep < PS::REP; ++rep)
+#pragma unroll
+          for (int g = 0; g < GP; ++g) dst[rep * GP + g] = v[g];
       }
-      constexpr int kIter = kUnit / 32;
-      float xs[kIter][G];
+      __syncthreads();
+
+      float tau[GP];
+      int cnt[GP];  // staged candidates of this warp, warp-uniform
 #pragma unroll
-      for (int it = 0; it < kIter; ++it) {
-        const int slot = lo + it * 32 + lane;
-        if (slot < hi) {
-          const uint32_t code = __ldg(codes + slot);
-          const float kn = to_f(norms[slot]);
-          float acc[G];
-          lookup_all<G>(lutrep, code, lane, acc);
+      for (int g = 0; g < GP; ++g) {
+        tau[g] = DUMP ? 0.f : a.row_tau[row0 + g];
+        cnt[g] = 0;
+      }
+      const float* lsc = a.list_scores + (size_t)row0 * kLMax;
+      const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
+
+      auto flush = [&](int g) {
+        __syncwarp();  // the staged entries of all lanes are visible
+        int base = 0;
+        if (lane == 0) base = atomicAdd(a.row_info + (size_t)(row0 + g) * kRI + PQHSA_RI_NCAND, cnt[g]);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        for (int i = lane; i < cnt[g]; i += 32) {
+          if (base + i < a.ccap) {
+            const int2 e = wstage[g * kWStage + i];
+            a.cand_slot[(size_t)(row0 + g) * a.ccap + base + i] = e.x;
+            a.cand_logit[(size_t)(row0 + g) * a.ccap + base + i] = __int_as_float(e.y);
+          }
+        }
+        __syncwarp();
+        cnt[g] = 0;
+      };
+
+      for (int u = u0 + warp; u < u1; u += kScanWarps) {
+        const bool sorted = u < n_units;
+        int lo, hi, l = 0;
+        if (sorted) {
+          lo = a.unit_off[(size_t)s * (a.ucap + 1) + u];
+          hi = a.unit_off[(size_t)s * (a.ucap + 1) + u + 1];
+          l = a.unit_list[(size_t)s * a.ucap + u];
+        } else {
+          lo = n_sorted + (u - n_units) * kUnit;
+          hi = min(lo + kUnit, n_sorted + n_tail);
+        }
+        // all loads of the unit first
+        uint32_t code[kIter];
+        float kn[kIter];
+        int lid[kIter];
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const float x = finish_logit(acc[g], ls[g], kn);
-            xs[it][g] = x;
+        for (int it = 0; it < kIter; ++it) {
+          const int slot = lo + it * 32 + lane;
+          code[it] = 0u;
+          kn[it] = 0.f;
+          lid[it] = l;
+          if (slot < hi) {
+            code[it] = __ldg(codes + slot);
+            kn[it] = to_f(norms[slot]);
+            if (!sorted) lid[it] = lids[slot];
+          }
+        }
+        float ls[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
+
+        float xs[kIter][GP];
+#pragma unroll
+        for (int it = 0; it < kIter; ++it) {
+          const int slot = lo + it * 32 + lane;
+          const bool valid = slot < hi;
+          float acc[GP];
+          pair_lookup<GP>(mytab, code[it], acc);
+#pragma unroll
+          for (int g = 0; g < GP; ++g) {
+            const float bias = sorted ? ls[g] : __ldg(lsc + g * kLMax + lid[it]);
+            const float x = finish_logit(acc[g], bias, kn[it]);
+            xs[it][g] = valid ? x : kNegInf;
             if constexpr (DUMP) {
-              a.dump[((size_t)s * G + g) * a.cap + slot] = x;
+              if (valid) a.dump[(size_t)(row0 + g) * a.cap + slot] = x;
             } else {
-              const int b = logit_bin(x, lo_b[g], iw_b[g]);
-              a.bins[((size_t)s * G + g) * a.cap + slot] = (uint16_t)b;
-              atomicAdd(&shist[g * kBins + b], 1u);
+              if (!sorted && valid) a.tail_logit[(size_t)(row0 + g) * a.tail_cap + (slot - n_sorted)] = x;
+              const bool pass_tau = valid && x >= tau[g];
+              const unsigned m = __ballot_sync(0xffffffffu, pass_tau);
+              if (m) {
+                const int n_new = __popc(m);
+                if (cnt[g] + n_new > kWStage) flush(g);
+                if (pass_tau)
+                  wstage[g * kWStage + cnt[g] + __popc(m & ((1u << lane) - 1u))] = make_int2(slot, __float_as_int(x));
+                cnt[g] += n_new;
+              }
             }
           }
-        } else {
+        }
+        if constexpr (!DUMP) {
+          if (sorted) {
+            float mx[GP];
 #pragma unroll
-          for (int g = 0; g < G; ++g) xs[it][g] = kNegInf;
+            for (int g = 0; g < GP; ++g) {
+              mx[g] = xs[0][g];
+#pragma unroll
+              for (int it = 1; it < kIter; ++it) mx[g] = fmaxf(mx[g], xs[it][g]);
+            }
+            const float mred = warp_reduce_multi<GP, true>(mx, lane);
+            float sm[GP];
+#pragma unroll
+            for (int g = 0; g < GP; ++g) {
+              const float mg = __shfl_sync(0xffffffffu, mred, g * (32 / GP));
+              sm[g] = 0.f;
+#pragma unroll
+              for (int it = 0; it < kIter; ++it) sm[g] += unit_term(xs[it][g], mg);  // -inf contributes 0
+            }
+            const float sred = warp_reduce_multi<GP, false>(sm, lane);
+            if ((lane & (32 / GP - 1)) == 0) {
+              const int g = lane / (32 / GP);
+              a.unit_max[(size_t)(row0 + g) * a.ucap + u] = mred;
+              a.unit_sum[(size_t)(row0 + g) * a.ucap + u] = sred;
+            }
+          }
         }
       }
       if constexpr (!DUMP) {
+        __syncwarp();
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float mx = xs[0][g];
-#pragma unroll
-          for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
-          mx = warp_max(mx);
-          float sm = 0.f;
-#pragma unroll
-          for (int it = 0; it < kIter; ++it) sm += unit_term(xs[it][g], mx);  // -inf contributes 0
-          sm = warp_sum(sm);
-          if (lane == 0) {
-            a.unit_max[((size_t)s * G + g) * a.ucap + u] = mx;
-            a.unit_sum[((size_t)s * G + g) * a.ucap + u] = sm;
-          }
-        }
-      }
-    } else {
-      // a chunk of the unsorted tail: every slot has its own list
-      const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-      const int t0 = (u - n_units) * kUnit;
-      const int t1 = min(t0 + kUnit, n_tail);
-      for (int t = t0 + lane; t < t1; t += 32) {
-        const int slot = n_sorted + t;
-        const uint32_t code = __ldg(codes + slot);
-        const float kn = to_f(norms[slot]);
-        const int l = lids[slot];
-        float acc[G];
-        lookup_all<G>(lutrep, code, lane, acc);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float x = finish_logit(acc[g], __ldg(lsc + g * kLMax + l), kn);
-          if constexpr (DUMP) {
-            a.dump[((size_t)s * G + g) * a.cap + slot] = x;
-          } else {
-            const int b = logit_bin(x, a.row_bin[((size_t)s * G + g) * 2], a.row_bin[((size_t)s * G + g) * 2 + 1]);
-            a.bins[((size_t)s * G + g) * a.cap + slot] = (uint16_t)b;
-            atomicAdd(&shist[g * kBins + b], 1u);
-            a.tail_logit[((size_t)s * G + g) * a.tail_cap + t] = x;
-          }
-        }
+        for (int g = 0; g < GP; ++g)
+          if (cnt[g]) flush(g);
       }
     }
   }
-
-  if constexpr (!DUMP) {
-    __syncthreads();
-    for (int i = tid; i < G * kBins; i += kScanThreads) {
-      const uint32_t v = shist[i];
-      if (v) atomicAdd(a.hist + (size_t)s * G * kBins + i, v);
-    }
-  }
-}
-
-static int g_sm_count = 0;
-int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-    g_sm_count = n;
-  }
-  return g_sm_count;
 }
 
 template <typename E, int G, bool DUMP>
 static int launch_scan_t(const pqhsa_params& p, const ScanArgs& a, cudaStream_t st) {
-  using S = LutShape<G>;
-  const size_t smem = S::kFloats * sizeof(float) + (DUMP ? 0 : (size_t)G * kBins * sizeof(uint32_t));
+  using PS = PairShape<G>;
+  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kScanWarps * PS::GP * kWStage * sizeof(int2);
   auto kern = scan_kernel<E, G, DUMP>;
-  if (smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return check_launch("scan: shared memory opt-in");
-  }
-  const int per_sm = smem > 110 * 1024 ? 1 : 2;
-  const int units_hi = p.num_lists + p.max_slots / kUnit + 1;
-  int ctas = (sm_count() * per_sm + p.num_streams - 1) / p.num_streams;
-  ctas = ctas > units_hi ? units_hi : ctas;
-  ctas = ctas < 1 ? 1 : ctas;
-  kern<<<dim3(ctas, p.num_streams), kScanThreads, smem, st>>>(a);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return check_launch("scan: shared memory opt-in");
+  const long long units_hi = (long long)p.num_streams * (p.num_lists + p.max_slots / kUnit + 2);
+  long long ctas = sm_count();
+  if (ctas > units_hi) ctas = units_hi;
+  if (ctas < 1) ctas = 1;
+  kern<<<(unsigned)ctas, kScanThreads, smem, st>>>(a);
   return check_launch("scan");
 }
 
@@ -257,16 +332,19 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
   a.state = static_cast<const int32_t*>(p.state);
   a.lut = reinterpret_cast<const float*>(ws + w.lut);
   a.list_scores = reinterpret_cast<const float*>(ws + w.list_scores);
-  a.bins = reinterpret_cast<uint16_t*>(ws + w.bins);
-  a.hist = reinterpret_cast<uint32_t*>(ws + w.hist);
+  a.row_tau = reinterpret_cast<const float*>(ws + w.row_tau);
+  a.row_info = reinterpret_cast<int32_t*>(ws + w.row_info);
+  a.cand_slot = reinterpret_cast<int32_t*>(ws + w.cand_slot);
+  a.cand_logit = reinterpret_cast<float*>(ws + w.cand_logit);
   a.unit_max = reinterpret_cast<float*>(ws + w.unit_max);
   a.unit_sum = reinterpret_cast<float*>(ws + w.unit_sum);
   a.tail_logit = reinterpret_cast<float*>(ws + w.tail_logit);
   a.dump = dump;
+  a.S = p.num_streams;
   a.cap = p.slot_capacity;
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
-  a.row_bin = reinterpret_cast<const float*>(ws + w.row_bin);
+  a.ccap = w.ccap;
   if (dump != nullptr) {
     PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G, true>(p, a, st))));
   } else {

@@ -19,17 +19,22 @@ __global__ void __launch_bounds__(kTopkThreads) topk_kernel(const float* __restr
   const int tid = threadIdx.x;
   if (tid == 0) emit_count = 0;
   auto key = [&](int i) -> uint32_t { return float_key(__ldg(row + i)); };
-  uint32_t T;
-  int t;
-  block_radix_threshold<kTopkThreads>(key, n, k, rsh, T, t);
-  auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)i : 0u; };
-  uint32_t T2;
-  int t2;
-  block_radix_threshold<kTopkThreads>(tie_key, n, t, rsh, T2, t2);
+  uint32_t T = 0u, T2 = 0u;
+  int t = 0;
+  const bool take_all = k >= n;
+  if (!take_all) {
+    const int ties = block_radix_threshold<kTopkThreads>(key, n, k, rsh, T, t);
+    if (ties != t) {
+      auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)i : 0u; };
+      int t2;
+      block_radix_threshold<kTopkThreads>(tie_key, n, t, rsh, T2, t2);
+    }
+  }
+  __syncthreads();
   for (int i = tid; i < n; i += kTopkThreads) {
     const float v = __ldg(row + i);
     const uint32_t kk = float_key(v);
-    if (kk > T || (kk == T && ~(uint32_t)i >= T2)) {
+    if (take_all || kk > T || (kk == T && ~(uint32_t)i >= T2)) {
       const int o = atomicAdd(&emit_count, 1);
       if (o < k) {
         out_idx[(size_t)blockIdx.x * k + o] = i;

@@ -103,6 +103,7 @@ class DeviceIndexPool:
         max_full: int | None = None,
         hist_lo: float = 0.0,
         hist_width: float | None = None,
+        select_margin: float = 0.0,
     ):
         if dtype not in _DTYPE_CODE:
             raise ValueError(f"unsupported dtype {dtype}: need float32, bfloat16 or float16")
@@ -151,6 +152,7 @@ class DeviceIndexPool:
         p.scale = float(scale)
         p.hist_lo = float(hist_lo)
         p.hist_inv_width = 0.0 if hist_width is None else float(1.0 / hist_width)
+        p.select_margin = float(select_margin)
         for name in ("codes", "norms", "list_ids", "slot_pos", "slot_unit", "unit_off", "unit_list", "coarse",
                      "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max"):
             setattr(p, name, getattr(self, name).data_ptr())
@@ -161,6 +163,7 @@ class DeviceIndexPool:
         p.workspace = self.workspace.data_ptr()
         p.workspace_bytes = int(self.layout.total_bytes)
         self._kv_keepalive = None
+        self.graph_headroom = 0
 
     # ---- loading ---------------------------------------------------------
     def load_stream(self, s: int, idx: StreamIndexTensors | None, *, seq_len: int, req: int, kv_head: int) -> None:
@@ -268,7 +271,8 @@ class DeviceIndexPool:
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def _prep(self, q: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
-        self.p.max_slots = int((self.h_sorted + self.h_tail).max()) if self.S else 0
+        # grids are sized for the largest stream plus the growth a captured graph may see
+        self.p.max_slots = min(int((self.h_sorted + self.h_tail).max()) + int(self.graph_headroom), self.cap)
         full = int((np.minimum(self.sink, self.h_seq) + np.maximum(
             self.h_seq - (np.minimum(self.sink, self.h_seq) + self.h_sorted + self.h_tail), 0)).max())
         if full > self.max_full:
@@ -323,6 +327,14 @@ class DeviceIndexPool:
                 raise ValueError(f"new_k/new_v must be contiguous {self.dtype} tensors of {self.S}x128 elements")
         _lib.call("pqhsa_append_kv", C.byref(self.p), new_k.data_ptr(), new_v.data_ptr(), self._stream())
         self.h_seq += 1
+
+    def note_replayed(self, appends: int = 0, encodes: int = 0) -> None:
+        """Advance the host mirrors after replaying a captured CUDA graph that held
+        ``appends`` append_kv and ``encodes`` single-key append_encode calls per stream
+        (the device counters advance by themselves).  Negative values undo the
+        bookkeeping of the capture pass, which runs no kernels."""
+        self.h_seq += appends
+        self.h_tail += encodes
 
     def note_external_append(self, count: int = 1) -> None:
         """The caller (e.g. vLLM) already wrote ``count`` new rows per request into the pages."""
@@ -382,16 +394,16 @@ class DeviceIndexPool:
         spec = {
             "lut": (torch.float32, (self.S, self.G, _lib.SUBSPACES, _lib.CODES)),
             "list_scores": (torch.float32, (self.S, self.G, _lib.MAX_LISTS)),
-            "bins": (torch.int16, (R, self.cap)),
-            "hist": (torch.int32, (R, _lib.HIST_BINS)),
+            "row_bin": (torch.float32, (R, 2)),
+            "row_tau": (torch.float32, (R,)),
             "unit_max": (torch.float32, (R, self.ucap)),
             "unit_sum": (torch.float32, (R, self.ucap)),
             "tail_logit": (torch.float32, (R, lay.tail_cap)),
             "row_info": (torch.int32, (R, _lib.ROW_INFO_INTS)),
-            "row_amax": (torch.float32, (R,)),
-            "row_bin": (torch.float32, (R, 2)),
+            "cand_slot": (torch.int32, (R, lay.ccap)),
+            "cand_logit": (torch.float32, (R, lay.ccap)),
             "sel_slot": (torch.int32, (R, lay.kcap)),
-            "cand_slot": (torch.int32, (R, self.cap)),
+            "sel_off": (torch.int64, (R, lay.kcap)),
             "partial": (torch.float32, (R, lay.chunks, _lib.HEAD_DIM + 2)),
         }[name]
         dt, shape = spec

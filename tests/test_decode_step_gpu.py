@@ -16,8 +16,9 @@ def _check_case(case, pool, check_scores=True):
     out = pool.decode_step(q)
     torch.cuda.synchronize()
     out = out.float().cpu()
+    # row_info of the step (the scoring call below starts a new step and clears the counters)
+    info = pool.ws_view("row_info").cpu().clone()
     scores = pool.scan_scores(q).cpu() if check_scores else None
-    info = pool.ws_view("row_info").cpu()
     worst_out = 0.0
     for s, st in enumerate(case.streams):
         qs = case.queries.reshape(case.num_streams, case.G, 128)[s].float()
@@ -45,7 +46,7 @@ def _check_case(case, pool, check_scores=True):
                 assert ok, f"row {row}: {ndiff} members differ beyond boundary ties"
             err = assert_output_close(out[s, g], det.output[g], case.dtype, f"row {row}")
             worst_out = max(worst_out, err)
-    return worst_out
+    return info
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
@@ -80,3 +81,22 @@ def test_full_lists_512():
     case = make_case(B=1, Hkv=1, G=4, S=6000, L=512, dtype=torch.bfloat16, seed=11)
     pool, _, _ = pool_from_case(case)
     _check_case(case, pool)
+
+
+def test_sampled_threshold_path_long_context():
+    # more than 4096 indexed keys: the candidate threshold comes from the sample histogram
+    case = make_case(B=1, Hkv=2, G=4, S=14000, L=256, dtype=torch.bfloat16, seed=13)
+    pool, _, _ = pool_from_case(case)
+    info = _check_case(case, pool)
+    assert int(info[:, 4].sum()) == 0, "the exact fallback should not be needed at the default margin"
+    k = int(info[0, 0])
+    assert (info[:, 2] >= k).all() and (info[:, 2] < 8 * k + 4096).all(), "candidate count out of the expected range"
+
+
+def test_forced_fallback_is_still_exact():
+    # a negative margin puts the threshold above the K-th logit: too few candidates, so the
+    # selection kernel must fall back to all keys and still return the exact top-K
+    case = make_case(B=1, Hkv=1, G=4, S=9000, L=128, dtype=torch.bfloat16, seed=17)
+    pool, _, _ = pool_from_case(case, select_margin=-9.0)
+    info = _check_case(case, pool)
+    assert int(info[:, 4].sum()) >= 1, "expected at least one row to take the fallback"
