@@ -135,16 +135,20 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   }
 
   // ---- the CTA of this stream that arrives last places the candidate thresholds ----
-  __threadfence();
+  // (the barrier makes the CTA's stores visible to thread 0, whose fence then publishes them
+  //  device-wide before the ticket; the last CTA reads the others' results through L2)
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const int t = atomicAdd(a.ticket + s, 1);
     is_last = (t == (int)gridDim.y - 1);
+    if (is_last) {
+      __threadfence();
+      a.ticket[s] = 0;  // ready for the next launch
+    }
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
-  if (tid == 0) a.ticket[s] = 0;  // ready for the next launch
 
   const int32_t* st = a.state + (size_t)s * kST;
   const int n_sorted = st[PQHSA_ST_N_SORTED];

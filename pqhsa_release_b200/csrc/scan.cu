@@ -16,30 +16,34 @@
 // Slots of the unsorted tail carry their own list id and are scored in the same
 // launch; their logits are kept individually.
 //
-// Table lookups.  The scan is bound by shared-memory bandwidth, not HBM: a key
-// needs its G sums of 8 table entries.  The kernel therefore folds the 8 nibble
-// tables into 4 byte-pair tables (256 entries of min(G,4) floats) when it enters
-// a stream, and replicates them so that lane j of a quarter warp reads replica
-// j: every LDS.128 hits distinct banks whatever the codes are.  4 conflict-free
-// 16-byte lookups per key = 64 B of shared-memory traffic per key for 4 rows;
-// G = 8 runs two such passes.  (128 KB of tables per CTA.)
+// The scan is bound by instruction issue and shared-memory bandwidth, not HBM
+// (8 bytes per key against G sums of 8 table entries), so the inner loop is
+// built to be short:
+//   * the 8 nibble tables are folded into 4 byte-pair tables (256 entries of
+//     min(G,4) floats) when a CTA enters a stream, replicated so that lane j of a
+//     quarter warp reads replica j: every LDS.128 hits distinct banks whatever the
+//     codes are - 4 conflict-free 16-byte lookups per key (128 KB of tables);
+//     G = 8 runs two such passes;
+//   * the 4 rows of a pass are carried as two packed f32x2 values (add / mul on
+//     two rows per instruction, same IEEE rounding as the scalar form);
+//   * the unit maximum is one redux.sync.max.f32 per row;
+//   * a key whose logit reaches the row's threshold is a candidate: the lane
+//     drops (slot, row, logit) into a lane-private shared-memory buffer and the
+//     warp flushes the buffers together, one global atomic per row and flush.
 //
 // Outputs per query row: per-unit (max, sum exp) - a unit's logits stay in
-// registers, the sum is taken against the unit's final maximum, so every key
+// registers and the sum is taken against the unit's final maximum, so every key
 // contributes exactly unit_term(logit, max) and the selection kernel can remove
 // a selected key again without cancellation error - the tail logits, and the
-// candidates (slot, logit) with logit >= the row's threshold.  Candidates are
-// compacted per warp: ballot + prefix count into a warp-private shared-memory
-// buffer, written out with one global atomic per 64 candidates.  The logits
-// themselves are never written.  Dump mode writes all fp32 logits instead
-// (tests / stand-alone scoring).
+// candidates.  The logits themselves are never written; the separate dump kernel
+// writes all of them for tests and the stand-alone scoring entry point.
 #include "common.cuh"
 
 namespace pqhsa {
 
 constexpr int kScanThreads = 1024;
 constexpr int kScanWarps = kScanThreads / 32;
-constexpr int kWStage = 64;  // staged candidates per warp and row
+constexpr int kLanePriv = 8;  // lane-private staged candidates
 constexpr int kIter = kUnit / 32;
 
 template <int G> struct PairShape {
@@ -66,76 +70,137 @@ struct ScanArgs {
   float* unit_sum;
   float* tail_logit;
   float* dump;
-  int S, cap, ucap, tail_cap, ccap;
+  int S, G, cap, ucap, tail_cap, ccap;
 };
 
-// Reduce GP values across the warp: each halving step exchanges half of the
-// values, so 4 values cost 6 shuffles instead of 20.  Afterwards the lanes of
-// group j = lane / (32 / GP) hold the total of value j.
-template <int GP, bool MAX>
-__device__ __forceinline__ float warp_reduce_multi(float (&v)[GP], int lane) {
-  auto op = [](float a, float b) { return MAX ? fmaxf(a, b) : a + b; };
+__device__ __forceinline__ float redux_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// Sum GP values across the warp: each halving step exchanges half of the values, so 4
+// values cost 6 shuffles instead of 20.  Afterwards the lanes of group j = lane / (32 / GP)
+// hold the total of value j.
+template <int GP>
+__device__ __forceinline__ float warp_sum_multi(const float (&v)[GP], int lane) {
   if constexpr (GP == 4) {
     const bool hi = lane & 16;
     float k0 = hi ? v[2] : v[0], k1 = hi ? v[3] : v[1];
     const float s0 = hi ? v[0] : v[2], s1 = hi ? v[1] : v[3];
-    k0 = op(k0, __shfl_xor_sync(0xffffffffu, s0, 16));
-    k1 = op(k1, __shfl_xor_sync(0xffffffffu, s1, 16));
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
     const bool h2 = lane & 8;
     float k = h2 ? k1 : k0;
     const float s = h2 ? k0 : k1;
-    k = op(k, __shfl_xor_sync(0xffffffffu, s, 8));
+    k += __shfl_xor_sync(0xffffffffu, s, 8);
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    for (int o = 4; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
     return k;  // lanes 0-7: value 0, 8-15: value 1, 16-23: value 2, 24-31: value 3
   } else if constexpr (GP == 2) {
     const bool hi = lane & 16;
     float k = hi ? v[1] : v[0];
     const float s = hi ? v[0] : v[1];
-    k = op(k, __shfl_xor_sync(0xffffffffu, s, 16));
+    k += __shfl_xor_sync(0xffffffffu, s, 16);
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    for (int o = 8; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
     return k;  // lanes 0-15: value 0, 16-31: value 1
   } else {
     float k = v[0];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) k = op(k, __shfl_xor_sync(0xffffffffu, k, o));
+    for (int o = 16; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
     return k;
   }
 }
 
+// logits of one key for the GP rows of a pass, from the replicated pair tables
 template <int GP>
-__device__ __forceinline__ void pair_lookup(const float* __restrict__ base, uint32_t code, float (&acc)[GP]) {
-#pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    const uint32_t byte = (code >> (8 * p)) & 255u;
-    const float* src = base + (p * 256 + byte) * 32;
-    float t[GP];
-    if constexpr (GP == 4) {
-      const float4 v = *reinterpret_cast<const float4*>(src);
-      t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
-    } else if constexpr (GP == 2) {
-      const float2 v = *reinterpret_cast<const float2*>(src);
-      t[0] = v.x; t[1] = v.y;
-    } else {
-      t[0] = *src;
-    }
-#pragma unroll
-    for (int g = 0; g < GP; ++g) acc[g] = (p == 0) ? t[g] : __fadd_rn(acc[g], t[g]);
+__device__ __forceinline__ void score_key(const float* __restrict__ mytab, uint32_t code, const float (&ls)[GP],
+                                          float kn, float (&x)[GP]) {
+  const float* p0 = mytab + ((code & 255u) << 5);
+  const float* p1 = mytab + 8192 + (((code >> 8) & 255u) << 5);
+  const float* p2 = mytab + 16384 + (((code >> 16) & 255u) << 5);
+  const float* p3 = mytab + 24576 + ((code >> 24) << 5);
+  if constexpr (GP == 4) {
+    const float4 t0 = *reinterpret_cast<const float4*>(p0), t1 = *reinterpret_cast<const float4*>(p1);
+    const float4 t2 = *reinterpret_cast<const float4*>(p2), t3 = *reinterpret_cast<const float4*>(p3);
+    float2 a = __fadd2_rn(make_float2(t0.x, t0.y), make_float2(t1.x, t1.y));
+    float2 b = __fadd2_rn(make_float2(t0.z, t0.w), make_float2(t1.z, t1.w));
+    a = __fadd2_rn(a, make_float2(t2.x, t2.y));
+    b = __fadd2_rn(b, make_float2(t2.z, t2.w));
+    a = __fadd2_rn(a, make_float2(t3.x, t3.y));
+    b = __fadd2_rn(b, make_float2(t3.z, t3.w));
+    a = __fmul2_rn(__fadd2_rn(a, make_float2(ls[0], ls[1])), make_float2(kn, kn));
+    b = __fmul2_rn(__fadd2_rn(b, make_float2(ls[2], ls[3])), make_float2(kn, kn));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else if constexpr (GP == 2) {
+    const float2 t0 = *reinterpret_cast<const float2*>(p0), t1 = *reinterpret_cast<const float2*>(p1);
+    const float2 t2 = *reinterpret_cast<const float2*>(p2), t3 = *reinterpret_cast<const float2*>(p3);
+    float2 a = __fadd2_rn(__fadd2_rn(__fadd2_rn(t0, t1), t2), t3);
+    a = __fmul2_rn(__fadd2_rn(a, make_float2(ls[0], ls[1])), make_float2(kn, kn));
+    x[0] = a.x; x[1] = a.y;
+  } else {
+    const float a = __fadd_rn(__fadd_rn(__fadd_rn(*p0, *p1), *p2), *p3);
+    x[0] = finish_logit(a, ls[0], kn);
   }
 }
 
-template <typename E, int G, bool DUMP>
+// Warp-collective: write every lane's privately staged candidates to the rows'
+// candidate lists (one atomic per row), lane `l` owning entries wst[e * 32 + l].
+template <int GP>
+__device__ __noinline__ void flush_lane_buffers(const int2* wst, int pc, uint32_t tagw, int lane, int row0,
+                                                int32_t* row_info, int32_t* cand_slot, float* cand_logit,
+                                                int ccap) {
+  int c[GP], nxt[GP];
+#pragma unroll
+  for (int g = 0; g < GP; ++g) c[g] = 0;
+#pragma unroll
+  for (int e = 0; e < kLanePriv; ++e) {
+    const int tg = (tagw >> (2 * e)) & 3u;
+#pragma unroll
+    for (int g = 0; g < GP; ++g) c[g] += (e < pc && tg == g) ? 1 : 0;
+  }
+#pragma unroll
+  for (int g = 0; g < GP; ++g) {
+    int incl = c[g];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int tot = __shfl_sync(0xffffffffu, incl, 31);
+    int b = 0;
+    if (lane == 0 && tot > 0) b = atomicAdd(row_info + (size_t)(row0 + g) * kRI + PQHSA_RI_NCAND, tot);
+    nxt[g] = __shfl_sync(0xffffffffu, b, 0) + incl - c[g];
+  }
+#pragma unroll
+  for (int e = 0; e < kLanePriv; ++e) {
+    if (e < pc) {
+      const int tg = (tagw >> (2 * e)) & 3u;
+      const int2 v = wst[e * 32 + lane];
+      int o = 0;
+#pragma unroll
+      for (int g = 0; g < GP; ++g)
+        if (tg == g) o = nxt[g]++;
+      if (o < ccap) {
+        cand_slot[(size_t)(row0 + tg) * ccap + o] = v.x;
+        cand_logit[(size_t)(row0 + tg) * ccap + o] = __int_as_float(v.y);
+      }
+    }
+  }
+}
+
+template <typename E, int G>
 __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanArgs a) {
   using PS = PairShape<G>;
   constexpr int GP = PS::GP;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* tab = reinterpret_cast<float*>(smem_raw);                         // pair tables
-  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);                // [warps][GP][kWStage] (slot, logit bits)
+  float* tab = reinterpret_cast<float*>(smem_raw);           // pair tables
+  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);  // [warps][kLanePriv][32] (slot, logit bits)
   __shared__ float lut_s[GP][kM * kC];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int2* wstage = stage + (size_t)warp * GP * kWStage;
+  int2* wst = stage + (size_t)warp * kLanePriv * 32;
 
   // this CTA's share [g0, g1) of the global unit sequence; streams are walked in order
   long long total = 0;
@@ -160,6 +225,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanArgs a)
     const uint32_t* codes = a.codes + (size_t)s * a.cap;
     const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
     const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+    const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
+    const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
 
 #pragma unroll 1
     for (int pass = 0; pass < PS::NP; ++pass) {
@@ -168,149 +235,160 @@ __global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanArgs a)
       for (int i = tid; i < GP * kM * kC; i += kScanThreads)
         lut_s[i / (kM * kC)][i % (kM * kC)] = a.lut[(size_t)row0 * kM * kC + i];
       __syncthreads();
-      // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g]
-      {
-        const int e = tid;  // 4 * 256 entries, one per thread
-        const int p = e >> 8;
-        const uint32_t byte = e & 255;
+      // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g].  Consecutive
+      // threads write consecutive GP-float vectors (conflict-free stores); an entry is
+      // recomputed for each of its replicas, which is cheaper than a strided store.
+      for (int i = tid; i < 4 * 256 * PS::REP; i += kScanThreads) {
+        const int e = i / PS::REP;  // p * 256 + byte
         float v[GP];
 #pragma unroll
-        for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], p, byte);
-        float* dst = tab + (size_t)e * 32;
-#pragma unroll
-        for (int rep = 0; rep < PS::REP; ++rep)
-#pragma unroll
-          for (int g = 0; g < GP; ++g) dst[rep * GP + g] = v[g];
+        for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], e >> 8, (uint32_t)(e & 255));
+        float* dst = tab + (size_t)i * GP;
+        if constexpr (GP == 4) {
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        } else if constexpr (GP == 2) {
+          *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+        } else {
+          dst[0] = v[0];
+        }
       }
       __syncthreads();
 
       float tau[GP];
-      int cnt[GP];  // staged candidates of this warp, warp-uniform
 #pragma unroll
-      for (int g = 0; g < GP; ++g) {
-        tau[g] = DUMP ? 0.f : a.row_tau[row0 + g];
-        cnt[g] = 0;
-      }
+      for (int g = 0; g < GP; ++g) tau[g] = a.row_tau[row0 + g];
       const float* lsc = a.list_scores + (size_t)row0 * kLMax;
       const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
-
-      auto flush = [&](int g) {
-        __syncwarp();  // the staged entries of all lanes are visible
-        int base = 0;
-        if (lane == 0) base = atomicAdd(a.row_info + (size_t)(row0 + g) * kRI + PQHSA_RI_NCAND, cnt[g]);
-        base = __shfl_sync(0xffffffffu, base, 0);
-        for (int i = lane; i < cnt[g]; i += 32) {
-          if (base + i < a.ccap) {
-            const int2 e = wstage[g * kWStage + i];
-            a.cand_slot[(size_t)(row0 + g) * a.ccap + base + i] = e.x;
-            a.cand_logit[(size_t)(row0 + g) * a.ccap + base + i] = __int_as_float(e.y);
-          }
-        }
-        __syncwarp();
-        cnt[g] = 0;
-      };
+      int pc = 0;         // this lane's staged candidates
+      uint32_t tagw = 0;  // their rows, 2 bits each
 
       for (int u = u0 + warp; u < u1; u += kScanWarps) {
-        const bool sorted = u < n_units;
-        int lo, hi, l = 0;
-        if (sorted) {
-          lo = a.unit_off[(size_t)s * (a.ucap + 1) + u];
-          hi = a.unit_off[(size_t)s * (a.ucap + 1) + u + 1];
-          l = a.unit_list[(size_t)s * a.ucap + u];
-        } else {
-          lo = n_sorted + (u - n_units) * kUnit;
-          hi = min(lo + kUnit, n_sorted + n_tail);
-        }
-        // all loads of the unit first
-        uint32_t code[kIter];
-        float kn[kIter];
-        int lid[kIter];
+        if (u < n_units) {
+          const int lo = uoff[u], hi = uoff[u + 1];
+          const int l = ulist[u];
+          uint32_t code[kIter];
+          float kn[kIter];
 #pragma unroll
-        for (int it = 0; it < kIter; ++it) {
-          const int slot = lo + it * 32 + lane;
-          code[it] = 0u;
-          kn[it] = 0.f;
-          lid[it] = l;
-          if (slot < hi) {
-            code[it] = __ldg(codes + slot);
-            kn[it] = to_f(norms[slot]);
-            if (!sorted) lid[it] = lids[slot];
+          for (int it = 0; it < kIter; ++it) {
+            const int slot = lo + it * 32 + lane;
+            code[it] = 0u;
+            kn[it] = 0.f;
+            if (slot < hi) {
+              code[it] = __ldg(codes + slot);
+              kn[it] = to_f(norms[slot]);
+            }
           }
-        }
-        float ls[GP];
+          float ls[GP];
 #pragma unroll
-        for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
-
-        float xs[kIter][GP];
+          for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
+          float xs[kIter][GP];
 #pragma unroll
-        for (int it = 0; it < kIter; ++it) {
-          const int slot = lo + it * 32 + lane;
-          const bool valid = slot < hi;
-          float acc[GP];
-          pair_lookup<GP>(mytab, code[it], acc);
+          for (int it = 0; it < kIter; ++it) {
+            const int slot = lo + it * 32 + lane;
+            const bool valid = slot < hi;
+            score_key<GP>(mytab, code[it], ls, kn[it], xs[it]);
 #pragma unroll
-          for (int g = 0; g < GP; ++g) {
-            const float bias = sorted ? ls[g] : __ldg(lsc + g * kLMax + lid[it]);
-            const float x = finish_logit(acc[g], bias, kn[it]);
-            xs[it][g] = valid ? x : kNegInf;
-            if constexpr (DUMP) {
-              if (valid) a.dump[(size_t)(row0 + g) * a.cap + slot] = x;
-            } else {
-              if (!sorted && valid) a.tail_logit[(size_t)(row0 + g) * a.tail_cap + (slot - n_sorted)] = x;
-              const bool pass_tau = valid && x >= tau[g];
-              const unsigned m = __ballot_sync(0xffffffffu, pass_tau);
-              if (m) {
-                const int n_new = __popc(m);
-                if (cnt[g] + n_new > kWStage) flush(g);
-                if (pass_tau)
-                  wstage[g * kWStage + cnt[g] + __popc(m & ((1u << lane) - 1u))] = make_int2(slot, __float_as_int(x));
-                cnt[g] += n_new;
+            for (int g = 0; g < GP; ++g) {
+              xs[it][g] = valid ? xs[it][g] : kNegInf;
+              if (valid && xs[it][g] >= tau[g]) {
+                wst[pc * 32 + lane] = make_int2(slot, __float_as_int(xs[it][g]));
+                tagw |= (uint32_t)g << (2 * pc);
+                ++pc;
               }
             }
+            if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
+              flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
+              pc = 0;
+              tagw = 0u;
+            }
           }
-        }
-        if constexpr (!DUMP) {
-          if (sorted) {
-            float mx[GP];
+          // unit statistics: max per row (one redux each), then the sum against that max
+          float sm[GP], mg[GP];
+#pragma unroll
+          for (int g = 0; g < GP; ++g) {
+            float mx = xs[0][g];
+#pragma unroll
+            for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
+            mg[g] = redux_max(mx);
+            sm[g] = 0.f;
+#pragma unroll
+            for (int it = 0; it < kIter; ++it) sm[g] += unit_term(xs[it][g], mg[g]);  // -inf contributes 0
+          }
+          const float sred = warp_sum_multi<GP>(sm, lane);
+          if ((lane & (32 / GP - 1)) == 0) {
+            const int g = lane / (32 / GP);
+            float mine = mg[0];
+#pragma unroll
+            for (int gg = 1; gg < GP; ++gg)
+              if (gg == g) mine = mg[gg];
+            a.unit_max[(size_t)(row0 + g) * a.ucap + u] = mine;
+            a.unit_sum[(size_t)(row0 + g) * a.ucap + u] = sred;
+          }
+        } else {
+          // a chunk of the unsorted tail: every slot has its own list; logits are kept one by one
+          const int t0 = (u - n_units) * kUnit, t1 = min(t0 + kUnit, n_tail);
+          for (int t = t0 + lane; t - lane < t1; t += 32) {
+            const bool valid = t < t1;
+            const int slot = n_sorted + (valid ? t : t0);
+            const uint32_t code = __ldg(codes + slot);
+            const float knv = to_f(norms[slot]);
+            const int l = lids[slot];
+            float ls[GP], x[GP];
+#pragma unroll
+            for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
+            score_key<GP>(mytab, code, ls, knv, x);
 #pragma unroll
             for (int g = 0; g < GP; ++g) {
-              mx[g] = xs[0][g];
-#pragma unroll
-              for (int it = 1; it < kIter; ++it) mx[g] = fmaxf(mx[g], xs[it][g]);
+              if (valid) {
+                a.tail_logit[(size_t)(row0 + g) * a.tail_cap + t] = x[g];
+                if (x[g] >= tau[g]) {
+                  wst[pc * 32 + lane] = make_int2(slot, __float_as_int(x[g]));
+                  tagw |= (uint32_t)g << (2 * pc);
+                  ++pc;
+                }
+              }
             }
-            const float mred = warp_reduce_multi<GP, true>(mx, lane);
-            float sm[GP];
-#pragma unroll
-            for (int g = 0; g < GP; ++g) {
-              const float mg = __shfl_sync(0xffffffffu, mred, g * (32 / GP));
-              sm[g] = 0.f;
-#pragma unroll
-              for (int it = 0; it < kIter; ++it) sm[g] += unit_term(xs[it][g], mg);  // -inf contributes 0
-            }
-            const float sred = warp_reduce_multi<GP, false>(sm, lane);
-            if ((lane & (32 / GP - 1)) == 0) {
-              const int g = lane / (32 / GP);
-              a.unit_max[(size_t)(row0 + g) * a.ucap + u] = mred;
-              a.unit_sum[(size_t)(row0 + g) * a.ucap + u] = sred;
+            if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
+              flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
+              pc = 0;
+              tagw = 0u;
             }
           }
         }
       }
-      if constexpr (!DUMP) {
-        __syncwarp();
-#pragma unroll
-        for (int g = 0; g < GP; ++g)
-          if (cnt[g]) flush(g);
-      }
+      if (__any_sync(0xffffffffu, pc > 0))
+        flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
     }
   }
 }
 
-template <typename E, int G, bool DUMP>
+// All logits of all slots, fp32 [R, cap]: same arithmetic (pq_sum_row / finish_logit) as the
+// scan, one thread per slot.  Not on the decode path.
+template <typename E>
+__global__ void __launch_bounds__(256) scan_dump_kernel(const ScanArgs a) {
+  extern __shared__ float lut_d[];  // [G][128]
+  const int s = blockIdx.y, tid = threadIdx.x;
+  for (int i = tid; i < a.G * kM * kC; i += 256) lut_d[i] = a.lut[(size_t)s * a.G * kM * kC + i];
+  __syncthreads();
+  const int32_t* st = a.state + (size_t)s * kST;
+  const int n = st[PQHSA_ST_N_SORTED] + st[PQHSA_ST_N_TAIL];
+  const int slot = blockIdx.x * 256 + tid;
+  if (slot >= n) return;
+  const uint32_t code = __ldg(a.codes + (size_t)s * a.cap + slot);
+  const float kn = to_f(static_cast<const E*>(a.norms)[(size_t)s * a.cap + slot]);
+  const int l = a.list_ids[(size_t)s * a.cap + slot];
+  for (int g = 0; g < a.G; ++g) {
+    const int row = s * a.G + g;
+    a.dump[(size_t)row * a.cap + slot] =
+        finish_logit(pq_sum_row(lut_d + g * kM * kC, code), __ldg(a.list_scores + (size_t)row * kLMax + l), kn);
+  }
+}
+
+template <typename E, int G>
 static int launch_scan_t(const pqhsa_params& p, const ScanArgs& a, cudaStream_t st) {
   using PS = PairShape<G>;
-  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kScanWarps * PS::GP * kWStage * sizeof(int2);
-  auto kern = scan_kernel<E, G, DUMP>;
+  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kScanWarps * kLanePriv * 32 * sizeof(int2);
+  auto kern = scan_kernel<E, G>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return check_launch("scan: shared memory opt-in");
   const long long units_hi = (long long)p.num_streams * (p.num_lists + p.max_slots / kUnit + 2);
@@ -341,15 +419,19 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
   a.tail_logit = reinterpret_cast<float*>(ws + w.tail_logit);
   a.dump = dump;
   a.S = p.num_streams;
+  a.G = p.group;
   a.cap = p.slot_capacity;
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
   a.ccap = w.ccap;
   if (dump != nullptr) {
-    PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G, true>(p, a, st))));
-  } else {
-    PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G, false>(p, a, st))));
+    if (p.max_slots == 0) return PQHSA_OK;
+    const dim3 grid((p.max_slots + 255) / 256, p.num_streams);
+    const size_t smem = (size_t)p.group * kM * kC * sizeof(float);
+    PQHSA_DISPATCH_E(p.dtype, scan_dump_kernel<E><<<grid, 256, smem, st>>>(a));
+    return check_launch("scan_dump");
   }
+  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G>(p, a, st))));
   return PQHSA_OK;
 }
 

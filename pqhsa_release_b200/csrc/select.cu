@@ -24,8 +24,8 @@
 
 namespace pqhsa {
 
-constexpr int kFinThreads = 512;
-constexpr int kFinCache = 8192;  // candidate keys cached in shared memory
+constexpr int kFinThreads = 1024;
+constexpr int kFinPer = 8;  // candidates per thread held in registers on the normal path
 
 struct FinishArgs {
   const uint32_t* codes;
@@ -52,8 +52,8 @@ template <typename E>
 __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a) {
   __shared__ float lut_s[kM * kC];
   __shared__ RadixShared rsh;
+  __shared__ RadixShared2 rsh2;
   __shared__ int emit_count;
-  extern __shared__ uint32_t key_cache[];  // kFinCache keys
   const int row = blockIdx.x, s = row / a.G;
   const int tid = threadIdx.x;
   int32_t* ri = a.row_info + (size_t)row * kRI;
@@ -82,35 +82,65 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     if (!fallback) return clog[i];
     return finish_logit(pq_sum_row(lut_s, __ldg(codes + i)), __ldg(lsc + lids[i]), to_f(norms[i]));
   };
-  const bool cached = C <= kFinCache;
-  if (cached) {
-    for (int i = tid; i < C; i += kFinThreads) key_cache[i] = float_key(logit_of(i));
-    __syncthreads();
-  }
-  auto key = [&](int i) -> uint32_t { return cached ? key_cache[i] : float_key(logit_of(i)); };
-
-  uint32_t T = 0u, T2 = 0u;
-  int t = 0;
-  const bool take_all = K >= C;
-  if (!take_all) {
-    const int ties = block_radix_threshold<kFinThreads>(key, C, K, rsh, T, t);
-    if (ties != t) {  // more keys tie at the K-th value than fit: lowest slots first
-      auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)slot_of(i) : 0u; };
-      int t2;
-      block_radix_threshold<kFinThreads>(tie_key, C, t, rsh, T2, t2);
-    }
-  }
+  auto key = [&](int i) -> uint32_t { return float_key(logit_of(i)); };
   int32_t* sel = a.sel_slot + (size_t)row * a.kcap;
   long long* soff = a.sel_off + (size_t)row * a.kcap;
-  // pass 1: compact the selected (slot, logit) pairs; the logit is parked in sel_off
-  for (int i = tid; i < C; i += kFinThreads) {
-    const uint32_t k = take_all ? 1u : key(i);
-    const int slot = slot_of(i);
-    if (take_all || k > T || (k == T && ~(uint32_t)slot >= T2)) {
-      const int o = atomicAdd(&emit_count, 1);
-      if (o < a.kcap) {
-        sel[o] = slot;
-        soff[o] = (long long)__float_as_uint(logit_of(i));
+  const bool take_all = K >= C;
+  uint32_t T = 0u, T2 = 0u;
+  int t = 0;
+  if (!fallback && C <= kFinThreads * kFinPer) {
+    // normal path: the candidates sit in registers, kFinPer per thread
+    uint32_t kreg[kFinPer];
+    int sreg[kFinPer];
+#pragma unroll
+    for (int j = 0; j < kFinPer; ++j) {
+      const int i = j * kFinThreads + tid;
+      kreg[j] = 0u;
+      sreg[j] = 0;
+      if (i < C) {
+        kreg[j] = float_key(clog[i]);
+        sreg[j] = cand[i];
+      }
+    }
+    if (!take_all) {
+      const int ties = block_radix_threshold_regs<kFinThreads, kFinPer>(kreg, K, rsh2, T, t);
+      if (ties != t) {  // more keys tie at the K-th value than fit: lowest slots first
+        auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)slot_of(i) : 0u; };
+        int t2;
+        block_radix_threshold<kFinThreads>(tie_key, C, t, rsh, T2, t2);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kFinPer; ++j) {
+      const uint32_t k = kreg[j];
+      if (k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2))) {
+        const int o = atomicAdd(&emit_count, 1);
+        if (o < a.kcap) {
+          sel[o] = sreg[j];
+          soff[o] = (long long)__float_as_uint(clog[j * kFinThreads + tid]);
+        }
+      }
+    }
+  } else {
+    // all N keys (the threshold estimate failed) or an oversized candidate list: keys are
+    // recomputed on every pass
+    if (!take_all) {
+      const int ties = block_radix_threshold<kFinThreads>(key, C, K, rsh, T, t);
+      if (ties != t) {
+        auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)slot_of(i) : 0u; };
+        int t2;
+        block_radix_threshold<kFinThreads>(tie_key, C, t, rsh, T2, t2);
+      }
+    }
+    for (int i = tid; i < C; i += kFinThreads) {
+      const uint32_t k = take_all ? 1u : key(i);
+      const int slot = slot_of(i);
+      if (take_all || k > T || (k == T && ~(uint32_t)slot >= T2)) {
+        const int o = atomicAdd(&emit_count, 1);
+        if (o < a.kcap) {
+          sel[o] = slot;
+          soff[o] = (long long)__float_as_uint(logit_of(i));
+        }
       }
     }
   }
@@ -181,7 +211,7 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.tail_cap = w.tail_cap;
   a.kcap = w.kcap;
   a.ccap = w.ccap;
-  PQHSA_DISPATCH_E(p.dtype, finish_kernel<E><<<R, kFinThreads, kFinCache * sizeof(uint32_t), st>>>(a));
+  PQHSA_DISPATCH_E(p.dtype, finish_kernel<E><<<R, kFinThreads, 0, st>>>(a));
   return check_launch("finish");
 }
 
