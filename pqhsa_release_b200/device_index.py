@@ -220,6 +220,25 @@ class DeviceIndexPool:
             "positions": pos[order],
         }
 
+    def export_stream_state(self, s: int) -> StreamIndexTensors | None:
+        """Everything needed to reinstall stream ``s`` with :meth:`load_stream` (token order)."""
+        n = int(self.h_sorted[s] + self.h_tail[s])
+        if n == 0:
+            return None
+        lists = int(self.state[s, _lib.ST_N_LISTS])
+        e = self.export_stream(s)
+        return StreamIndexTensors(
+            packed_codes=e["packed_codes"].clone(), list_ids=e["list_ids"].clone(), key_norms=e["key_norms"].clone(),
+            coarse_centroids=self.coarse[s, :lists].clone(), codebooks=self.codebooks[s].clone(),
+            value_means=self.vmeans[s, :lists].clone(), value_sums=self.vsum[s, :lists].clone(),
+            value_counts=self.vcnt[s, :lists].clone(),
+        )
+
+    def export_index(self, s: int) -> dict[str, torch.Tensor]:
+        """Codebooks of stream ``s`` (the rows in use) for a refresh or a state dict."""
+        lists = int(self.state[s, _lib.ST_N_LISTS])
+        return {"coarse": self.coarse[s, :lists], "codebooks": self.codebooks[s], "value_means": self.vmeans[s, :lists]}
+
     # ---- KV cache binding ------------------------------------------------
     def bind_kv_contiguous(self, keys: torch.Tensor, values: torch.Tensor) -> None:
         """keys/values: [B, Hkv, capacity, 128] of the pool dtype (any strides

@@ -111,3 +111,63 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
             )
         )
     return out
+
+
+@torch.no_grad()
+def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list[dict], new_count: int,
+                         cfg: IVFPQConfig) -> list[StreamIndexTensors]:
+    """Codebook-moving refresh of S streams that share N (pq_hsa/index/ivfpq.py:647-707):
+    the last ``new_count`` keys pull the coarse centroids and the code words towards
+    their mini-batch means (EMA with ``online_codebook_lr``), then every key is
+    re-assigned and re-encoded and the value means are rebuilt.  ``current[i]`` holds
+    stream i's ``coarse`` [L, 128] and ``codebooks`` [8, 16, 16]."""
+    s, n, d = keys.shape
+    dtype = keys.dtype
+    lr = cfg.online_codebook_lr
+    kf = keys.float()
+    norms = torch.linalg.vector_norm(kf, dim=-1).to(dtype).clamp_min(cfg.eps)
+    unit = kf / norms.float().unsqueeze(-1)
+    coarse = torch.stack([c["coarse"].float() for c in current])        # [S, L, D]
+    books = torch.stack([c["codebooks"].float() for c in current])      # [S, M, 16, sub]
+    lists = coarse.shape[1]
+    upd = unit[:, n - new_count:]
+    ones = torch.ones(s, new_count, dtype=torch.float32, device=keys.device)
+
+    def ema(cent, x, assign):
+        k = cent.shape[1]
+        sums = torch.zeros_like(cent)
+        sums.scatter_add_(1, assign.unsqueeze(-1).expand(-1, -1, x.shape[-1]), x)
+        cnt = torch.zeros(s, k, dtype=torch.float32, device=x.device)
+        cnt.scatter_add_(1, assign, ones)
+        live = (cnt > 0).unsqueeze(-1)
+        means = sums / cnt.clamp_min(cfg.eps).unsqueeze(-1)
+        return torch.where(live, (1.0 - lr) * cent + lr * means, cent)
+
+    coarse = ema(coarse, upd, _assign(upd, coarse)).to(dtype).float()
+    ures = upd - torch.gather(coarse, 1, _assign(upd, coarse).unsqueeze(-1).expand(-1, -1, d))
+    m, sub = cfg.num_subspaces, d // cfg.num_subspaces
+    for j in range(m):
+        chunk = ures[:, :, j * sub : (j + 1) * sub].contiguous()
+        books[:, j] = ema(books[:, j], chunk, _assign(chunk, books[:, j]))
+    books = books.to(dtype).float()
+    lid = _assign(unit, coarse)
+    resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
+    words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
+    for j in range(m):
+        chunk = resid[:, :, j * sub : (j + 1) * sub]
+        d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
+        words |= d2.argmin(dim=-1) << (4 * j)
+    vf = values.float()
+    vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
+    vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
+    vcnt = torch.zeros(s, lists, dtype=torch.float32, device=keys.device)
+    vcnt.scatter_add_(1, lid, torch.ones_like(lid, dtype=torch.float32))
+    vmean = torch.where(vcnt.unsqueeze(-1) > 0, vsum / vcnt.clamp_min(1).unsqueeze(-1), torch.zeros_like(vsum))
+    return [
+        StreamIndexTensors(
+            packed_codes=words_to_codes(words[i]), list_ids=lid[i], key_norms=norms[i],
+            coarse_centroids=coarse[i].to(dtype), codebooks=books[i].to(dtype), value_means=vmean[i].to(dtype),
+            value_sums=vsum[i], value_counts=vcnt[i].to(torch.int32),
+        )
+        for i in range(s)
+    ]

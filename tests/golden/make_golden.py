@@ -1,0 +1,115 @@
+"""Generate the golden fixtures of this directory by running the REFERENCE itself.
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference package (pq_hsa) is imported from the given path and driven through
+its own public API (IVFPQSparseAttention: build_cache / forward_many / append /
+apply_pending_index_update) on small seeded inputs; what it computes is stored in
+``golden_*.npz`` beside this script.  The inputs are not stored: they come from
+``pqhsa_release_b200.workloads`` with the seeds recorded in ``CASES`` and are
+guarded by a checksum, so a drifting generator fails the tests loudly instead of
+silently comparing different data.
+
+The fixtures pin the CPU oracle (tests/test_oracle_golden.py) and, through the
+stored index tensors, the CUDA path (tests/test_golden_gpu.py).  Nothing here is
+needed at test time except the .npz files.
+"""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+
+from pqhsa_release_b200 import workloads  # noqa: E402
+
+# name -> (kind, seed, context, lists, group, dtype, strategy, interval, appends)
+CASES = {
+    "c0_fp32": ("config0", 0, 1700, 64, 3, "float32", "incremental", 1, 24),
+    "mix_bf16": ("mixture", 1, 2300, 96, 4, "bfloat16", "incremental", 4, 24),
+    "mix_deferred": ("mixture", 2, 1500, 48, 2, "bfloat16", "deferred", 8, 20),
+}
+
+
+def case_inputs(name: str):
+    """(keys [S, D], values [S, D], queries [G, D], new_keys [A, D], new_values [A, D]) in fp32,
+    holding values representable in the case dtype."""
+    kind, seed, ctx, lists, group, dtype, strategy, interval, appends = CASES[name]
+    dt = getattr(torch, dtype)
+    if kind == "config0":
+        k, v, q1 = workloads.config0_stream(seed, ctx)
+        g = torch.Generator().manual_seed(seed + 99)
+        q = torch.stack([q1 + 0.3 * torch.randn(128, generator=g) for _ in range(group)])
+    else:
+        kk, vv = workloads.mixture_kv(seed, 1, ctx, dtype=dt, components=16)
+        k, v = kk[0].float(), vv[0].float()
+        q = workloads.planted_queries(seed + 500, kk, group).float()
+    g = torch.Generator().manual_seed(seed + 7)
+    nk = (k[torch.randint(0, ctx, (appends,), generator=g)] + 0.5 * torch.randn(appends, 128, generator=g))
+    nv = torch.randn(appends, 128, generator=g)
+    rd = lambda t: t.to(dt).float()
+    return rd(k), rd(v), rd(q), rd(nk), rd(nv)
+
+
+def checksum(*tensors) -> float:
+    return float(sum(t.double().abs().sum() for t in tensors))
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    from pq_hsa.attention.sparse_attention import IVFPQSparseAttention, SparseAttentionConfig
+    from pq_hsa.index.ivfpq import IVFPQConfig
+
+    for name, (kind, seed, ctx, lists, group, dtype, strategy, interval, appends) in CASES.items():
+        k, v, q, nk, nv = case_inputs(name)
+        ic = IVFPQConfig(num_lists=lists, nprobe=64, num_subspaces=8, num_bits=4, residual=True, coarse_max_iter=1,
+                         pq_max_iter=2, pack_codes=True, topk_block_size=1024, kernel_backend="torch",
+                         rotation="none", direction_normalize=True, seed=0)
+        ac = SparseAttentionConfig(sink_tokens=4, local_window=128, retrieval_top_fraction=0.02, exact_rerank=True,
+                                   mode="hybrid", hybrid_value_mode="centroid", hybrid_topk_source="all_pq",
+                                   hybrid_denominator_source="all_pq", index_update_interval=interval,
+                                   index_update_strategy=strategy, collect_attention_details=False)
+        att = IVFPQSparseAttention(ic, ac).build_cache(k, v)
+        idx = att.cache.index
+        scale = 1.0 / 128 ** 0.5
+        out = {
+            "input_checksum": np.float64(checksum(k, v, q, nk, nv)),
+            "packed_codes": idx.packed_codes.numpy().copy(),
+            "list_ids": idx.list_ids.to(torch.int32).numpy().copy(),
+            "key_norms": idx.key_norms.numpy().copy(),
+            "coarse": idx.coarse_centroids.numpy().copy(),
+            "codebooks": idx.pq.codebooks.numpy().copy(),
+            "value_means": att.cache.retrieval_value_centroids.numpy().copy(),
+        }
+        approx = idx.approximate_scores(q) * scale
+        out["approx_logits"] = approx.numpy().copy()
+        kk = int(np.ceil(approx.shape[1] * 0.02))
+        out["topk"] = torch.topk(approx, k=kk, dim=1, sorted=True).indices.numpy().copy()
+        out["output0"] = torch.stack([o.output for o in att.forward_many(q)]).numpy().copy()
+        # decode steps: append one token, attend with a rotating query
+        outs = []
+        for i in range(appends):
+            att.append(nk[i], nv[i])
+            if strategy == "deferred" and i == appends // 2:
+                att.apply_pending_index_update()
+            outs.append(torch.stack([o.output for o in att.forward_many(q + 0.01 * i)]))
+        idx = att.cache.index
+        out["outputs_after_appends"] = torch.stack(outs).numpy().copy()
+        out["packed_codes_end"] = idx.packed_codes.numpy().copy()
+        out["list_ids_end"] = idx.list_ids.to(torch.int32).numpy().copy()
+        out["key_norms_end"] = idx.key_norms.numpy().copy()
+        out["value_means_end"] = att.cache.retrieval_value_centroids.numpy().copy()
+        out["coarse_end"] = idx.coarse_centroids.numpy().copy()
+        out["codebooks_end"] = idx.pq.codebooks.numpy().copy()
+        np.savez_compressed(HERE / f"golden_{name}.npz", **out)
+        print(name, "indexed", idx.num_vectors, "bytes", (HERE / f"golden_{name}.npz").stat().st_size)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,173 @@
+"""The adapters with the reference's call signatures, on the GPU: contracts the reference
+tests for its own adapters (tests/test_decode_adapter.py, tests/test_kv_cache_growth.py
+there) plus parity with the oracle holding the same index."""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from helpers import assert_output_close
+from oracle.pqhsa_oracle import OracleAttentionConfig, OracleIndex, OracleIndexConfig, OracleStream
+from pqhsa_release_b200 import workloads
+from pqhsa_release_b200.config import paper_attention_config, paper_index_config
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, H, S, G=1, dtype=torch.bfloat16, seed=0):
+    ks, vs, qs = [], [], []
+    for b in range(B):
+        k, v = workloads.mixture_kv(seed * 100 + b, H, S, dtype=dtype, components=16)
+        ks.append(k); vs.append(v); qs.append(workloads.planted_queries(seed * 100 + 50 + b, k, G))
+    return torch.stack(ks), torch.stack(vs), torch.stack(qs)
+
+
+def _oracle_of(engine, s, frac, interval=256, strategy="deferred"):
+    """Oracle stream holding exactly the index the device holds for stream ``s``."""
+    b, h = divmod(s, engine.H)
+    n = engine.length
+    keys = engine.keys[b, h, :n].float().cpu()
+    values = engine.values[b, h, :n].float().cpu()
+    st = OracleStream(OracleIndexConfig(num_lists=engine.icfg.num_lists),
+                      OracleAttentionConfig(sink_tokens=engine.acfg.sink_tokens, local_window=engine.acfg.local_window,
+                                            retrieval_top_fraction=frac, index_update_interval=interval,
+                                            index_update_strategy=strategy))
+    st.keys, st.values, st.length = keys, values, n
+    st.indexed_length = engine.indexed_length
+    e = engine.pool.export_stream_state(s)
+    if e is not None:
+        ix = OracleIndex(st.icfg)
+        ix.packed, ix.list_ids = e.packed_codes.cpu(), e.list_ids.cpu()
+        ix.norms, ix.coarse, ix.codebooks = e.key_norms.float().cpu(), e.coarse_centroids.float().cpu(), e.codebooks.float().cpu()
+        st.index, st.value_means = ix, e.value_means.float().cpu()
+    return st
+
+
+def test_all_tokens_selected_equals_dense_attention():
+    # reference contract: tests/test_decode_adapter.py:11-47
+    from pqhsa_release_b200 import IVFPQDecodeAttentionAdapter
+
+    k, v, q = _inputs(2, 2, 700, dtype=torch.float32, seed=1)
+    ad = IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=32),
+                                     paper_attention_config(retrieval_top_fraction=1.0, sink_tokens=2, local_window=8))
+    ad.build_cache(k.cuda(), v.cuda())
+    assert ad.leading_shape == (2, 2) and len(ad.streams) == 4
+    out = ad.forward(q.cuda()).context.cpu()
+    logits = torch.einsum("bhd,bhsd->bhs", q, k) / 128 ** 0.5
+    dense = torch.einsum("bhs,bhsd->bhd", torch.softmax(logits, -1), v)
+    assert float((out - dense).abs().max()) <= 5e-4 * float(dense.abs().max())
+
+
+def test_shape_and_state_errors():
+    from pqhsa_release_b200 import IVFPQDecodeAttentionAdapter
+
+    ad = IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=16), paper_attention_config())
+    with pytest.raises(RuntimeError):
+        ad.forward(torch.zeros(1, 1, 128, device="cuda"))
+    with pytest.raises(ValueError):
+        ad.build_cache(torch.zeros(4, 128, device="cuda"), torch.zeros(4, 128, device="cuda"))
+    with pytest.raises(RuntimeError):
+        ad.build_cache(torch.zeros(1, 1, 300, 128), torch.zeros(1, 1, 300, 128))   # CPU tensors: no fallback
+    k, v, q = _inputs(1, 2, 400, seed=2)
+    ad.build_cache(k.cuda(), v.cuda())
+    with pytest.raises(ValueError):
+        ad.forward(torch.zeros(1, 3, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        ad.decode_step(q.cuda())
+    with pytest.raises(ValueError):
+        ad.append(torch.zeros(1, 2, 2, 128, device="cuda"), torch.zeros(1, 2, 2, 128, device="cuda"))
+
+
+@pytest.mark.parametrize("strategy, interval", [("incremental", 1), ("incremental", 5), ("deferred", 6)])
+def test_decode_steps_follow_the_oracle(strategy, interval):
+    """decode_step appends before attending (reference tests/test_decode_adapter.py:91-145); recent
+    tokens stay exact until the update interval (tests/test_acceptance_contracts.py:78-128)."""
+    from pqhsa_release_b200 import IVFPQDecodeAttentionAdapter
+
+    dtype = torch.bfloat16
+    k, v, q = _inputs(1, 2, 1200, dtype=dtype, seed=3)
+    ac = paper_attention_config(retrieval_top_fraction=0.03, index_update_interval=interval,
+                                index_update_strategy=strategy)
+    ad = IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=48), ac).build_cache(k.cuda(), v.cuda())
+    gen = torch.Generator().manual_seed(9)
+    for step in range(14):
+        nk = (k[:, :, 11 * step + 5].float() + 0.3 * torch.randn(1, 2, 128, generator=gen)).to(dtype)
+        nv = torch.randn(1, 2, 128, generator=gen).to(dtype)
+        qq = (q.float() + 0.02 * step).to(dtype)
+        out = ad.decode_step(qq.cuda(), nk.cuda().unsqueeze(2), nv.cuda().unsqueeze(2)).context.float().cpu()
+        eng = ad.attention
+        assert eng.length == 1201 + step
+        if strategy == "deferred" and step == 9:
+            assert ad.apply_pending_index_update() == 2 and ad.apply_pending_index_update() == 0
+            out = ad.forward(qq.cuda()).context.float().cpu()
+        s_end, r_end = eng.bounds()
+        for s in range(2):
+            st = _oracle_of(eng, s, 0.03)
+            assert st.index.num_vectors == r_end - s_end
+            det = st.forward_detail(qq[0, s : s + 1].float())
+            assert_output_close(out[0, s], det.output[0], dtype, f"step {step} stream {s}")
+
+
+def test_state_dict_round_trip():
+    from pqhsa_release_b200 import IVFPQDecodeAttentionAdapter
+
+    k, v, q = _inputs(1, 2, 900, seed=4)
+    ac = paper_attention_config(retrieval_top_fraction=0.05, index_update_interval=1, index_update_strategy="incremental")
+    ad = IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=32), ac).build_cache(k.cuda(), v.cuda())
+    for i in range(3):
+        ad.append(k[:, :, i].cuda(), v[:, :, i].cuda())
+    want = ad.forward(q.cuda()).context
+    state = ad.state_dict()
+    again = IVFPQDecodeAttentionAdapter.from_state_dict(state)
+    got = again.forward(q.cuda()).context
+    assert again.attention.length == 903 and again.leading_shape == (1, 2)
+    assert float((got.float() - want.float()).abs().max()) <= 1e-2 * float(want.float().abs().max())
+    with pytest.raises(ValueError):
+        IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=16), ac).load_state_dict(state)
+
+
+@pytest.mark.parametrize("layout", ["5d", "4d"])
+def test_gqa_sidecar_reads_vllm_pages_in_place(layout):
+    """Both FLASH_ATTN page layouts, 16-token blocks, a permuted block table: the sidecar on the
+    pages equals the sidecar on a contiguous copy and the oracle."""
+    from pqhsa_release_b200 import GQASidecar
+    from pqhsa_release_b200.paged_kv import gather_paged_kv, write_paged_token
+
+    dtype, Hkv, G, S, bs = torch.bfloat16, 2, 4, 1000, 16
+    k, v, q = _inputs(1, Hkv, S, G=G, dtype=dtype, seed=5)
+    nblk = 80
+    gen = torch.Generator().manual_seed(1)
+    table = torch.randperm(nblk, generator=gen)[: (S + 64 + bs - 1) // bs].to(torch.int32).reshape(1, -1).cuda()
+    if layout == "5d":
+        kv_cache = torch.zeros(2, nblk, bs, Hkv, 128, dtype=dtype, device="cuda")
+    else:
+        kv_cache = torch.zeros(nblk, Hkv, bs, 256, dtype=dtype, device="cuda")
+    for t in range(S):
+        write_paged_token(kv_cache, table, 0, t, k[0, :, t].cuda(), v[0, :, t].cuda())
+    kk, vv = gather_paged_kv(kv_cache, table, 0, S)
+    assert torch.equal(kk.cpu(), k) and torch.equal(vv.cpu(), v)
+    md = SimpleNamespace(block_table=table)
+    ic = paper_index_config(num_lists=32)
+    ac = paper_attention_config(retrieval_top_fraction=0.04, index_update_interval=1, index_update_strategy="incremental")
+    paged = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv)
+    paged.set_paged_kv_context(kv_cache, md, 0)
+    paged.build_cache(kk, vv)
+    assert paged.engine.keys is None, "the paged sidecar must not hold a K/V copy"
+    flat = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv).build_cache(k.cuda(), v.cuda())
+    gen = torch.Generator().manual_seed(2)
+    for step in range(4):
+        qq = (q.float() + 0.03 * step).to(dtype).cuda()
+        a, b = paged.forward(qq).float().cpu(), flat.forward(qq).float().cpu()
+        assert float((a - b).abs().max()) <= 1e-2 * float(b.abs().max())
+        for s in range(Hkv):
+            st = _oracle_of(flat.engine, s, 0.04)
+            det = st.forward_detail(qq[0, s * G : (s + 1) * G].float().cpu())
+            for g in range(G):
+                assert_output_close(a[0, s * G + g], det.output[g], dtype, f"step {step} head {s * G + g}")
+        nk, nv = torch.randn(1, Hkv, 128, generator=gen).to(dtype), torch.randn(1, Hkv, 128, generator=gen).to(dtype)
+        write_paged_token(kv_cache, table, 0, S + step, nk[0].cuda(), nv[0].cuda())   # vLLM writes the page
+        assert paged.lean_append(nk.cuda(), nv.cuda())
+        flat.append(nk.cuda(), nv.cuda())
+    with pytest.raises(ValueError):
+        paged.forward(torch.zeros(2, Hkv * G, 128, dtype=dtype, device="cuda"))

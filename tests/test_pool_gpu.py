@@ -1,0 +1,161 @@
+"""Pool-level GPU parity through the C ABI: golden fixtures of the reference, ragged
+batches, the unsorted tail with incremental encoding, and the stand-alone top-k."""
+
+import ctypes as C
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_output_close, make_case, pool_from_case, topk_sets_match
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE / "golden"))
+from make_golden import CASES, case_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["c0_fp32", "mix_bf16"])
+def test_cuda_path_reproduces_the_reference_fixture(name):
+    """Index tensors exactly as the reference built them -> scores, top-k set and output of
+    the reference's own forward_many."""
+    from pqhsa_release_b200.device_index import DeviceIndexPool, StreamIndexTensors
+
+    kind, seed, ctx, lists, group, dtype, strategy, interval, appends = CASES[name]
+    g = np.load(HERE / "golden" / f"golden_{name}.npz")
+    k, v, q, nk, nv = case_inputs(name)
+    # the fixture is fp32 throughout (the reference ran in fp32 on values representable in `dtype`)
+    dt = torch.float32
+    G = 4 if group == 4 else 1
+    rows = q[:G] if group >= G else q
+    pool = DeviceIndexPool(num_streams=1, group=G, dtype=dt, device="cuda", slot_capacity=ctx + 64,
+                           num_lists=lists, sink_tokens=4, local_window=128, scale=128 ** -0.5, top_fraction=0.02)
+    kc = torch.zeros(1, 1, ctx + 64, 128, dtype=dt, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc[0, 0, :ctx], vc[0, 0, :ctx] = k.cuda(), v.cuda()
+    pool.bind_kv_contiguous(kc, vc)
+    idx = StreamIndexTensors(torch.from_numpy(g["packed_codes"]), torch.from_numpy(g["list_ids"]).long(),
+                             torch.from_numpy(g["key_norms"]), torch.from_numpy(g["coarse"]),
+                             torch.from_numpy(g["codebooks"]), torch.from_numpy(g["value_means"]))
+    pool.load_stream(0, idx, seq_len=ctx, req=0, kv_head=0)
+    qd = rows.cuda().reshape(1, G, 128).contiguous()
+    out = pool.decode_step(qd)
+    torch.cuda.synchronize()
+    n = g["approx_logits"].shape[1]
+    pos = pool.slot_pos[0, :n].long().cpu() - 4
+    scores = pool.scan_scores(qd).cpu()
+    for r in range(G):
+        want = torch.from_numpy(g["approx_logits"][r])
+        got = torch.empty_like(want)
+        got[pos] = scores[r, :n]
+        assert float((got - want).abs().max()) <= 1e-3 * float(want.abs().max())
+        sel = pool.selected_positions(r).cpu()
+        ok, nd = topk_sets_match(torch.cat([torch.zeros(4), want]), sel, torch.sort(torch.from_numpy(g["topk"][r]) + 4).values,
+                                 rtol=1e-5)
+        assert ok, f"{nd} members differ beyond boundary ties"
+        assert_output_close(out[0, r].cpu(), torch.from_numpy(g["output0"][r]), dt, f"row {r}")
+
+
+def test_ragged_batch_of_requests():
+    """Requests of different context lengths in one launch (one index per stream, per-stream counts)."""
+    ctxs = [700, 2600, 1500, 140]
+    case = make_case(B=4, Hkv=2, G=4, S=2600, L=64, dtype=torch.bfloat16, seed=21, contexts=ctxs)
+    pool, _, _ = pool_from_case(case)
+    q = case.queries.cuda().reshape(case.num_streams, 4, 128).contiguous()
+    out = pool.decode_step(q).float().cpu()
+    info = pool.ws_view("row_info").cpu()
+    for s, st in enumerate(case.streams):
+        det = st.forward_detail(case.queries.reshape(case.num_streams, 4, 128)[s].float())
+        for g in range(4):
+            assert int(info[s * 4 + g, 0]) == det.topk_local.shape[1]
+            assert_output_close(out[s, g], det.output[g], case.dtype, f"stream {s} row {g}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_incremental_encode_matches_the_oracle(dtype):
+    """append_kv + append_encode against IVFPQIndex.add semantics: list ids and codes bit for bit
+    (a differing assignment must be a numerical tie), norms and value means to storage precision,
+    and the step after each append against the oracle that holds the same index."""
+    from helpers import round_to
+
+    case = make_case(B=1, Hkv=2, G=2, S=900, L=32, dtype=dtype, seed=23, interval=1, strategy="incremental")
+    pool, kc, vc = pool_from_case(case)
+    gen = torch.Generator().manual_seed(5)
+    mism = total = 0
+    for step in range(12):
+        nk = (case.keys[0, :, step * 7 + 3].float() + 0.3 * torch.randn(2, 128, generator=gen)).to(dtype)
+        nv = torch.randn(2, 128, generator=gen).to(dtype)
+        pool.append_kv(nk.cuda().contiguous(), nv.cuda().contiguous())
+        pool.append_encode(1)
+        torch.cuda.synchronize()
+        for s, st in enumerate(case.streams):
+            n_before = st.index.num_vectors
+            st.append(nk[s].float(), nv[s].float())      # the oracle encodes the key that left the window
+            assert st.index.num_vectors == n_before + 1
+            # storage rounding of what the oracle appended, as the device stores it
+            st.index.norms[-1] = round_to(st.index.norms[-1:], dtype)[0]
+            dev = pool.export_stream(s)
+            total += 1
+            same = int(dev["list_ids"][-1]) == int(st.index.list_ids[-1]) and torch.equal(
+                dev["packed_codes"][-1].cpu(), st.index.packed[-1])
+            if not same:
+                mism += 1
+                # adopt the device's assignment so that later steps compare like with like
+                st.index.list_ids[-1] = int(dev["list_ids"][-1])
+                st.index.packed[-1] = dev["packed_codes"][-1].cpu()
+            assert abs(float(dev["key_norms"][-1]) - float(st.index.norms[-1])) <= 1e-6 * float(st.index.norms[-1]) + (
+                0 if dtype == torch.float32 else 1e-2 * float(st.index.norms[-1]))
+            assert int(dev["positions"][-1]) == 4 + st.index.num_vectors - 1
+            # value means: device keeps fp32 running sums and stores the mean in `dtype`
+            lists = st.index.coarse.shape[0]
+            vm_dev = pool.vmeans[s, :lists].float().cpu()
+            from oracle.pqhsa_oracle import list_value_means
+
+            s0, r0 = st.bounds()
+            vm, _, _ = list_value_means(st.index.list_ids, st.values[s0:r0], lists)
+            assert float((vm_dev - vm).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2)
+            st.value_means = vm_dev.clone()
+        q = (case.queries.float() + 0.05 * step).to(dtype)
+        out = pool.decode_step(q.cuda().reshape(2, 2, 128).contiguous()).float().cpu()
+        for s, st in enumerate(case.streams):
+            det = st.forward_detail(q.reshape(2, 2, 128)[s].float())
+            for g in range(2):
+                assert_output_close(out[s, g], det.output[g], dtype, f"step {step} stream {s} row {g}")
+    assert mism <= max(1, total // 20), f"{mism} of {total} encodes differ from the oracle"
+    # folding the tail into the sorted region changes nothing
+    q = case.queries.cuda().reshape(2, 2, 128).contiguous()
+    before = pool.decode_step(q).float().cpu()
+    pool.compact()
+    assert int(pool.h_tail.max()) == 0
+    after = pool.decode_step(q).float().cpu()
+    assert float((before - after).abs().max()) <= 2e-2 * float(before.abs().max())
+
+
+def test_standalone_topk_radix_against_torch_topk():
+    from pqhsa_release_b200 import _lib
+
+    gen = torch.Generator().manual_seed(3)
+    for n, k in [(5000, 100), (131, 131), (4096, 1), (70000, 1400)]:
+        x = torch.randn(3, n, generator=gen)
+        x[1, : n // 2] = x[1, : n // 2].round()          # many exact ties
+        xd = x.cuda()
+        idx = torch.full((3, k), -1, dtype=torch.int32, device="cuda")
+        val = torch.zeros(3, k, device="cuda")
+        _lib.call("pqhsa_topk_radix", xd.data_ptr(), 3, n, n, k, idx.data_ptr(), val.data_ptr(),
+                  torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        ref = torch.topk(x, k, dim=1)
+        for r in range(3):
+            got = idx[r].cpu().long()
+            assert len(set(got.tolist())) == k and int(got.min()) >= 0
+            # same multiset of values (ties may pick different members), values match the indices
+            assert torch.equal(torch.sort(x[r][got]).values, torch.sort(ref.values[r]).values)
+            assert torch.equal(val[r].cpu(), x[r][got])
+            # ties at the k-th value go to the lower index
+            kth = ref.values[r].min()
+            tied = torch.nonzero(x[r] == kth).flatten()
+            chosen = sorted(i for i in got.tolist() if x[r, i] == kth)
+            assert chosen == tied[: len(chosen)].tolist()
