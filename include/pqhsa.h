@@ -240,6 +240,25 @@ int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t
  * (pq_hsa/kernels/triton_lut_scan.py:1027-1104).  Needs pqhsa_lut_build first. */
 int pqhsa_scan_scores(const pqhsa_params* p, float* scores, void* stream);
 
+/* The same result as pqhsa_lut_build followed by pqhsa_scan_scores, for a caller that
+ * cannot allocate device memory (an attention backend inside an inference server whose
+ * free memory has all gone to the KV cache; a C host that owns only the buffers it was
+ * handed).  It has no counterpart in the reference.  p->workspace is ignored: the
+ * per-query tables go to a fixed array inside the library, so nothing is allocated or
+ * freed, here or in any library routine.  Limits and rules:
+ *   - at most PQHSA_STATIC_MAX_ROWS query rows (num_streams * group) per call, else
+ *     PQHSA_E_CAPACITY; the array (~0.7 MB) stays resident on every GPU that loads the
+ *     library until the process exits;
+ *   - the first call on a device looks up the array's device address (a one-time set-up
+ *     that talks to the CUDA runtime): make that first call before any stream capture;
+ *   - every call uses the same array: calls whose kernels could overlap on the GPU
+ *     (different streams, no ordering between them) race with each other.  The array keeps
+ *     whatever the last call left; the counters that must start at zero are cleared on
+ *     the stream at the start of each call.
+ * scores: float [R, slot_capacity]; q, the index pool and max_slots as for pqhsa_scan_scores. */
+#define PQHSA_STATIC_MAX_ROWS 256
+int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, void* stream);
+
 /* Stand-alone exact top-k of float rows: scores [rows, row_stride] (first n
  * valid) -> out_idx int32 [rows, k] (unordered) and out_val float [rows, k].
  * Ties at the k-th value are resolved towards the lower index.  Counterpart of

@@ -67,6 +67,7 @@ EXPORTS = {
     "pqhsa_append_kv": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p]),
     "pqhsa_append_encode": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_scan_scores": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
+    "pqhsa_scan_scores_static": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_topk_radix": (
         C.c_int,
         [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p],
