@@ -182,7 +182,7 @@ class StepRunner:
         self.out = torch.zeros(S, G, D, dtype=wl.dtype, device=dev)
         self.gathered = torch.zeros(world, S, G, D, dtype=wl.dtype, device=dev) if world > 1 else None
         self.graph = None
-        self.launches_per_step = 9  # append_kv, append_encode, lut, scan, threshold, collect, finish, attend, merge
+        self.launches_per_step = 5  # tables + append + encode, scan, select, attend, merge
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture
@@ -194,9 +194,7 @@ class StepRunner:
 
     def _body(self):
         p = self.pool
-        p.append_kv(self.nk, self.nv)
-        p.append_encode(1)
-        p.decode_step(self.q, self.out)
+        p.decode_step_append(self.q, self.nk, self.nv, encode=1, out=self.out)
         if self.gathered is not None:
             torch.distributed.all_gather_into_tensor(self.gathered, self.out)
 

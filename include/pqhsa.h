@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define PQHSA_ABI_VERSION 2
+#define PQHSA_ABI_VERSION 3
 
 /* fixed shape of the index (pq_hsa/kernels/cuda/pq_fused_h20.cu:26-35 fixes the
  * same: 8 subspaces x 4 bits, at most 512 lists, head_dim 128) */
@@ -120,6 +120,11 @@ typedef struct pqhsa_params {
   const void *codes, *norms, *list_ids, *slot_pos, *slot_unit, *unit_off, *unit_list;
   const void *coarse, *codebooks, *vmeans;
   void *vsum, *vcnt, *state, *norm_max;
+  const void *sample;      /* optional int32 [S, PQHSA_SAMPLE_KEYS, 4]: for sample i of a stream, the slot
+                              j = floor(i * n_sorted / 4096) of its list-sorted region as (code, norm as float
+                              bits, list id, j) - a contiguous copy of what the threshold estimate reads, to
+                              be refreshed whenever the sorted region changes; NULL = gather from the index.
+                              Only read for streams with more than PQHSA_SAMPLE_KEYS sorted slots. */
 
   const void *k_base, *v_base;
   const int32_t *block_table;
@@ -216,6 +221,18 @@ enum pqhsa_stage {
   PQHSA_STAGE_ATTEND = 3,   /* exact attention partials (the gather)   */
   PQHSA_STAGE_MERGE = 4     /* background + final merge                */
 };
+
+/* A whole decode step including the token append, in five launches:
+ *   pqhsa_append_kv(new_k, new_v) + pqhsa_append_encode(enc_count, uniform_count) + pqhsa_decode_step
+ * with the row write, the encode and the table construction running side by side in the first
+ * kernel (they touch disjoint data; the stream counters change once all three are done).  Same
+ * results as the three calls in sequence.  new_k / new_v: E [S, 128], 16-byte aligned, or both
+ * NULL when the caller's cache write already happened (no row is written, the length stays).
+ * The per-layer step of the reference's decode loop (pq_append_prep + deferred incremental
+ * encode + attention, benchmarks/e2e_pq_param_sweep.py:6308-6969). */
+int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const void* new_v,
+                             const int32_t* enc_count, int32_t uniform_count, void* stream);
+
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
 
 /* Write one new K/V row per stream into the cache at position seq_len and bump

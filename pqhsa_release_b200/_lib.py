@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 4096
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
@@ -35,6 +35,7 @@ class Params(C.Structure):
         ("slot_unit", C.c_void_p), ("unit_off", C.c_void_p), ("unit_list", C.c_void_p),
         ("coarse", C.c_void_p), ("codebooks", C.c_void_p), ("vmeans", C.c_void_p),
         ("vsum", C.c_void_p), ("vcnt", C.c_void_p), ("state", C.c_void_p), ("norm_max", C.c_void_p),
+        ("sample", C.c_void_p),
         ("k_base", C.c_void_p), ("v_base", C.c_void_p), ("block_table", C.c_void_p),
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
@@ -63,6 +64,7 @@ EXPORTS = {
     "pqhsa_scan_select": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_attend_merge": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "pqhsa_decode_step_append": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_run_stage": (C.c_int, [C.POINTER(Params), C.c_int, C.c_void_p]),
     "pqhsa_append_kv": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p]),
     "pqhsa_append_encode": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p]),

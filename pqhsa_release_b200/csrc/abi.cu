@@ -158,7 +158,7 @@ int pqhsa_lut_build(const pqhsa_params* p, void* stream) {
   if (!p->q) return set_error(PQHSA_E_NULL, "q is null");
   pqhsa_ws_layout w;
   layout_of(p, &w);
-  return launch_lut_build(*p, w, (cudaStream_t)stream);
+  return launch_lut_build(*p, w, nullptr, (cudaStream_t)stream);
 }
 
 int pqhsa_scan_select(const pqhsa_params* p, void* stream) {
@@ -182,7 +182,33 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
   pqhsa_ws_layout w;
   layout_of(p, &w);
   cudaStream_t st = (cudaStream_t)stream;
-  if (int rc = launch_lut_build(*p, w, st)) return rc;
+  if (int rc = launch_lut_build(*p, w, nullptr, st)) return rc;
+  if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
+  if (int rc = launch_select(*p, w, st)) return rc;
+  if (int rc = launch_attend(*p, w, st)) return rc;
+  return launch_merge(*p, w, st);
+}
+
+int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const void* new_v, const int32_t* enc_count,
+                             int32_t uniform_count, void* stream) {
+  if (int rc = check_params(p, true, true, true)) return rc;
+  if ((new_k == nullptr) != (new_v == nullptr)) return set_error(PQHSA_E_NULL, "new_k and new_v go together");
+  if (((uintptr_t)new_k | (uintptr_t)new_v) & 15) return set_error(PQHSA_E_SHAPE, "new_k / new_v must be 16-byte aligned");
+  if (uniform_count < 0) return set_error(PQHSA_E_SHAPE, "uniform_count must be non-negative");
+  const bool encode = enc_count != nullptr || uniform_count > 0;
+  if (encode && (!p->vsum || !p->vcnt)) return set_error(PQHSA_E_NULL, "vsum / vcnt is null");
+  pqhsa_ws_layout w;
+  layout_of(p, &w);
+  cudaStream_t st = (cudaStream_t)stream;
+  StepAppend ap = {new_k, new_v, enc_count, uniform_count};
+  if (new_k != nullptr && encode && p->local_window == 0) {
+    // the key to encode may be the row written in this very step: keep the two in order
+    if (int rc = launch_append_kv(*p, new_k, new_v, st)) return rc;
+    if (int rc = launch_append_encode(*p, enc_count, uniform_count, st)) return rc;
+    if (int rc = launch_lut_build(*p, w, nullptr, st)) return rc;
+  } else {
+    if (int rc = launch_lut_build(*p, w, &ap, st)) return rc;
+  }
   if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
   if (int rc = launch_select(*p, w, st)) return rc;
   if (int rc = launch_attend(*p, w, st)) return rc;
@@ -197,7 +223,7 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
   layout_of(p, &w);
   cudaStream_t st = (cudaStream_t)stream;
   switch (stage) {
-    case PQHSA_STAGE_LUT: return launch_lut_build(*p, w, st);
+    case PQHSA_STAGE_LUT: return launch_lut_build(*p, w, nullptr, st);
     case PQHSA_STAGE_SCAN: return launch_scan(*p, w, nullptr, st);
     case PQHSA_STAGE_SELECT: return launch_select(*p, w, st);
     case PQHSA_STAGE_ATTEND: return launch_attend(*p, w, st);

@@ -33,7 +33,14 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o);
 int sm_count();
 
 // kernel launchers, one translation unit each; all return a pqhsa_status
-int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+// What the first kernel of a step does besides the tables when the token append is fused into it.
+struct StepAppend {
+  const void* new_k;         // E [S, 128] or null: no row is written and the length stays
+  const void* new_v;
+  const int32_t* enc_count;  // device int32 [S] or null
+  int32_t uniform_count;     // keys to encode per stream when enc_count is null
+};
+int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st);
 int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cudaStream_t st);
 int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
 int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
@@ -161,12 +168,13 @@ __device__ __forceinline__ float pq_sum_row(const float* lut, uint32_t code) {
   return acc;
 }
 
-// Contribution of one key to the exp-sum of its scan unit, relative to the
-// unit's maximum logit.  The scan adds it and the selection subtracts it for a
-// selected key: same inputs, same instructions, so the removal is exact.
-__device__ __forceinline__ float unit_term(float logit, float unit_max) {
-  return ex2(__fmul_rn(__fsub_rn(logit, unit_max), kLog2e));
-}
+// Contribution of one key to the exp-sum of its scan unit, relative to the unit's maximum
+// logit: 2^(logit * log2(e) + ref), ref = unit_ref(unit maximum), one fused multiply-add
+// (the scan runs it on two rows at a time with the packed form, which rounds identically).
+// The scan adds it and the selection subtracts it for a selected key: same inputs, same
+// operations, so the removal is exact.
+__device__ __forceinline__ float unit_ref(float unit_max) { return -__fmul_rn(unit_max, kLog2e); }
+__device__ __forceinline__ float unit_term(float logit, float ref) { return ex2(__fmaf_rn(logit, kLog2e, ref)); }
 
 // histogram bin of a logit: monotone non-decreasing in the logit
 __device__ __forceinline__ int logit_bin(float logit, float lo, float inv_w) {

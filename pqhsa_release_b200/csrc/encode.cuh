@@ -1,0 +1,232 @@
+// Incremental encode of keys that have left the local window (shared by the stand-alone
+// append_encode kernel and the fused first kernel of a decode step).
+//
+// Mirrors IVFPQIndex.add with fixed codebooks (pq_hsa/index/ivfpq.py:598-645): |k| and
+// direction (:1052-1059), nearest list by Euclidean distance (:1001-1005), residual
+// (:1012-1016), nearest code word per subspace (pq_hsa/index/pq.py:97-115), nibble packing
+// (pq_hsa/index/packing.py:6-34); and the running per-list value mean of
+// pq_hsa/attention/kv_cache.py:730-776.  All arithmetic is fp32 on the stored element
+// values; ties go to the lower index as torch.argmin does.
+#pragma once
+#include "common.cuh"
+
+namespace pqhsa {
+
+struct EncodeArgs {
+  uint32_t* codes;
+  void* norms;
+  uint16_t* list_ids;
+  int32_t* slot_pos;
+  const void* coarse;
+  const void* codebooks;
+  void* vmeans;
+  float* vsum;
+  int32_t* vcnt;
+  int32_t* state;
+  float* norm_max;
+  const void* k_base;
+  const void* v_base;
+  KvAddr kv;
+  const int32_t* enc_count;
+  int uniform_count, cap, tail_cap, num_lists, sink;
+};
+
+inline EncodeArgs make_encode_args(const pqhsa_params& p, const int32_t* cnt, int32_t uni) {
+  EncodeArgs a;
+  a.codes = static_cast<uint32_t*>(const_cast<void*>(p.codes));
+  a.norms = const_cast<void*>(p.norms);
+  a.list_ids = static_cast<uint16_t*>(const_cast<void*>(p.list_ids));
+  a.slot_pos = static_cast<int32_t*>(const_cast<void*>(p.slot_pos));
+  a.coarse = p.coarse;
+  a.codebooks = p.codebooks;
+  a.vmeans = const_cast<void*>(p.vmeans);
+  a.vsum = static_cast<float*>(p.vsum);
+  a.vcnt = static_cast<int32_t*>(p.vcnt);
+  a.state = static_cast<int32_t*>(p.state);
+  a.norm_max = static_cast<float*>(p.norm_max);
+  a.k_base = p.k_base;
+  a.v_base = p.v_base;
+  a.kv = make_kvaddr(p);
+  a.enc_count = cnt;
+  a.uniform_count = uni;
+  a.cap = p.slot_capacity;
+  a.tail_cap = p.tail_capacity;
+  a.num_lists = p.num_lists;
+  a.sink = p.sink_tokens;
+  return a;
+}
+
+// Encodes the next `count` tokens after the indexed region of stream s (all threads of the CTA
+// take part; THREADS is the CTA size, a multiple of 128 and at least 128).  seq_len is the
+// stream's length including any token appended in the same launch.  Returns the new tail count
+// (the caller stores it).
+template <typename E, int THREADS>
+__device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, const int seq_len) {
+  constexpr int kEncThreads = THREADS;
+  __shared__ float unit[kD];
+  __shared__ float resid[kD];
+  __shared__ float red[kEncThreads / 32];
+  __shared__ float best_d[kEncThreads / 32];
+  __shared__ int best_l[kEncThreads / 32];
+  __shared__ uint32_t code_sh;
+  __shared__ int list_sh;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t* st = a.state + (size_t)s * kST;
+  const int count = a.enc_count ? a.enc_count[s] : a.uniform_count;
+  const int n_sorted = st[PQHSA_ST_N_SORTED];
+  int n_tail = st[PQHSA_ST_N_TAIL];
+  const int nl = st[PQHSA_ST_N_LISTS];
+  const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
+  const int sink_end = min(a.sink, seq_len);
+  const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
+  const E* books = static_cast<const E*>(a.codebooks) + (size_t)s * kM * kC * kSub;
+  const E* kb = static_cast<const E*>(a.k_base);
+  const E* vb = static_cast<const E*>(a.v_base);
+
+  for (int it = 0; it < count; ++it) {
+    const int pos = sink_end + n_sorted + n_tail;
+    const int slot = n_sorted + n_tail;
+    // never index a token that is not in the cache, never overrun the pool
+    if (pos >= seq_len || slot >= a.cap || n_tail >= a.tail_cap) break;
+    const long long off = a.kv.offset(req, head, pos);
+
+    // |k| and the unit direction
+    float kval = 0.f;
+    if (tid < kD) kval = to_f(kb[off + tid]);
+    const float sq = warp_sum(kval * kval);
+    __syncthreads();
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kEncThreads / 32; ++i) tot += red[i];
+    const float nrm = fmaxf(sqrtf(tot), 1e-12f);
+    if (tid < kD) unit[tid] = kval / nrm;
+    __syncthreads();
+
+    // nearest list: argmin_l |u - c_l|^2 = |c_l|^2 - 2 u.c_l (+ |u|^2, constant)
+    // 4 lanes per list (32 dims each, four 16-byte loads), 64 lists per pass, two passes of
+    // loads in flight at a time: the 128 KB of centroids stream in a handful of round trips
+    float bd = __builtin_huge_valf();
+    int bl = 0x7fffffff;
+    {
+      const int sub = tid & 3, grp = tid >> 2;  // 64 groups of 4 lanes
+      constexpr int kGroups = kEncThreads / 4;
+      float uq[32];
+#pragma unroll
+      for (int d = 0; d < 32; ++d) uq[d] = unit[sub * 32 + d];
+      for (int l0 = 0; l0 < nl; l0 += 2 * kGroups) {
+        float c[2][32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int l = l0 + h * kGroups + grp;
+          if (l < nl) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float t[8];
+              load8(coarse + (size_t)l * kD + sub * 32 + j * 8, t);
+#pragma unroll
+              for (int d = 0; d < 8; ++d) c[h][j * 8 + d] = t[d];
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int l = l0 + h * kGroups + grp;
+          float dist = 0.f;
+          if (l < nl) {
+#pragma unroll
+            for (int d = 0; d < 32; ++d) {
+              const float df = uq[d] - c[h][d];
+              dist = fmaf(df, df, dist);
+            }
+          }
+          dist += __shfl_xor_sync(0xffffffffu, dist, 1);
+          dist += __shfl_xor_sync(0xffffffffu, dist, 2);
+          if (l < nl && dist < bd) {  // l ascends within a thread, so strict < keeps the lowest index on ties
+            bd = dist;
+            bl = l;
+          }
+        }
+      }
+      // best over the 8 groups of a warp (distance, then lower list index)
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+        const int ol = __shfl_xor_sync(0xffffffffu, bl, o);
+        if (od < bd || (od == bd && ol < bl)) {
+          bd = od;
+          bl = ol;
+        }
+      }
+    }
+    if (lane == 0) {
+      best_d[warp] = bd;
+      best_l[warp] = bl;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float d0 = best_d[0];
+      int l0 = best_l[0];
+      for (int i = 1; i < kEncThreads / 32; ++i)
+        if (best_d[i] < d0 || (best_d[i] == d0 && best_l[i] < l0)) {
+          d0 = best_d[i];
+          l0 = best_l[i];
+        }
+      list_sh = l0;
+      code_sh = 0u;
+    }
+    __syncthreads();
+    const int lid = list_sh;
+    if (tid < kD) resid[tid] = unit[tid] - to_f(coarse[(size_t)lid * kD + tid]);
+    __syncthreads();
+
+    // nearest code word per subspace: thread (m, c) for tid < 128, 16 lanes per subspace
+    if (tid < kM * kC) {
+      const int m = tid / kC, c = tid % kC;
+      const E* cw = books + (size_t)tid * kSub;
+      float dist = 0.f;
+#pragma unroll
+      for (int d = 0; d < kSub; ++d) {
+        const float df = resid[m * kSub + d] - to_f(cw[d]);
+        dist = fmaf(df, df, dist);
+      }
+      int bc = c;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        const float od = __shfl_xor_sync(0xffffffffu, dist, o);
+        const int oc = __shfl_xor_sync(0xffffffffu, bc, o);
+        if (od < dist || (od == dist && oc < bc)) {
+          dist = od;
+          bc = oc;
+        }
+      }
+      if (c == 0) atomicOr(&code_sh, (uint32_t)bc << (4 * m));
+    }
+    __syncthreads();
+
+    if (tid == 0) {
+      a.codes[(size_t)s * a.cap + slot] = code_sh;
+      static_cast<E*>(a.norms)[(size_t)s * a.cap + slot] = from_f<E>(nrm);
+      a.list_ids[(size_t)s * a.cap + slot] = (uint16_t)lid;
+      a.slot_pos[(size_t)s * a.cap + slot] = pos;
+      const float stored = to_f(from_f<E>(nrm));
+      if (stored > a.norm_max[s]) a.norm_max[s] = stored;
+    }
+    // running value mean of the list
+    if (tid < kD) {
+      const size_t vi = ((size_t)s * a.num_lists + lid) * kD + tid;
+      const float nsum = a.vsum[vi] + to_f(vb[off + tid]);
+      const int ncnt = a.vcnt[(size_t)s * a.num_lists + lid] + 1;
+      a.vsum[vi] = nsum;
+      static_cast<E*>(a.vmeans)[vi] = from_f<E>(nsum / (float)ncnt);
+    }
+    __syncthreads();
+    if (tid == 0) a.vcnt[(size_t)s * a.num_lists + lid] += 1;
+    ++n_tail;
+    __syncthreads();
+  }
+  return n_tail;
+}
+
+}  // namespace pqhsa

@@ -1,5 +1,9 @@
-// Per-query, per-head table construction and candidate-threshold estimate
-// (first kernel of a decode step).
+// First kernel of a decode step: per-query, per-head table construction and the
+// candidate-threshold estimate, optionally fused with the step's token append (raw K/V row
+// write) and the incremental encode of the key that left the local window.  The CTAs of a
+// stream take roles by blockIdx.y - tables, list scores (64 lists each), encode - and run
+// side by side; nobody changes a stream counter before every CTA of the stream has arrived,
+// so all roles see the same state.
 //
 // For every stream s and query row g:
 //   lut[s][g][m][c]      = scale * <q_g restricted to subspace m, codebooks[s][m][c]>
@@ -19,7 +23,7 @@
 // tau is only a filter: if fewer than K candidates turn up (probability ~1e-9 at
 // the default margin of 6 sigma) the selection kernel falls back to all keys, so
 // the result is exact either way.
-#include "common.cuh"
+#include "encode.cuh"
 
 namespace pqhsa {
 
@@ -30,11 +34,12 @@ struct LutArgs {
   const void* q;
   const void* codebooks;
   const void* coarse;
-  const int32_t* state;
+  int32_t* state;
   const float* norm_max;
   const uint32_t* codes;
   const void* norms;
   const uint16_t* list_ids;
+  const int4* sample;  // [S, kSample] (code, norm as float bits, list, slot) of the stratified sample, or null
   float* lut;
   float* list_scores;
   int32_t* row_info;
@@ -46,6 +51,15 @@ struct LutArgs {
   double top_fraction;
   int topk_fixed;
   float fixed_lo, fixed_inv_w, margin;
+  // fused append (all null / 0 when the kernel only builds tables)
+  void* k_base;
+  void* v_base;
+  const void* new_k;
+  const void* new_v;
+  KvAddr kv;
+  int list_ctas;  // CTAs per stream with the list-score role
+  int encode;     // 1: one more CTA per stream encodes enc.enc_count[s] / enc.uniform_count keys
+  EncodeArgs enc;
 };
 
 template <typename E, int G>
@@ -56,13 +70,40 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   __shared__ float lut_s[G][kM * kC];
   __shared__ uint32_t wsum[kLutThreads / 32];
   __shared__ int is_last;
+  __shared__ float bin_s[G][2];
   const int s = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const E* q = static_cast<const E*>(a.q);
-  for (int i = tid; i < G * kD; i += kLutThreads) qs[i / kD][i % kD] = to_f(q[(size_t)s * G * kD + i]) * a.scale;
-  __syncthreads();
+  const bool append = a.new_k != nullptr;
+  const int seq_old = a.state[(size_t)s * kST + PQHSA_ST_SEQ_LEN];
+
+  if ((int)blockIdx.y > a.list_ctas) {
+    // encode role: the token just appended counts as part of the stream
+    const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old + (append ? 1 : 0));
+    if (tid == 0) a.state[(size_t)s * kST + PQHSA_ST_N_TAIL] = n_tail;
+  } else {
+    for (int i = tid; i < G * kD; i += kLutThreads) qs[i / kD][i % kD] = to_f(q[(size_t)s * G * kD + i]) * a.scale;
+    __syncthreads();
+  }
 
   if (blockIdx.y == 0) {
+    if (a.sample != nullptr) {  // the last CTA of the stream will want the sample: start it towards L2
+      const char* sp = reinterpret_cast<const char*>(a.sample + (size_t)s * kSample) + (size_t)tid * 128;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(sp));
+    }
+    if (append && tid < 2 * kD / 8) {
+      // the step's K/V row, 16 bytes per thread (elements are 2 or 4 bytes: 8 or 4 per vector)
+      constexpr int kVec = 16 / (int)sizeof(E);
+      const int32_t* st = a.state + (size_t)s * kST;
+      const long long off = a.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], seq_old);
+      for (int i = tid; i < 2 * kD / kVec; i += 2 * kD / 8) {
+        const bool isv = i >= kD / kVec;
+        const int e = (isv ? i - kD / kVec : i) * kVec;
+        const E* src = static_cast<const E*>(isv ? a.new_v : a.new_k) + (size_t)s * kD + e;
+        E* dst = static_cast<E*>(isv ? a.v_base : a.k_base) + off + e;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+      }
+    }
     if (tid < kM * kC) {
       const int m = tid / kC;
       const E* cw = static_cast<const E*>(a.codebooks) + ((size_t)s * kM * kC + tid) * kSub;
@@ -88,21 +129,16 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
     }
     __syncthreads();
     if (tid < G) {
-      // |logit| <= (scale |q| max_l |c_l| + sum_m max_c |lut[m][c]|) * max |k|, |c_l| <= 1
-      float lo = a.fixed_lo, inv_w = a.fixed_inv_w;
-      if (!(a.fixed_inv_w > 0.f)) {
-        float qq = 0.f, pm = 0.f;
-        for (int d = 0; d < kD; ++d) qq = fmaf(qs[tid][d], qs[tid][d], qq);
+      // |logit| <= (scale |q| max_l |c_l| + sum_m max_c |lut[m][c]|) * max |k|, |c_l| <= 1: the part
+      // that does not depend on the norms is parked here; the last CTA multiplies max |k| in
+      // (the encode role may still be raising it)
+      float qq = 0.f, pm = 0.f;
+      for (int d = 0; d < kD; ++d) qq = fmaf(qs[tid][d], qs[tid][d], qq);
 #pragma unroll
-        for (int m = 0; m < kM; ++m) pm += sub_max[tid][m];
-        const float bound = (sqrtf(qq) + pm) * a.norm_max[s] * 1.0001f;
-        lo = -bound;
-        inv_w = bound > 1e-30f ? (float)(kBins / 2) / bound : 1.f;
-      }
-      a.row_bin[((size_t)s * G + tid) * 2] = lo;
-      a.row_bin[((size_t)s * G + tid) * 2 + 1] = inv_w;
+      for (int m = 0; m < kM; ++m) pm += sub_max[tid][m];
+      a.row_bin[((size_t)s * G + tid) * 2] = sqrtf(qq) + pm;
     }
-  } else {
+  } else if ((int)blockIdx.y <= a.list_ctas) {
     // list scores: one warp per list, a lane owns 4 dims
     const int l0 = (blockIdx.y - 1) * kListsPerCta;
     float qr[G][4];
@@ -150,11 +186,23 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   __syncthreads();
   if (!is_last) return;
 
-  const int32_t* st = a.state + (size_t)s * kST;
+  // every CTA of the stream is done: counters may change now; what other CTAs wrote is read through L2
+  int32_t* st = a.state + (size_t)s * kST;
+  if (append && tid == 0) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
   const int n_sorted = st[PQHSA_ST_N_SORTED];
-  const int n = n_sorted + st[PQHSA_ST_N_TAIL];
+  const int n = n_sorted + __ldcg(st + PQHSA_ST_N_TAIL);
   const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
   if (tid < G) {
+    float lo = a.fixed_lo, inv_w = a.fixed_inv_w;
+    if (!(a.fixed_inv_w > 0.f)) {
+      const float bound = __ldcg(a.row_bin + ((size_t)s * G + tid) * 2) * __ldcg(a.norm_max + s) * 1.0001f;
+      lo = -bound;
+      inv_w = bound > 1e-30f ? (float)(kBins / 2) / bound : 1.f;
+    }
+    a.row_bin[((size_t)s * G + tid) * 2] = lo;
+    a.row_bin[((size_t)s * G + tid) * 2 + 1] = inv_w;
+    bin_s[tid][0] = lo;
+    bin_s[tid][1] = inv_w;
     int32_t* ri = a.row_info + ((size_t)s * G + tid) * kRI;
     ri[PQHSA_RI_K] = K;
     ri[PQHSA_RI_N] = n;
@@ -178,8 +226,8 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   float lo[G], iw[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    lo[g] = __ldcg(a.row_bin + ((size_t)s * G + g) * 2);
-    iw[g] = __ldcg(a.row_bin + ((size_t)s * G + g) * 2 + 1);
+    lo[g] = bin_s[g][0];
+    iw[g] = bin_s[g][1];
   }
   const uint32_t* codes = a.codes + (size_t)s * a.cap;
   const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
@@ -189,13 +237,24 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   uint32_t code[kPer];
   float kn[kPer];
   int li[kPer];
+  if (a.sample != nullptr) {
+    const int4* rec = a.sample + (size_t)s * kSample;  // the same slots, gathered when the layout was made
 #pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    const int i = tid + j * kLutThreads;
-    const int slot = (int)((long long)(i < ns ? i : 0) * n_sorted / ns);
-    code[j] = __ldg(codes + slot);
-    kn[j] = to_f(norms[slot]);
-    li[j] = lids[slot];
+    for (int j = 0; j < kPer; ++j) {
+      const int4 v = __ldg(rec + tid + j * kLutThreads);
+      code[j] = (uint32_t)v.x;
+      kn[j] = __int_as_float(v.y);
+      li[j] = v.z;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = tid + j * kLutThreads;
+      const int slot = (int)((long long)(i < ns ? i : 0) * n_sorted / ns);
+      code[j] = __ldg(codes + slot);
+      kn[j] = to_f(norms[slot]);
+      li[j] = lids[slot];
+    }
   }
   float lsv[kPer][G];
 #pragma unroll
@@ -254,13 +313,13 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
 }
 
 template <typename E, int G>
-static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
+static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st) {
   char* ws = static_cast<char*>(p.workspace);
   LutArgs a;
   a.q = p.q;
   a.codebooks = p.codebooks;
   a.coarse = p.coarse;
-  a.state = static_cast<const int32_t*>(p.state);
+  a.state = static_cast<int32_t*>(p.state);
   a.norm_max = static_cast<const float*>(p.norm_max);
   a.codes = static_cast<const uint32_t*>(p.codes);
   a.norms = p.norms;
@@ -279,19 +338,28 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.fixed_lo = p.hist_lo;
   a.fixed_inv_w = p.hist_inv_width;
   a.margin = p.select_margin;
+  a.sample = static_cast<const int4*>(p.sample);
+  a.list_ctas = (p.num_lists + kListsPerCta - 1) / kListsPerCta;
+  a.k_base = const_cast<void*>(p.k_base);
+  a.v_base = const_cast<void*>(p.v_base);
+  a.kv = make_kvaddr(p);
+  a.new_k = ap ? ap->new_k : nullptr;
+  a.new_v = ap ? ap->new_v : nullptr;
+  a.encode = (ap && (ap->enc_count != nullptr || ap->uniform_count > 0)) ? 1 : 0;
+  a.enc = make_encode_args(p, ap ? ap->enc_count : nullptr, ap ? ap->uniform_count : 0);
   const size_t smem = (size_t)G * kBins * sizeof(uint32_t);
   auto kern = lut_build_kernel<E, G>;
   if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("lut_build: shared memory opt-in");
   }
-  const dim3 grid(p.num_streams, 1 + (p.num_lists + kListsPerCta - 1) / kListsPerCta);
+  const dim3 grid(p.num_streams, 1 + a.list_ctas + a.encode);
   kern<<<grid, kLutThreads, smem, st>>>(a);
   return check_launch("lut_build");
 }
 
-int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
-  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_lut_build_t<E, G>(p, w, st))));
+int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st) {
+  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_lut_build_t<E, G>(p, w, ap, st))));
   return PQHSA_OK;
 }
 

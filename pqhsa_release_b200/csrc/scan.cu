@@ -10,40 +10,43 @@
 // consecutive slots of ONE list, so the list score is a warp-uniform register
 // and the per-list log-sum-exp is a warp reduction with no atomics.  All units
 // of all streams form one global sequence; a persistent grid (one CTA per SM)
-// takes equal contiguous shares of it, so ragged contexts balance by
-// themselves.  A warp takes one unit at a time; lanes take consecutive slots
-// (coalesced 4-byte code and 2-byte norm loads, all of a unit in flight at once).
-// Slots of the unsorted tail carry their own list id and are scored in the same
-// launch; their logits are kept individually.
+// takes equal shares of it, so ragged contexts balance by themselves.  Inside a
+// stream the sequence is a stride permutation of the units, so every CTA gets
+// units from all over the stream (lists with many candidates do not pile up on one
+// CTA).  The unit headers of a share are staged in shared memory; a warp takes one
+// unit at a time, lanes take consecutive slots (coalesced 4-byte code and 2-byte
+// norm loads), and the loads of a warp's next unit are issued before the current
+// one is scored.  Slots of the unsorted tail carry their own list id and are
+// scored in the same launch; their logits are kept individually.
 //
-// The scan is bound by instruction issue and shared-memory bandwidth, not HBM
-// (8 bytes per key against G sums of 8 table entries), so the inner loop is
-// built to be short:
+// The scan is bound by instruction issue, not HBM (8 bytes per key against G sums
+// of 8 table entries), so the inner loop is built to be short:
 //   * the 8 nibble tables are folded into 4 byte-pair tables (256 entries of
 //     min(G,4) floats) when a CTA enters a stream, replicated so that lane j of a
 //     quarter warp reads replica j: every LDS.128 hits distinct banks whatever the
 //     codes are - 4 conflict-free 16-byte lookups per key (128 KB of tables);
 //     G = 8 runs two such passes;
-//   * the 4 rows of a pass are carried as two packed f32x2 values (add / mul on
+//   * the rows of a pass are carried as packed f32x2 values (add / mul / fma on
 //     two rows per instruction, same IEEE rounding as the scalar form);
 //   * the unit maximum is one redux.sync.max.f32 per row;
-//   * a key whose logit reaches the row's threshold is a candidate: the lane
-//     drops (slot, row, logit) into a lane-private shared-memory buffer and the
-//     warp flushes the buffers together, one global atomic per row and flush.
+//   * a row looks for candidates (logit >= the row's threshold) only in units whose
+//     maximum reaches the threshold; a candidate goes to a lane-private shared-memory
+//     buffer and the warp flushes the buffers together, one global atomic per row
+//     and flush.
 //
 // Outputs per query row: per-unit (max, sum exp) - a unit's logits stay in
 // registers and the sum is taken against the unit's final maximum, so every key
-// contributes exactly unit_term(logit, max) and the selection kernel can remove
-// a selected key again without cancellation error - the tail logits, and the
-// candidates.  The logits themselves are never written; the separate dump kernel
-// writes all of them for tests and the stand-alone scoring entry point.
+// contributes exactly unit_term(logit, reference) and the selection kernel can
+// remove a selected key again without cancellation error - the tail logits, and
+// the candidates.  The logits themselves are never written; the separate dump
+// kernel writes all of them for tests and the stand-alone scoring entry point.
 #include "common.cuh"
 
 namespace pqhsa {
 
-constexpr int kScanThreads = 1024;
-constexpr int kScanWarps = kScanThreads / 32;
-constexpr int kLanePriv = 8;  // lane-private staged candidates
+constexpr int kScanThreads = 512;  // 16 warps with 128 registers each: a unit in flight and one being scored
+constexpr int kLanePriv = 8;       // lane-private staged candidates
+constexpr int kHdr = 512;     // unit headers staged in shared memory at a time
 constexpr int kIter = kUnit / 32;
 
 template <int G> struct PairShape {
@@ -190,175 +193,297 @@ __device__ __noinline__ void flush_lane_buffers(const int2* wst, int pc, uint32_
   }
 }
 
-template <typename E, int G>
-__global__ void __launch_bounds__(kScanThreads, 1) scan_kernel(const ScanArgs a) {
+template <typename E, int G, int T>
+__global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
   using PS = PairShape<G>;
   constexpr int GP = PS::GP;
+  constexpr int W = T / 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* tab = reinterpret_cast<float*>(smem_raw);           // pair tables
-  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);  // [warps][kLanePriv][32] (slot, logit bits)
+  float* tab = reinterpret_cast<float*>(smem_raw);                        // pair tables
+  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);               // [W][kLanePriv][32] (slot, logit bits)
+  float* lsc_s = reinterpret_cast<float*>(stage + W * kLanePriv * 32);    // [kLMax][GP] list scores of the pass
+  int4* hdr = reinterpret_cast<int4*>(lsc_s + kLMax * GP);                // [kHdr] staged units (first slot, slots, list, unit)
   __shared__ float lut_s[GP][kM * kC];
+  __shared__ long long s_red[32];
+  __shared__ int s_pref[T], s_ut[T], s_first;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int2* wst = stage + (size_t)warp * kLanePriv * 32;
 
-  // this CTA's share [g0, g1) of the global unit sequence; streams are walked in order
-  long long total = 0;
-  for (int s = 0; s < a.S; ++s) {
+  auto units_of = [&](int s) -> int {
     const int32_t* st = a.state + (size_t)s * kST;
-    total += st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
-  }
+    return st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
+  };
+
+  // total number of units (all streams), one load per thread
+  long long part = 0;
+  for (int s = tid; s < a.S; s += T) part += units_of(s);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) s_red[warp] = part;
+  __syncthreads();
+  long long total = 0;
+#pragma unroll
+  for (int w = 0; w < W; ++w) total += s_red[w];
+  // this CTA's share [g0, g1) of the global unit sequence
   const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
   if (g0 >= g1) return;
 
-  long long sbase = 0;  // global index of the first unit of stream s
-  for (int s = 0; s < a.S && sbase < g1; ++s) {
-    const int32_t* st = a.state + (size_t)s * kST;
-    const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
-    const int u_tot = n_units + (n_tail + kUnit - 1) / kUnit;
-    const long long lo_g = sbase > g0 ? sbase : g0;
-    const long long hi_g = sbase + u_tot < g1 ? sbase + u_tot : g1;
-    const int u0 = (int)(lo_g - sbase), u1 = (int)(hi_g - sbase);
-    sbase += u_tot;
-    if (u0 >= u1) continue;
+  long long carry = 0;  // global index of the first unit of stream `base`
+  for (int base = 0; base < a.S && carry < g1; base += T) {
+    // exclusive prefix of the unit counts of streams base .. base + T - 1
+    const int ut = base + tid < a.S ? units_of(base + tid) : 0;
+    int incl = ut;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    __syncthreads();  // s_red, s_pref, s_ut, s_first of the previous round are no longer read
+    if (lane == 31) s_red[warp] = incl;
+    if (tid == 0) s_first = 0;
+    __syncthreads();
+    int woff = 0, ctot = 0;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const int v = (int)s_red[w];
+      woff += w < warp ? v : 0;
+      ctot += v;
+    }
+    const int excl = woff + incl - ut;
+    s_pref[tid] = excl;
+    s_ut[tid] = ut;
+    if (ut > 0 && carry + excl <= g0 && g0 < carry + excl + ut) s_first = tid;  // the stream holding g0
+    __syncthreads();
+    if (carry + ctot > g0) {
+      const int tend = min(T, a.S - base);
+      for (int t = s_first; t < tend; ++t) {
+        const long long sb = carry + s_pref[t];
+        const int u_tot = s_ut[t];
+        if (sb >= g1) break;
+        if (u_tot == 0 || sb + u_tot <= g0) continue;
+        const int s = base + t;
+        const int u0 = (int)((sb > g0 ? sb : g0) - sb), u1 = (int)((sb + u_tot < g1 ? sb + u_tot : g1) - sb);
 
-    const uint32_t* codes = a.codes + (size_t)s * a.cap;
-    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
-    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-    const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
-    const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
+        const int32_t* st = a.state + (size_t)s * kST;
+        const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
+        const uint32_t* codes = a.codes + (size_t)s * a.cap;
+        const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+        const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+        const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
+        const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
+        // first slot of unit u (sorted units, then 128-slot chunks of the tail); also valid for u = u_tot
+        auto unit_first = [&](int u) -> int {
+          return u < n_units ? uoff[u] : n_sorted + min((u - n_units) * kUnit, n_tail);
+        };
+        // Position x of the stream's share sequence is unit (x * stride) mod u_tot, stride a prime that
+        // does not divide u_tot: a bijection that hands every CTA units from all over the stream.  Lists
+        // with many candidates would otherwise all fall to the one CTA that owns their range.
+        int stride = 127;
+        if (u_tot % stride == 0) stride = 131;
 
 #pragma unroll 1
-    for (int pass = 0; pass < PS::NP; ++pass) {
-      const int row0 = s * G + pass * GP;  // first query row of this pass
-      __syncthreads();                     // the previous tables are no longer in use
-      for (int i = tid; i < GP * kM * kC; i += kScanThreads)
-        lut_s[i / (kM * kC)][i % (kM * kC)] = a.lut[(size_t)row0 * kM * kC + i];
-      __syncthreads();
-      // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g].  Consecutive
-      // threads write consecutive GP-float vectors (conflict-free stores); an entry is
-      // recomputed for each of its replicas, which is cheaper than a strided store.
-      for (int i = tid; i < 4 * 256 * PS::REP; i += kScanThreads) {
-        const int e = i / PS::REP;  // p * 256 + byte
-        float v[GP];
+        for (int pass = 0; pass < PS::NP; ++pass) {
+          const int row0 = s * G + pass * GP;  // first query row of this pass
+          __syncthreads();                     // tables, list scores and headers of the previous pass are done with
+          for (int i = tid; i < GP * kM * kC; i += T)
+            lut_s[i / (kM * kC)][i % (kM * kC)] = a.lut[(size_t)row0 * kM * kC + i];
+          for (int i = tid; i < GP * kLMax; i += T)  // [g][l] in global memory -> [l][g] here
+            lsc_s[(i % kLMax) * GP + i / kLMax] = a.list_scores[(size_t)row0 * kLMax + i];
+          __syncthreads();
+          // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g].  Consecutive
+          // threads write consecutive GP-float vectors (conflict-free stores); an entry is
+          // recomputed for each of its replicas, which is cheaper than a strided store.
+          for (int i = tid; i < 4 * 256 * PS::REP; i += T) {
+            const int e = i / PS::REP;  // p * 256 + byte
+            float v[GP];
 #pragma unroll
-        for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], e >> 8, (uint32_t)(e & 255));
-        float* dst = tab + (size_t)i * GP;
-        if constexpr (GP == 4) {
-          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-        } else if constexpr (GP == 2) {
-          *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
-        } else {
-          dst[0] = v[0];
-        }
-      }
-      __syncthreads();
+            for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], e >> 8, (uint32_t)(e & 255));
+            float* dst = tab + (size_t)i * GP;
+            if constexpr (GP == 4) {
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            } else if constexpr (GP == 2) {
+              *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+            } else {
+              dst[0] = v[0];
+            }
+          }
 
-      float tau[GP];
+          float tau[GP];
 #pragma unroll
-      for (int g = 0; g < GP; ++g) tau[g] = a.row_tau[row0 + g];
-      const float* lsc = a.list_scores + (size_t)row0 * kLMax;
-      const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
-      int pc = 0;         // this lane's staged candidates
-      uint32_t tagw = 0;  // their rows, 2 bits each
+          for (int g = 0; g < GP; ++g) tau[g] = a.row_tau[row0 + g];
+          const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
+          int pc = 0;         // this lane's staged candidates
+          uint32_t tagw = 0;  // their rows, 2 bits each
 
-      for (int u = u0 + warp; u < u1; u += kScanWarps) {
-        if (u < n_units) {
-          const int lo = uoff[u], hi = uoff[u + 1];
-          const int l = ulist[u];
-          uint32_t code[kIter];
-          float kn[kIter];
-#pragma unroll
-          for (int it = 0; it < kIter; ++it) {
-            const int slot = lo + it * 32 + lane;
-            code[it] = 0u;
-            kn[it] = 0.f;
-            if (slot < hi) {
-              code[it] = __ldg(codes + slot);
-              kn[it] = to_f(norms[slot]);
+          for (int h0 = u0; h0 < u1; h0 += kHdr) {
+            const int cnt = min(kHdr, u1 - h0);
+            __syncthreads();  // tables complete; the previous header chunk is done with
+            for (int i = tid; i < cnt; i += T) {
+              const int u = (int)(((long long)(h0 + i) * stride) % u_tot);  // position in the share -> unit
+              const int lo = unit_first(u);
+              hdr[i] = make_int4(lo, unit_first(u + 1) - lo, u < n_units ? (int)ulist[u] : 0xFFFF, u);
             }
-          }
-          float ls[GP];
+            __syncthreads();
+
+            // a warp's units: i = warp, warp + W, ...; the codes and norms of the next one are
+            // requested before the current one is scored
+            uint32_t code[kIter], code_n[kIter];
+            E kn[kIter], kn_n[kIter];
+            int4 cur = make_int4(0, 0, 0, 0), nxt = make_int4(0, 0, 0, 0);  // (first slot, slots, list, unit)
+            auto fetch = [&](int i, int4& r, uint32_t (&c)[kIter], E (&k)[kIter]) {
+              r = hdr[i];
+              const uint32_t* cp = codes + r.x + lane;
+              const E* np = norms + r.x + lane;
 #pragma unroll
-          for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
-          float xs[kIter][GP];
-#pragma unroll
-          for (int it = 0; it < kIter; ++it) {
-            const int slot = lo + it * 32 + lane;
-            const bool valid = slot < hi;
-            score_key<GP>(mytab, code[it], ls, kn[it], xs[it]);
-#pragma unroll
-            for (int g = 0; g < GP; ++g) {
-              xs[it][g] = valid ? xs[it][g] : kNegInf;
-              if (valid && xs[it][g] >= tau[g]) {
-                wst[pc * 32 + lane] = make_int2(slot, __float_as_int(xs[it][g]));
-                tagw |= (uint32_t)g << (2 * pc);
-                ++pc;
-              }
-            }
-            if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
-              flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
-              pc = 0;
-              tagw = 0u;
-            }
-          }
-          // unit statistics: max per row (one redux each), then the sum against that max
-          float sm[GP], mg[GP];
-#pragma unroll
-          for (int g = 0; g < GP; ++g) {
-            float mx = xs[0][g];
-#pragma unroll
-            for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
-            mg[g] = redux_max(mx);
-            sm[g] = 0.f;
-#pragma unroll
-            for (int it = 0; it < kIter; ++it) sm[g] += unit_term(xs[it][g], mg[g]);  // -inf contributes 0
-          }
-          const float sred = warp_sum_multi<GP>(sm, lane);
-          if ((lane & (32 / GP - 1)) == 0) {
-            const int g = lane / (32 / GP);
-            float mine = mg[0];
-#pragma unroll
-            for (int gg = 1; gg < GP; ++gg)
-              if (gg == g) mine = mg[gg];
-            a.unit_max[(size_t)(row0 + g) * a.ucap + u] = mine;
-            a.unit_sum[(size_t)(row0 + g) * a.ucap + u] = sred;
-          }
-        } else {
-          // a chunk of the unsorted tail: every slot has its own list; logits are kept one by one
-          const int t0 = (u - n_units) * kUnit, t1 = min(t0 + kUnit, n_tail);
-          for (int t = t0 + lane; t - lane < t1; t += 32) {
-            const bool valid = t < t1;
-            const int slot = n_sorted + (valid ? t : t0);
-            const uint32_t code = __ldg(codes + slot);
-            const float knv = to_f(norms[slot]);
-            const int l = lids[slot];
-            float ls[GP], x[GP];
-#pragma unroll
-            for (int g = 0; g < GP; ++g) ls[g] = __ldg(lsc + g * kLMax + l);
-            score_key<GP>(mytab, code, ls, knv, x);
-#pragma unroll
-            for (int g = 0; g < GP; ++g) {
-              if (valid) {
-                a.tail_logit[(size_t)(row0 + g) * a.tail_cap + t] = x[g];
-                if (x[g] >= tau[g]) {
-                  wst[pc * 32 + lane] = make_int2(slot, __float_as_int(x[g]));
-                  tagw |= (uint32_t)g << (2 * pc);
-                  ++pc;
+              for (int it = 0; it < kIter; ++it) {
+                c[it] = 0u;
+                k[it] = E(0.f);
+                if (it * 32 + lane < r.y) {
+                  c[it] = __ldg(cp + it * 32);
+                  k[it] = np[it * 32];
                 }
               }
-            }
-            if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
-              flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
-              pc = 0;
-              tagw = 0u;
+            };
+            int i = warp;
+            if (i < cnt) fetch(i, cur, code, kn);
+            for (; i < cnt; i += W) {
+              if (i + W < cnt) fetch(i + W, nxt, code_n, kn_n);
+              const int lo = cur.x, n = cur.y, u = cur.w;
+              if (cur.z != 0xFFFF) {
+                float ls[GP];
+                if constexpr (GP == 4) {
+                  const float4 v = *reinterpret_cast<const float4*>(lsc_s + cur.z * 4);
+                  ls[0] = v.x; ls[1] = v.y; ls[2] = v.z; ls[3] = v.w;
+                } else if constexpr (GP == 2) {
+                  const float2 v = *reinterpret_cast<const float2*>(lsc_s + cur.z * 2);
+                  ls[0] = v.x; ls[1] = v.y;
+                } else {
+                  ls[0] = lsc_s[cur.z];
+                }
+                float xs[kIter][GP];
+#pragma unroll
+                for (int it = 0; it < kIter; ++it) {
+                  if ((it + 1) * 32 <= n) {  // warp-uniform: every lane has a key
+                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), xs[it]);
+                  } else if (it * 32 < n) {  // warp-uniform: the ragged end
+                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), xs[it]);
+                    if (it * 32 + lane >= n) {
+#pragma unroll
+                      for (int g = 0; g < GP; ++g) xs[it][g] = kNegInf;
+                    }
+                  } else {
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) xs[it][g] = kNegInf;
+                  }
+                }
+                // unit maximum per row (one redux each)
+                float mg[GP];
+#pragma unroll
+                for (int g = 0; g < GP; ++g) {
+                  float mx = xs[0][g];
+#pragma unroll
+                  for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
+                  mg[g] = redux_max(mx);
+                }
+                // candidates: only rows whose unit maximum reaches the threshold look at their keys
+#pragma unroll
+                for (int g = 0; g < GP; ++g) {
+                  if (mg[g] >= tau[g]) {  // warp-uniform
+#pragma unroll
+                    for (int it = 0; it < kIter; ++it) {
+                      if (xs[it][g] >= tau[g]) {
+                        wst[pc * 32 + lane] = make_int2(lo + it * 32 + lane, __float_as_int(xs[it][g]));
+                        tagw |= (uint32_t)g << (2 * pc);
+                        ++pc;
+                      }
+                    }
+                    if (__any_sync(0xffffffffu, pc > kLanePriv - kIter)) {
+                      flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit,
+                                             a.ccap);
+                      pc = 0;
+                      tagw = 0u;
+                    }
+                  }
+                }
+                // the sum of unit_term(logit, reference of the unit maximum); -inf contributes 0
+                float sm[GP];
+                if constexpr (GP >= 2) {
+#pragma unroll
+                  for (int g = 0; g < GP; g += 2) {
+                    const float2 ref = make_float2(unit_ref(mg[g]), unit_ref(mg[g + 1]));
+                    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int it = 0; it < kIter; ++it) {
+                      const float2 t =
+                          __ffma2_rn(make_float2(xs[it][g], xs[it][g + 1]), make_float2(kLog2e, kLog2e), ref);
+                      acc = __fadd2_rn(acc, make_float2(ex2(t.x), ex2(t.y)));
+                    }
+                    sm[g] = acc.x;
+                    sm[g + 1] = acc.y;
+                  }
+                } else {
+                  const float ref = unit_ref(mg[0]);
+                  sm[0] = 0.f;
+#pragma unroll
+                  for (int it = 0; it < kIter; ++it) sm[0] += unit_term(xs[it][0], ref);
+                }
+                const float sred = warp_sum_multi<GP>(sm, lane);
+                if ((lane & (32 / GP - 1)) == 0) {
+                  const int g = lane / (32 / GP);
+                  float mine = mg[0];
+#pragma unroll
+                  for (int gg = 1; gg < GP; ++gg)
+                    if (gg == g) mine = mg[gg];
+                  a.unit_max[(size_t)(row0 + g) * a.ucap + u] = mine;
+                  a.unit_sum[(size_t)(row0 + g) * a.ucap + u] = sred;
+                }
+              } else {
+                // a chunk of the unsorted tail: every slot has its own list; logits are kept one by one
+#pragma unroll
+                for (int it = 0; it < kIter; ++it) {
+                  if (it * 32 < n) {  // warp-uniform
+                    const bool valid = it * 32 + lane < n;
+                    const int slot = lo + (valid ? it * 32 + lane : 0);
+                    const int l = lids[slot];
+                    float ls[GP], x[GP];
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) ls[g] = lsc_s[l * GP + g];
+                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), x);
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) {
+                      if (valid) {
+                        a.tail_logit[(size_t)(row0 + g) * a.tail_cap + (slot - n_sorted)] = x[g];
+                        if (x[g] >= tau[g]) {
+                          wst[pc * 32 + lane] = make_int2(slot, __float_as_int(x[g]));
+                          tagw |= (uint32_t)g << (2 * pc);
+                          ++pc;
+                        }
+                      }
+                    }
+                    if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
+                      flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit,
+                                             a.ccap);
+                      pc = 0;
+                      tagw = 0u;
+                    }
+                  }
+                }
+              }
+              cur = nxt;
+#pragma unroll
+              for (int it = 0; it < kIter; ++it) {
+                code[it] = code_n[it];
+                kn[it] = kn_n[it];
+              }
             }
           }
+          if (__any_sync(0xffffffffu, pc > 0))
+            flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
         }
       }
-      if (__any_sync(0xffffffffu, pc > 0))
-        flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
     }
+    carry += ctot;
   }
 }
 
@@ -384,18 +509,19 @@ __global__ void __launch_bounds__(256) scan_dump_kernel(const ScanArgs a) {
   }
 }
 
-template <typename E, int G>
+template <typename E, int G, int T>
 static int launch_scan_t(const pqhsa_params& p, const ScanArgs& a, cudaStream_t st) {
   using PS = PairShape<G>;
-  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kScanWarps * kLanePriv * 32 * sizeof(int2);
-  auto kern = scan_kernel<E, G>;
+  const size_t smem = PS::kFloats * sizeof(float) + (size_t)(T / 32) * kLanePriv * 32 * sizeof(int2) +
+                      (size_t)kLMax * PS::GP * sizeof(float) + (size_t)kHdr * sizeof(int4);
+  auto kern = scan_kernel<E, G, T>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return check_launch("scan: shared memory opt-in");
   const long long units_hi = (long long)p.num_streams * (p.num_lists + p.max_slots / kUnit + 2);
   long long ctas = sm_count();
   if (ctas > units_hi) ctas = units_hi;
   if (ctas < 1) ctas = 1;
-  kern<<<(unsigned)ctas, kScanThreads, smem, st>>>(a);
+  kern<<<(unsigned)ctas, T, smem, st>>>(a);
   return check_launch("scan");
 }
 
@@ -431,7 +557,7 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
     PQHSA_DISPATCH_E(p.dtype, scan_dump_kernel<E><<<grid, 256, smem, st>>>(a));
     return check_launch("scan_dump");
   }
-  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G>(p, a, st))));
+  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_scan_t<E, G, kScanThreads>(p, a, st))));
   return PQHSA_OK;
 }
 

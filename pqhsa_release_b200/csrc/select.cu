@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
       if (!ok[j]) continue;
       soff[base + j * kFinThreads + tid] = a.kv.offset(req, head, pos[j]);
       if (slot[j] < n_sorted)
-        atomicAdd(a.unit_sum + (size_t)row * a.ucap + u[j], -unit_term(x[j], um[j]));
+        atomicAdd(a.unit_sum + (size_t)row * a.ucap + u[j], -unit_term(x[j], unit_ref(um[j])));
       else
         a.tail_logit[(size_t)row * a.tail_cap + (slot[j] - n_sorted)] = kNegInf;
     }

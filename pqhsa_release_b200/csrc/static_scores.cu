@@ -85,6 +85,6 @@ extern "C" int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, vo
   w.row_tau = kOffRowTau;
   w.ticket = kOffTicket;
   w.row_info = kOffRowInfo;
-  if (int rc = launch_lut_build(q, w, st)) return rc;
+  if (int rc = launch_lut_build(q, w, nullptr, st)) return rc;
   return launch_scan(q, w, scores, st);
 }

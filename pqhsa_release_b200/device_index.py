@@ -134,6 +134,8 @@ class DeviceIndexPool:
         self.vsum = torch.zeros(S, L, D, dtype=torch.float32, device=dev)
         self.vcnt = torch.zeros(S, L, dtype=torch.int32, device=dev)
         self.state = torch.zeros(S, _lib.STATE_INTS, dtype=torch.int32, device=dev)
+        # contiguous copy of the slots the threshold estimate samples: (code, norm bits, list, slot)
+        self.sample = torch.zeros(S, _lib.SAMPLE_KEYS, 4, dtype=torch.int32, device=dev)
         # host mirrors of the device counters (every update is deterministic)
         self.h_sorted = np.zeros(S, dtype=np.int64)
         self.h_tail = np.zeros(S, dtype=np.int64)
@@ -154,7 +156,7 @@ class DeviceIndexPool:
         p.hist_inv_width = 0.0 if hist_width is None else float(1.0 / hist_width)
         p.select_margin = float(select_margin)
         for name in ("codes", "norms", "list_ids", "slot_pos", "slot_unit", "unit_off", "unit_list", "coarse",
-                     "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max"):
+                     "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max", "sample"):
             setattr(p, name, getattr(self, name).data_ptr())
         self.p = p
         self.layout = WsLayout()
@@ -207,6 +209,20 @@ class DeviceIndexPool:
             st[_lib.ST_N_SORTED], st[_lib.ST_N_UNITS], st[_lib.ST_N_LISTS] = n, u, lists
         self.state[s] = st.to(dev)
         self.h_sorted[s], self.h_tail[s], self.h_seq[s] = n, 0, seq_len
+        self._refresh_sample(s, n)
+
+    def _refresh_sample(self, s: int, n_sorted: int) -> None:
+        """Copy the slots floor(i * n_sorted / 4096), i < 4096, of the sorted region of stream ``s``
+        into the sample array (streams with at most 4096 sorted slots are never sampled)."""
+        ns = _lib.SAMPLE_KEYS
+        if n_sorted <= ns:
+            return
+        j = (torch.arange(ns, device=self.device, dtype=torch.int64) * n_sorted) // ns
+        rec = self.sample[s]
+        rec[:, 0] = self.codes[s][j]
+        rec[:, 1] = self.norms[s][j].float().view(torch.int32)
+        rec[:, 2] = self.list_ids[s][j].to(torch.int32) & 0xFFFF
+        rec[:, 3] = j.to(torch.int32)
 
     def export_stream(self, s: int) -> dict[str, torch.Tensor]:
         """Slots of stream ``s`` back in token order (for tests and state dicts)."""
@@ -339,6 +355,29 @@ class DeviceIndexPool:
         _lib.call("pqhsa_scan_scores", C.byref(self.p), scores.data_ptr(), self._stream())
         return scores
 
+    def decode_step_append(self, q: torch.Tensor, new_k: torch.Tensor | None, new_v: torch.Tensor | None,
+                           encode: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """append_kv(new_k, new_v) + append_encode(encode) + decode_step(q) as one call of five
+        launches (the first kernel does the append, the encode and the tables side by side)."""
+        if (new_k is None) != (new_v is None):
+            raise ValueError("new_k and new_v go together")
+        for t in (new_k, new_v):
+            if t is not None and (t.dtype != self.dtype or not t.is_contiguous() or t.numel() != self.S * _lib.HEAD_DIM):
+                raise ValueError(f"new_k/new_v must be contiguous {self.dtype} tensors of {self.S}x128 elements")
+        encode = int(encode)
+        if encode:
+            if int((self.h_tail + encode).max()) > self.tail_capacity:
+                raise RuntimeError("tail capacity exhausted: compact() the pool first")
+            self.h_tail += encode
+        if new_k is not None:
+            self.h_seq += 1
+        if out is None:
+            out = torch.empty_like(q)
+        self._prep(q, out)
+        _lib.call("pqhsa_decode_step_append", C.byref(self.p), new_k.data_ptr() if new_k is not None else None,
+                  new_v.data_ptr() if new_v is not None else None, None, encode, self._stream())
+        return out
+
     def append_kv(self, new_k: torch.Tensor, new_v: torch.Tensor) -> None:
         """Write one K/V row per stream at its current length and advance it."""
         for t in (new_k, new_v):
@@ -406,6 +445,7 @@ class DeviceIndexPool:
             self.state[s, _lib.ST_N_TAIL] = 0
             self.state[s, _lib.ST_N_UNITS] = u
             self.h_sorted[s], self.h_tail[s] = n, 0
+            self._refresh_sample(s, n)
 
     # ---- workspace views (after a synchronise) ----------------------------
     def ws_view(self, name: str) -> torch.Tensor:

@@ -159,3 +159,34 @@ def test_standalone_topk_radix_against_torch_topk():
             tied = torch.nonzero(x[r] == kth).flatten()
             chosen = sorted(i for i in got.tolist() if x[r, i] == kth)
             assert chosen == tied[: len(chosen)].tolist()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_step_equals_the_three_calls(dtype):
+    """pqhsa_decode_step_append (append, encode and tables in one kernel) leaves the same index,
+    counters and cache rows as append_kv + append_encode + decode_step, and the same output."""
+    case = make_case(B=2, Hkv=2, G=4, S=5000, L=96, dtype=dtype, seed=21, interval=1, strategy="incremental")
+    a, ka, va = pool_from_case(case)
+    b, kb, vb = pool_from_case(case)
+    gen = torch.Generator().manual_seed(5)
+    q0 = case.queries.cuda().reshape(case.num_streams, case.G, 128).contiguous()
+    for step in range(3):
+        nk = torch.randn(case.num_streams, 128, generator=gen).to(dtype).cuda()
+        nv = torch.randn(case.num_streams, 128, generator=gen).to(dtype).cuda()
+        q = (q0.float() * (1 + 0.1 * step)).to(dtype).contiguous()
+        a.append_kv(nk, nv)
+        a.append_encode(1)
+        want = a.decode_step(q)
+        got = b.decode_step_append(q, nk, nv, encode=1)
+        torch.cuda.synchronize()
+        assert torch.equal(a.state, b.state)
+        n = int(a.h_sorted[0] + a.h_tail[0])
+        for name in ("codes", "norms", "list_ids", "slot_pos", "vmeans", "vsum", "vcnt", "norm_max"):
+            assert torch.equal(getattr(a, name), getattr(b, name)), name
+        assert torch.equal(ka, kb) and torch.equal(va, vb)
+        ia, ib = a.ws_view("row_info"), b.ws_view("row_info")
+        assert torch.equal(ia[:, :2], ib[:, :2]) and int(ib[:, 4].sum()) == 0
+        for row in range(case.num_streams * case.G):
+            assert torch.equal(a.selected_positions(row), b.selected_positions(row))
+        assert float((got.float() - want.float()).abs().max()) <= 2e-3 * float(want.float().abs().max())
+        assert n == 5000 - 4 - 128 + step + 1
