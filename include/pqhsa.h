@@ -145,6 +145,7 @@ typedef struct pqhsa_ws_layout {
   size_t total_bytes;
   size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>                 */
   size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>                    */
+  size_t pair_tab;     /* float  [S, G/GP, 4, 256, GP], GP = min(G, 4): byte-pair sums of lut for the scan */
   size_t row_bin;      /* float  [R, 2]   sample histogram origin and 1 / bin width       */
   size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
   size_t ticket;       /* int32  [S]      arrival counter of the table kernel's CTAs       */
@@ -152,13 +153,11 @@ typedef struct pqhsa_ws_layout {
   size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max), selected keys removed */
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */
   size_t row_info;     /* int32  [R, 8]   see enum pqhsa_row_info_slot                     */
-  size_t cand_slot;    /* int32  [R, ccap]  slots whose logit reached the threshold        */
-  size_t cand_logit;   /* float  [R, ccap]  their logits                                   */
+  size_t hitmap;       /* uint32 [R, unit_capacity, 4]  bit b of word (u, i): slot first(u) + 32 i + b reached the threshold */
   size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */
   size_t sel_off;      /* int64  [R, kcap]  element offset of their K/V rows in the cache  */
   size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)        */
   int32_t kcap;        /* row stride of sel_* */
-  int32_t ccap;        /* row stride of cand_* */
   int32_t tail_cap;    /* row stride of tail_logit */
   int32_t chunks;      /* split-K partials per row */
 } pqhsa_ws_layout;
@@ -166,7 +165,7 @@ typedef struct pqhsa_ws_layout {
 enum pqhsa_row_info_slot {
   PQHSA_RI_K = 0,        /* keys to select                                              */
   PQHSA_RI_N = 1,        /* indexed keys of the stream                                  */
-  PQHSA_RI_NCAND = 2,    /* candidates found by the scan (may exceed ccap: overflow)    */
+  PQHSA_RI_NCAND = 2,    /* keys whose logit reached the candidate threshold            */
   PQHSA_RI_NSEL = 3,     /* keys selected (== K after the finish kernel)                */
   PQHSA_RI_FALLBACK = 4, /* 1 if the finish kernel had to select from all keys          */
   PQHSA_RI_INTS = 8

@@ -47,11 +47,12 @@ class WsLayout(C.Structure):
     """``pqhsa_ws_layout`` of include/pqhsa.h."""
 
     _fields_ = [
-        ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("row_bin", C.c_size_t),
+        ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("pair_tab", C.c_size_t),
+        ("row_bin", C.c_size_t),
         ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
-        ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("cand_slot", C.c_size_t),
-        ("cand_logit", C.c_size_t), ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t),
-        ("kcap", C.c_int32), ("ccap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
+        ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
+        ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t),
+        ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]
 
 

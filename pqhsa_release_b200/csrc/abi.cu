@@ -51,10 +51,6 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   const size_t S = (size_t)p->num_streams, G = (size_t)p->group, R = S * G;
   const size_t cap = (size_t)p->slot_capacity;
   o->kcap = topk_capacity(p);
-  // candidates: a few times K is the normal case, the whole stream when the context is short
-  size_t cc = 4 * (size_t)o->kcap + 2 * kSample;
-  if (cc > cap) cc = cap;
-  o->ccap = (int32_t)align_up(cc, 8);
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
   size_t off = 0;
@@ -65,6 +61,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   };
   o->lut = take(S * G * kM * kC * sizeof(float));
   o->list_scores = take(S * G * kLMax * sizeof(float));
+  o->pair_tab = take(S * G * 1024 * sizeof(float));
   o->row_bin = take(R * 2 * sizeof(float));
   o->row_tau = take(R * sizeof(float));
   o->ticket = take(S * sizeof(int32_t));
@@ -72,8 +69,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->unit_sum = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
   o->row_info = take(R * kRI * sizeof(int32_t));
-  o->cand_slot = take(R * (size_t)o->ccap * sizeof(int32_t));
-  o->cand_logit = take(R * (size_t)o->ccap * sizeof(float));
+  o->hitmap = take(R * (size_t)p->unit_capacity * (kUnit / 32) * sizeof(uint32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
   o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
   o->partial = take(R * (size_t)o->chunks * kPartial * sizeof(float));
@@ -93,6 +89,7 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
     return set_error(PQHSA_E_SHAPE, "num_lists must be in 1..%d, got %d", kLMax, p->num_lists);
   if (p->slot_capacity <= 0 || p->slot_capacity % 8 != 0)
     return set_error(PQHSA_E_SHAPE, "slot_capacity must be a positive multiple of 8, got %d", p->slot_capacity);
+  if (p->slot_capacity > (1 << 22)) return set_error(PQHSA_E_SHAPE, "slot_capacity %d exceeds %d", p->slot_capacity, 1 << 22);
   if (p->unit_capacity < p->num_lists + p->slot_capacity / kUnit)
     return set_error(PQHSA_E_SHAPE, "unit_capacity %d < num_lists + slot_capacity/%d", p->unit_capacity, kUnit);
   if (p->unit_capacity > 65535) return set_error(PQHSA_E_SHAPE, "unit_capacity %d does not fit 16 bits", p->unit_capacity);

@@ -190,6 +190,10 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+__device__ __forceinline__ float key_float(uint32_t k) {  // inverse of float_key
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
 // K = min(max(ceil(N * fraction), 0), N) in double precision
 // (pq_hsa/attention/sparse_attention.py:1779-1783); fraction < 0 selects the fixed count.
 __device__ __forceinline__ int resolve_topk(int n, double fraction, int fixed) {

@@ -41,6 +41,7 @@ struct LutArgs {
   const uint16_t* list_ids;
   const int4* sample;  // [S, kSample] (code, norm as float bits, list, slot) of the stratified sample, or null
   float* lut;
+  float* pair_tab;  // [S, G / GP, 4, 256, GP] byte-pair sums of the tables for the scan, GP = min(G, 4); or null
   float* list_scores;
   int32_t* row_info;
   float* row_bin;
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
 #pragma unroll
         for (int d = 0; d < kSub; ++d) acc = fmaf(qs[g][m * kSub + d], w[d], acc);
         a.lut[((size_t)s * G + g) * kM * kC + tid] = acc;
+        lut_s[g][tid] = acc;
         float mx = fabsf(acc);  // max over the 16 code words of this subspace (16 consecutive lanes)
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -128,6 +130,16 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
       }
     }
     __syncthreads();
+    if (a.pair_tab != nullptr) {
+      // the scan looks codes up a byte (two subspaces) at a time: entry (p, byte) = lut[2p][byte & 15] + lut[2p+1][byte >> 4]
+      constexpr int GP = G < 4 ? G : 4;
+      float* dst = a.pair_tab + (size_t)s * G * 1024;
+      for (int i = tid; i < G * 1024; i += kLutThreads) {
+        const int pass = i / (1024 * GP), rem = i % (1024 * GP);
+        const int e = rem / GP, g = rem % GP;
+        dst[i] = pair_entry(lut_s[pass * GP + g], e >> 8, (uint32_t)(e & 255));
+      }
+    }
     if (tid < G) {
       // |logit| <= (scale |q| max_l |c_l| + sum_m max_c |lut[m][c]|) * max |k|, |c_l| <= 1: the part
       // that does not depend on the norms is parked here; the last CTA multiplies max |k| in
@@ -325,6 +337,7 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.norms = p.norms;
   a.list_ids = static_cast<const uint16_t*>(p.list_ids);
   a.lut = reinterpret_cast<float*>(ws + w.lut);
+  a.pair_tab = w.pair_tab == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.pair_tab);
   a.list_scores = reinterpret_cast<float*>(ws + w.list_scores);
   a.row_info = reinterpret_cast<int32_t*>(ws + w.row_info);
   a.row_bin = reinterpret_cast<float*>(ws + w.row_bin);

@@ -44,8 +44,7 @@
 
 namespace pqhsa {
 
-constexpr int kScanThreads = 512;  // 16 warps with 128 registers each: a unit in flight and one being scored
-constexpr int kLanePriv = 8;       // lane-private staged candidates
+constexpr int kScanThreads = 1024;  // 32 warps of 64 registers: the loop is issue-bound and needs the warps
 constexpr int kHdr = 512;     // unit headers staged in shared memory at a time
 constexpr int kIter = kUnit / 32;
 
@@ -64,16 +63,15 @@ struct ScanArgs {
   const uint16_t* unit_list;
   const int32_t* state;
   const float* lut;
+  const float* pair_tab;
   const float* list_scores;
   const float* row_tau;
-  int32_t* row_info;
-  int32_t* cand_slot;
-  float* cand_logit;
+  uint32_t* hitmap;
   float* unit_max;
   float* unit_sum;
   float* tail_logit;
   float* dump;
-  int S, G, cap, ucap, tail_cap, ccap;
+  int S, G, cap, ucap, tail_cap;
 };
 
 __device__ __forceinline__ float redux_max(float v) {
@@ -148,67 +146,40 @@ __device__ __forceinline__ void score_key(const float* __restrict__ mytab, uint3
   }
 }
 
-// Warp-collective: write every lane's privately staged candidates to the rows'
-// candidate lists (one atomic per row), lane `l` owning entries wst[e * 32 + l].
-template <int GP>
-__device__ __noinline__ void flush_lane_buffers(const int2* wst, int pc, uint32_t tagw, int lane, int row0,
-                                                int32_t* row_info, int32_t* cand_slot, float* cand_logit,
-                                                int ccap) {
-  int c[GP], nxt[GP];
-#pragma unroll
-  for (int g = 0; g < GP; ++g) c[g] = 0;
-#pragma unroll
-  for (int e = 0; e < kLanePriv; ++e) {
-    const int tg = (tagw >> (2 * e)) & 3u;
-#pragma unroll
-    for (int g = 0; g < GP; ++g) c[g] += (e < pc && tg == g) ? 1 : 0;
-  }
-#pragma unroll
-  for (int g = 0; g < GP; ++g) {
-    int incl = c[g];
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    const int tot = __shfl_sync(0xffffffffu, incl, 31);
-    int b = 0;
-    if (lane == 0 && tot > 0) b = atomicAdd(row_info + (size_t)(row0 + g) * kRI + PQHSA_RI_NCAND, tot);
-    nxt[g] = __shfl_sync(0xffffffffu, b, 0) + incl - c[g];
-  }
-#pragma unroll
-  for (int e = 0; e < kLanePriv; ++e) {
-    if (e < pc) {
-      const int tg = (tagw >> (2 * e)) & 3u;
-      const int2 v = wst[e * 32 + lane];
-      int o = 0;
-#pragma unroll
-      for (int g = 0; g < GP; ++g)
-        if (tg == g) o = nxt[g]++;
-      if (o < ccap) {
-        cand_slot[(size_t)(row0 + tg) * ccap + o] = v.x;
-        cand_logit[(size_t)(row0 + tg) * ccap + o] = __int_as_float(v.y);
-      }
-    }
-  }
+// 16-byte asynchronous copy global -> shared (L2 only) and its group bookkeeping
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+               : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename E> struct ScanRing {
+  static constexpr int kCodeBytes = (kUnit / 4 + 1) * 16;                                  // 128 codes + alignment slack
+  static constexpr int kNormBytes = (kUnit * (int)sizeof(E) / 16 + 1) * 16;                // 128 norms + slack
+  static constexpr int kStageBytes = kCodeBytes + kNormBytes;
+  static constexpr int kDepth = 2;  // units per warp in the ring: one being scored, one in flight
+};
 
 template <typename E, int G, int T>
 __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
   using PS = PairShape<G>;
+  using RG = ScanRing<E>;
   constexpr int GP = PS::GP;
   constexpr int W = T / 32;
+  constexpr int D = RG::kDepth;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* tab = reinterpret_cast<float*>(smem_raw);                        // pair tables
-  int2* stage = reinterpret_cast<int2*>(tab + PS::kFloats);               // [W][kLanePriv][32] (slot, logit bits)
-  float* lsc_s = reinterpret_cast<float*>(stage + W * kLanePriv * 32);    // [kLMax][GP] list scores of the pass
-  int4* hdr = reinterpret_cast<int4*>(lsc_s + kLMax * GP);                // [kHdr] staged units (first slot, slots, list, unit)
-  __shared__ float lut_s[GP][kM * kC];
+  float* tab = reinterpret_cast<float*>(smem_raw);                              // pair tables, replicated
+  float* lsc_s = tab + PS::kFloats;                                             // [kLMax][GP] list scores of the pass
+  int4* hdr = reinterpret_cast<int4*>(lsc_s + kLMax * GP);                      // [kHdr] (first slot, slots, list, unit)
+  unsigned char* ring = reinterpret_cast<unsigned char*>(hdr + kHdr);           // [W][D] codes + norms of units in flight
   __shared__ long long s_red[32];
   __shared__ int s_pref[T], s_ut[T], s_first;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int2* wst = stage + (size_t)warp * kLanePriv * 32;
+  unsigned char* wring = ring + (size_t)warp * D * RG::kStageBytes;
 
   auto units_of = [&](int s) -> int {
     const int32_t* st = a.state + (size_t)s * kST;
@@ -286,70 +257,70 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
         for (int pass = 0; pass < PS::NP; ++pass) {
           const int row0 = s * G + pass * GP;  // first query row of this pass
           __syncthreads();                     // tables, list scores and headers of the previous pass are done with
-          for (int i = tid; i < GP * kM * kC; i += T)
-            lut_s[i / (kM * kC)][i % (kM * kC)] = a.lut[(size_t)row0 * kM * kC + i];
           for (int i = tid; i < GP * kLMax; i += T)  // [g][l] in global memory -> [l][g] here
             lsc_s[(i % kLMax) * GP + i / kLMax] = a.list_scores[(size_t)row0 * kLMax + i];
-          __syncthreads();
-          // pair tables, replicated: tab[((p * 256 + byte) * REP + rep) * GP + g].  Consecutive
-          // threads write consecutive GP-float vectors (conflict-free stores); an entry is
-          // recomputed for each of its replicas, which is cheaper than a strided store.
-          for (int i = tid; i < 4 * 256 * PS::REP; i += T) {
-            const int e = i / PS::REP;  // p * 256 + byte
-            float v[GP];
-#pragma unroll
-            for (int g = 0; g < GP; ++g) v[g] = pair_entry(lut_s[g], e >> 8, (uint32_t)(e & 255));
-            float* dst = tab + (size_t)i * GP;
-            if constexpr (GP == 4) {
-              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-            } else if constexpr (GP == 2) {
-              *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
-            } else {
-              dst[0] = v[0];
+          // Pair tables of the pass (made by the table kernel), replicated:
+          // tab[((p * 256 + byte) * REP + rep) * GP + g].  Consecutive threads write consecutive
+          // GP-float vectors (conflict-free stores); the REP threads of an entry read the same vector.
+          {
+            const float* src = a.pair_tab + (size_t)(s * PS::NP + pass) * (4 * 256 * GP);
+#pragma unroll 4
+            for (int i = tid; i < 4 * 256 * PS::REP; i += T) {
+              const int e = i / PS::REP;
+              if constexpr (GP == 4) {
+                reinterpret_cast<float4*>(tab)[i] = __ldg(reinterpret_cast<const float4*>(src) + e);
+              } else if constexpr (GP == 2) {
+                reinterpret_cast<float2*>(tab)[i] = __ldg(reinterpret_cast<const float2*>(src) + e);
+              } else {
+                tab[i] = __ldg(src + e);
+              }
             }
           }
-
           float tau[GP];
 #pragma unroll
           for (int g = 0; g < GP; ++g) tau[g] = a.row_tau[row0 + g];
           const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
-          int pc = 0;         // this lane's staged candidates
-          uint32_t tagw = 0;  // their rows, 2 bits each
 
           for (int h0 = u0; h0 < u1; h0 += kHdr) {
             const int cnt = min(kHdr, u1 - h0);
-            __syncthreads();  // tables complete; the previous header chunk is done with
+            __syncthreads();  // the previous header chunk is done with
             for (int i = tid; i < cnt; i += T) {
               const int u = (int)(((long long)(h0 + i) * stride) % u_tot);  // position in the share -> unit
               const int lo = unit_first(u);
               hdr[i] = make_int4(lo, unit_first(u + 1) - lo, u < n_units ? (int)ulist[u] : 0xFFFF, u);
             }
-            __syncthreads();
+            __syncthreads();  // headers, tables and list scores are in place
 
-            // a warp's units: i = warp, warp + W, ...; the codes and norms of the next one are
-            // requested before the current one is scored
-            uint32_t code[kIter], code_n[kIter];
-            E kn[kIter], kn_n[kIter];
-            int4 cur = make_int4(0, 0, 0, 0), nxt = make_int4(0, 0, 0, 0);  // (first slot, slots, list, unit)
-            auto fetch = [&](int i, int4& r, uint32_t (&c)[kIter], E (&k)[kIter]) {
-              r = hdr[i];
-              const uint32_t* cp = codes + r.x + lane;
-              const E* np = norms + r.x + lane;
-#pragma unroll
-              for (int it = 0; it < kIter; ++it) {
-                c[it] = 0u;
-                k[it] = E(0.f);
-                if (it * 32 + lane < r.y) {
-                  c[it] = __ldg(cp + it * 32);
-                  k[it] = np[it * 32];
-                }
+            // A warp's units: i = warp, warp + W, ...  Their codes and norms travel through a ring of D
+            // stages per warp, filled by 16-byte asynchronous copies issued D - 1 units ahead; a copy
+            // starts at the 16-byte boundary below the unit's first element.
+            auto request = [&](int i) {
+              if (i < cnt) {
+                const int4 h = hdr[i];
+                unsigned char* stg = wring + (size_t)((i / W) % D) * RG::kStageBytes;
+                const int c0 = h.x & ~3;                                  // codes: 4 per 16 bytes
+                const int cch = (h.x + h.y - c0 + 3) >> 2;                // at most 33 chunks
+                if (lane < cch) cp_async16(stg + lane * 16, codes + c0 + lane * 4);
+                if (lane == 0 && cch > 32) cp_async16(stg + 32 * 16, codes + c0 + 32 * 4);
+                constexpr int kPer = 16 / (int)sizeof(E);                 // norms per 16 bytes
+                const int n0 = h.x & ~(kPer - 1);
+                const int nch = (h.x + h.y - n0 + kPer - 1) / kPer;
+                if (lane < nch) cp_async16(stg + RG::kCodeBytes + lane * 16, norms + n0 + lane * kPer);
+                if (lane == 0 && nch > 32) cp_async16(stg + RG::kCodeBytes + 32 * 16, norms + n0 + 32 * kPer);
               }
+              cp_async_commit();  // one group per request, empty or not: the wait below counts groups
             };
-            int i = warp;
-            if (i < cnt) fetch(i, cur, code, kn);
-            for (; i < cnt; i += W) {
-              if (i + W < cnt) fetch(i + W, nxt, code_n, kn_n);
+#pragma unroll
+            for (int d = 0; d < D - 1; ++d) request(warp + d * W);
+            for (int i = warp; i < cnt; i += W) {
+              request(i + (D - 1) * W);
+              cp_async_wait<D - 1>();
+              __syncwarp();
+              const int4 cur = hdr[i];
               const int lo = cur.x, n = cur.y, u = cur.w;
+              const unsigned char* stg = wring + (size_t)((i / W) % D) * RG::kStageBytes;
+              const uint32_t* cs = reinterpret_cast<const uint32_t*>(stg) + (lo & 3) + lane;
+              const E* ns = reinterpret_cast<const E*>(stg + RG::kCodeBytes) + (lo & (16 / (int)sizeof(E) - 1)) + lane;
               if (cur.z != 0xFFFF) {
                 float ls[GP];
                 if constexpr (GP == 4) {
@@ -365,9 +336,9 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
 #pragma unroll
                 for (int it = 0; it < kIter; ++it) {
                   if ((it + 1) * 32 <= n) {  // warp-uniform: every lane has a key
-                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), xs[it]);
-                  } else if (it * 32 < n) {  // warp-uniform: the ragged end
-                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), xs[it]);
+                    score_key<GP>(mytab, cs[it * 32], ls, to_f(ns[it * 32]), xs[it]);
+                  } else if (it * 32 < n) {  // warp-uniform: the ragged end (the ring holds stale bytes there)
+                    score_key<GP>(mytab, cs[it * 32], ls, to_f(ns[it * 32]), xs[it]);
                     if (it * 32 + lane >= n) {
 #pragma unroll
                       for (int g = 0; g < GP; ++g) xs[it][g] = kNegInf;
@@ -386,25 +357,16 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
                   for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
                   mg[g] = redux_max(mx);
                 }
-                // candidates: only rows whose unit maximum reaches the threshold look at their keys
+                // candidates: one vote per row and 32 slots; the 4 words of a row and unit are one 16-byte store
 #pragma unroll
                 for (int g = 0; g < GP; ++g) {
-                  if (mg[g] >= tau[g]) {  // warp-uniform
+                  unsigned m[kIter];
 #pragma unroll
-                    for (int it = 0; it < kIter; ++it) {
-                      if (xs[it][g] >= tau[g]) {
-                        wst[pc * 32 + lane] = make_int2(lo + it * 32 + lane, __float_as_int(xs[it][g]));
-                        tagw |= (uint32_t)g << (2 * pc);
-                        ++pc;
-                      }
-                    }
-                    if (__any_sync(0xffffffffu, pc > kLanePriv - kIter)) {
-                      flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit,
-                                             a.ccap);
-                      pc = 0;
-                      tagw = 0u;
-                    }
-                  }
+                  for (int it = 0; it < kIter; ++it)
+                    m[it] = __ballot_sync(0xffffffffu, it * 32 + lane < n && xs[it][g] >= tau[g]);
+                  if (lane == 0)
+                    *reinterpret_cast<uint4*>(a.hitmap + ((size_t)(row0 + g) * a.ucap + u) * kIter) =
+                        make_uint4(m[0], m[1], m[2], m[3]);
                 }
                 // the sum of unit_term(logit, reference of the unit maximum); -inf contributes 0
                 float sm[GP];
@@ -449,37 +411,22 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
                     float ls[GP], x[GP];
 #pragma unroll
                     for (int g = 0; g < GP; ++g) ls[g] = lsc_s[l * GP + g];
-                    score_key<GP>(mytab, code[it], ls, to_f(kn[it]), x);
+                    score_key<GP>(mytab, cs[it * 32], ls, to_f(ns[it * 32]), x);
 #pragma unroll
                     for (int g = 0; g < GP; ++g) {
-                      if (valid) {
-                        a.tail_logit[(size_t)(row0 + g) * a.tail_cap + (slot - n_sorted)] = x[g];
-                        if (x[g] >= tau[g]) {
-                          wst[pc * 32 + lane] = make_int2(slot, __float_as_int(x[g]));
-                          tagw |= (uint32_t)g << (2 * pc);
-                          ++pc;
-                        }
-                      }
+                      if (valid) a.tail_logit[(size_t)(row0 + g) * a.tail_cap + (slot - n_sorted)] = x[g];
+                      const unsigned m = __ballot_sync(0xffffffffu, valid && x[g] >= tau[g]);
+                      if (lane == 0) a.hitmap[((size_t)(row0 + g) * a.ucap + u) * kIter + it] = m;
                     }
-                    if (__any_sync(0xffffffffu, pc > kLanePriv - GP)) {
-                      flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit,
-                                             a.ccap);
-                      pc = 0;
-                      tagw = 0u;
-                    }
+                  } else if (lane < GP) {
+                    a.hitmap[((size_t)(row0 + lane) * a.ucap + u) * kIter + it] = 0u;
                   }
                 }
               }
-              cur = nxt;
-#pragma unroll
-              for (int it = 0; it < kIter; ++it) {
-                code[it] = code_n[it];
-                kn[it] = kn_n[it];
-              }
+              __syncwarp();  // every lane is done with this stage before a later request refills it
             }
+            cp_async_wait<0>();
           }
-          if (__any_sync(0xffffffffu, pc > 0))
-            flush_lane_buffers<GP>(wst, pc, tagw, lane, row0, a.row_info, a.cand_slot, a.cand_logit, a.ccap);
         }
       }
     }
@@ -512,8 +459,8 @@ __global__ void __launch_bounds__(256) scan_dump_kernel(const ScanArgs a) {
 template <typename E, int G, int T>
 static int launch_scan_t(const pqhsa_params& p, const ScanArgs& a, cudaStream_t st) {
   using PS = PairShape<G>;
-  const size_t smem = PS::kFloats * sizeof(float) + (size_t)(T / 32) * kLanePriv * 32 * sizeof(int2) +
-                      (size_t)kLMax * PS::GP * sizeof(float) + (size_t)kHdr * sizeof(int4);
+  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kLMax * PS::GP * sizeof(float) + (size_t)kHdr * sizeof(int4) +
+                      (size_t)(T / 32) * ScanRing<E>::kDepth * ScanRing<E>::kStageBytes;
   auto kern = scan_kernel<E, G, T>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return check_launch("scan: shared memory opt-in");
@@ -535,11 +482,10 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
   a.unit_list = static_cast<const uint16_t*>(p.unit_list);
   a.state = static_cast<const int32_t*>(p.state);
   a.lut = reinterpret_cast<const float*>(ws + w.lut);
+  a.pair_tab = reinterpret_cast<const float*>(ws + w.pair_tab);
   a.list_scores = reinterpret_cast<const float*>(ws + w.list_scores);
   a.row_tau = reinterpret_cast<const float*>(ws + w.row_tau);
-  a.row_info = reinterpret_cast<int32_t*>(ws + w.row_info);
-  a.cand_slot = reinterpret_cast<int32_t*>(ws + w.cand_slot);
-  a.cand_logit = reinterpret_cast<float*>(ws + w.cand_logit);
+  a.hitmap = reinterpret_cast<uint32_t*>(ws + w.hitmap);
   a.unit_max = reinterpret_cast<float*>(ws + w.unit_max);
   a.unit_sum = reinterpret_cast<float*>(ws + w.unit_sum);
   a.tail_logit = reinterpret_cast<float*>(ws + w.tail_logit);
@@ -549,7 +495,6 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
   a.cap = p.slot_capacity;
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
-  a.ccap = w.ccap;
   if (dump != nullptr) {
     if (p.max_slots == 0) return PQHSA_OK;
     const dim3 grid((p.max_slots + 255) / 256, p.num_streams);

@@ -3,13 +3,15 @@
 // benchmarks/e2e_pq_param_sweep.py:212-217, :6642; here the scores never
 // leave the chip except for the ~2K candidates per row).
 //
-// One CTA per query row.  The candidates are the keys whose approximate logit
-// reached the row's threshold; if at least K turned up (and the list did not
-// overflow) the K best of them ARE the K best of all N keys, and a block radix
-// select over their stored logits picks them by (logit desc, slot asc).
+// One CTA per query row.  The scan left one bit per (row, slot): the key's
+// approximate logit reached the row's threshold.  The CTA turns the set bits into
+// a candidate list in shared memory and scores the candidates again from their
+// codes (bit-identical to the scan, a few thousand gathers that hit the L2 the
+// scan just filled).  If at least K turned up, the K best of them ARE the K best
+// of all N keys, and a block radix select picks them by (logit desc, slot asc).
 // Otherwise - the threshold estimate was too high, probability ~1e-9 at the
-// default margin - the same select runs over all N slots, re-scoring them from
-// their codes (bit-identical to the scan): slow, exact, and flagged in row_info.
+// default margin - the same select runs over all N slots: slow, exact, and
+// flagged in row_info.
 //
 // For every selected key the kernel then
 //   * resolves the element offset of its K/V row in the (paged) cache, so the
@@ -26,61 +28,107 @@ namespace pqhsa {
 
 constexpr int kFinThreads = 1024;
 constexpr int kFinPer = 8;  // candidates per thread held in registers on the normal path
+constexpr int kCandCap = 16384;  // candidates listed in shared memory; more than that selects from all keys
+constexpr int kSlotBits = 22;    // a list entry is slot | list << 22
 
 struct FinishArgs {
   const uint32_t* codes;
   const void* norms;
   const uint16_t* list_ids;
   const uint16_t* slot_unit;
+  const int32_t* unit_off;
+  const uint16_t* unit_list;
   const int32_t* slot_pos;
   const int32_t* state;
   const float* lut;
   const float* list_scores;
   int32_t* row_info;
-  const int32_t* cand_slot;
-  const float* cand_logit;
+  const uint32_t* hitmap;
   int32_t* sel_slot;
   long long* sel_off;
   const float* unit_max;
   float* unit_sum;
   float* tail_logit;
   KvAddr kv;
-  int G, cap, ucap, tail_cap, kcap, ccap;
+  int G, cap, ucap, tail_cap, kcap;
 };
 
 template <typename E>
 __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a) {
+  extern __shared__ uint32_t cslot[];  // [kCandCap] candidates as slot | list << kSlotBits
   __shared__ float lut_s[kM * kC];
+  __shared__ float lsc_s[kLMax];
   __shared__ RadixShared rsh;
   __shared__ RadixShared2 rsh2;
   __shared__ int emit_count;
+  __shared__ int wtot[kFinThreads / 32];
   const int row = blockIdx.x, s = row / a.G;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int32_t* ri = a.row_info + (size_t)row * kRI;
   const int K = ri[PQHSA_RI_K];
   if (K <= 0) return;
   const int32_t* st = a.state + (size_t)s * kST;
-  const int n_sorted = st[PQHSA_ST_N_SORTED];
-  const int N = n_sorted + st[PQHSA_ST_N_TAIL];
+  const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
+  const int N = n_sorted + n_tail;
   const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
-  int C = ri[PQHSA_RI_NCAND];
-  const bool fallback = C < K || C > a.ccap;
-  if (fallback) C = N;
-  const int32_t* cand = a.cand_slot + (size_t)row * a.ccap;
-  const float* clog = a.cand_logit + (size_t)row * a.ccap;
   const uint32_t* codes = a.codes + (size_t)s * a.cap;
   const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
   const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-  const float* lsc = a.list_scores + (size_t)row * kLMax;
+  const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
+  const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
 
   if (tid < kM * kC) lut_s[tid] = a.lut[(size_t)row * kM * kC + tid];
+  if (tid < kLMax) lsc_s[tid] = a.list_scores[(size_t)row * kLMax + tid];
   if (tid == 0) emit_count = 0;
+
+  // ---- the set bits of the row's hit words become a candidate list ----
+  const uint32_t* hm = a.hitmap + (size_t)row * a.ucap * (kUnit / 32);
+  const int nw = (n_units + (n_tail + kUnit - 1) / kUnit) * (kUnit / 32);
+  int mine = 0;
+  for (int w = tid; w < nw; w += kFinThreads) mine += __popc(hm[w]);
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  int before = 0, C = 0;
+#pragma unroll
+  for (int w = 0; w < kFinThreads / 32; ++w) {
+    const int v = wtot[w];
+    before += w < warp ? v : 0;
+    C += v;
+  }
+  const int ncand = C;
+  const bool fallback = C < K || C > kCandCap;
+  if (!fallback) {
+    int o = before + incl - mine;
+    for (int w = tid; w < nw; w += kFinThreads) {
+      uint32_t bits = hm[w];
+      if (bits == 0u) continue;
+      const int u = w / (kUnit / 32), it = w % (kUnit / 32);
+      const bool sorted = u < n_units;
+      const int first = (sorted ? uoff[u] : n_sorted + (u - n_units) * kUnit) + it * 32;
+      const uint32_t l = sorted ? ulist[u] : 0u;
+      while (bits) {
+        const int slot = first + __ffs((int)bits) - 1;
+        bits &= bits - 1u;
+        cslot[o++] = (uint32_t)slot | ((sorted ? l : (uint32_t)lids[slot]) << kSlotBits);
+      }
+    }
+  } else {
+    C = N;
+  }
   __syncthreads();
 
-  auto slot_of = [&](int i) -> int { return fallback ? i : cand[i]; };
+  constexpr uint32_t kSlotMask = (1u << kSlotBits) - 1u;
+  auto slot_of = [&](int i) -> int { return fallback ? i : (int)(cslot[i] & kSlotMask); };
   auto logit_of = [&](int i) -> float {
-    if (!fallback) return clog[i];
-    return finish_logit(pq_sum_row(lut_s, __ldg(codes + i)), __ldg(lsc + lids[i]), to_f(norms[i]));
+    const int slot = slot_of(i);
+    const int l = fallback ? (int)lids[slot] : (int)(cslot[i] >> kSlotBits);
+    return finish_logit(pq_sum_row(lut_s, __ldg(codes + slot)), lsc_s[l], to_f(norms[slot]));
   };
   auto key = [&](int i) -> uint32_t { return float_key(logit_of(i)); };
   int32_t* sel = a.sel_slot + (size_t)row * a.kcap;
@@ -97,9 +145,11 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
       const int i = j * kFinThreads + tid;
       kreg[j] = 0u;
       sreg[j] = 0;
-      if (i < C) {
-        kreg[j] = float_key(clog[i]);
-        sreg[j] = cand[i];
+      if (j * kFinThreads < C) {  // block-uniform: rounds past the list cost nothing
+        if (i < C) {
+          kreg[j] = key(i);
+          sreg[j] = slot_of(i);
+        }
       }
     }
     if (!take_all) {
@@ -112,12 +162,17 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     }
 #pragma unroll
     for (int j = 0; j < kFinPer; ++j) {
+      if (j * kFinThreads >= C) break;  // block-uniform
       const uint32_t k = kreg[j];
-      if (k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2))) {
-        const int o = atomicAdd(&emit_count, 1);
-        if (o < a.kcap) {
+      const bool take = k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2));
+      const unsigned m = __ballot_sync(0xffffffffu, take);  // one shared-memory atomic per warp, not per key
+      if (m != 0u) {
+        int o = 0;
+        if (lane == 0) o = atomicAdd(&emit_count, __popc(m));
+        o = __shfl_sync(0xffffffffu, o, 0) + __popc(m & ((1u << lane) - 1u));
+        if (take && o < a.kcap) {
           sel[o] = sreg[j];
-          soff[o] = (long long)__float_as_uint(clog[j * kFinThreads + tid]);
+          soff[o] = (long long)__float_as_uint(key_float(k));
         }
       }
     }
@@ -179,6 +234,7 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     }
   }
   if (tid == 0) {
+    ri[PQHSA_RI_NCAND] = ncand;
     ri[PQHSA_RI_NSEL] = emit_count;
     ri[PQHSA_RI_FALLBACK] = fallback ? 1 : 0;
   }
@@ -197,8 +253,9 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.lut = reinterpret_cast<const float*>(ws + w.lut);
   a.list_scores = reinterpret_cast<const float*>(ws + w.list_scores);
   a.row_info = reinterpret_cast<int32_t*>(ws + w.row_info);
-  a.cand_slot = reinterpret_cast<const int32_t*>(ws + w.cand_slot);
-  a.cand_logit = reinterpret_cast<const float*>(ws + w.cand_logit);
+  a.hitmap = reinterpret_cast<const uint32_t*>(ws + w.hitmap);
+  a.unit_off = static_cast<const int32_t*>(p.unit_off);
+  a.unit_list = static_cast<const uint16_t*>(p.unit_list);
   a.sel_slot = reinterpret_cast<int32_t*>(ws + w.sel_slot);
   a.sel_off = reinterpret_cast<long long*>(ws + w.sel_off);
   a.unit_max = reinterpret_cast<const float*>(ws + w.unit_max);
@@ -210,8 +267,13 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
   a.kcap = w.kcap;
-  a.ccap = w.ccap;
-  PQHSA_DISPATCH_E(p.dtype, finish_kernel<E><<<R, kFinThreads, 0, st>>>(a));
+  const size_t smem = (size_t)kCandCap * sizeof(uint32_t);
+  PQHSA_DISPATCH_E(p.dtype, {
+    auto kern = finish_kernel<E>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return check_launch("finish: shared memory opt-in");
+    kern<<<R, kFinThreads, smem, st>>>(a);
+  });
   return check_launch("finish");
 }
 

@@ -80,6 +80,7 @@ extern "C" int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, vo
   memset(&w, 0, sizeof(w));
   w.total_bytes = kStaticBytes;
   w.lut = kOffLut;
+  w.pair_tab = (size_t)-1;  // only the full scan reads pair tables
   w.list_scores = kOffListScores;
   w.row_bin = kOffRowBin;
   w.row_tau = kOffRowTau;

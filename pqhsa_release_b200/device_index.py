@@ -459,8 +459,7 @@ class DeviceIndexPool:
             "unit_sum": (torch.float32, (R, self.ucap)),
             "tail_logit": (torch.float32, (R, lay.tail_cap)),
             "row_info": (torch.int32, (R, _lib.ROW_INFO_INTS)),
-            "cand_slot": (torch.int32, (R, lay.ccap)),
-            "cand_logit": (torch.float32, (R, lay.ccap)),
+            "hitmap": (torch.int32, (R, self.ucap, _lib.UNIT_KEYS // 32)),
             "sel_slot": (torch.int32, (R, lay.kcap)),
             "sel_off": (torch.int64, (R, lay.kcap)),
             "partial": (torch.float32, (R, lay.chunks, _lib.HEAD_DIM + 2)),

@@ -63,7 +63,7 @@ def test_workspace_layout_is_ordered_and_aligned():
     offs = [getattr(lay, f) for f, _ in WsLayout._fields_[1:15]]
     assert offs == sorted(offs) and all(o % 256 == 0 for o in offs) and offs[-1] < lay.total_bytes
     assert lay.kcap >= int(131072 * 0.02) and lay.kcap % 8 == 0
-    assert lay.ccap >= lay.kcap and lay.chunks * 128 >= 200 + lay.kcap
+    assert lay.hitmap > lay.row_info and lay.chunks * 128 >= 200 + lay.kcap
 
 
 @pytest.mark.parametrize(
