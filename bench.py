@@ -358,7 +358,15 @@ def run_b200(args):
             print(json.dumps(line["stages_us"]), file=sys.stderr)
         print(json.dumps(line))
     if world > 1:
-        torch.distributed.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a communicator whose kernels sit in a live CUDA
+        # graph can block for ever.  Every rank has printed / finished once the barrier returns.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        runner.graph = None
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------

@@ -32,7 +32,7 @@ extern "C" {
 #define PQHSA_MAX_LISTS 512
 #define PQHSA_UNIT_KEYS 128     /* a scan unit = at most this many slots of one list */
 #define PQHSA_SAMPLE_KEYS 4096  /* keys scored per stream to place the candidate threshold */
-#define PQHSA_HIST_BINS 4096    /* resolution of the sample histogram */
+#define PQHSA_HIST_BINS 2048    /* resolution of the sample histogram */
 
 enum pqhsa_status {
   PQHSA_OK = 0,
@@ -125,6 +125,9 @@ typedef struct pqhsa_params {
                               bits, list id, j) - a contiguous copy of what the threshold estimate reads, to
                               be refreshed whenever the sorted region changes; NULL = gather from the index.
                               Only read for streams with more than PQHSA_SAMPLE_KEYS sorted slots. */
+  const void *sample_start;/* int32 [S, PQHSA_MAX_LISTS + 1], required with sample: index of the first sample
+                              record of list l (records are in slot order, hence sorted by list);
+                              entry num_lists = 4096 */
 
   const void *k_base, *v_base;
   const int32_t *block_table;
@@ -148,7 +151,9 @@ typedef struct pqhsa_ws_layout {
   size_t pair_tab;     /* float  [S, G/GP, 4, 256, GP], GP = min(G, 4): byte-pair sums of lut for the scan */
   size_t row_bin;      /* float  [R, 2]   sample histogram origin and 1 / bin width       */
   size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
-  size_t ticket;       /* int32  [S]      arrival counter of the table kernel's CTAs       */
+  size_t ticket;       /* int32  [S]      arrival counter of the table kernel's CTAs (0 between launches) */
+  size_t slog;         /* float  [R, PQHSA_SAMPLE_KEYS]  approximate logits of the sample keys           */
+  size_t norm_pend;    /* float  [S]      norm of a key encoded in the current launch                    */
   size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit                   */
   size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max), selected keys removed */
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */

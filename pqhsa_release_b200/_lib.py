@@ -10,7 +10,7 @@ import ctypes as C
 from pathlib import Path
 
 ABI_VERSION = 3
-SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 4096
+SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 2048
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
 RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK = range(5)
@@ -35,7 +35,7 @@ class Params(C.Structure):
         ("slot_unit", C.c_void_p), ("unit_off", C.c_void_p), ("unit_list", C.c_void_p),
         ("coarse", C.c_void_p), ("codebooks", C.c_void_p), ("vmeans", C.c_void_p),
         ("vsum", C.c_void_p), ("vcnt", C.c_void_p), ("state", C.c_void_p), ("norm_max", C.c_void_p),
-        ("sample", C.c_void_p),
+        ("sample", C.c_void_p), ("sample_start", C.c_void_p),
         ("k_base", C.c_void_p), ("v_base", C.c_void_p), ("block_table", C.c_void_p),
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
@@ -49,7 +49,7 @@ class WsLayout(C.Structure):
     _fields_ = [
         ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("pair_tab", C.c_size_t),
         ("row_bin", C.c_size_t),
-        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
+        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
         ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t),
         ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),

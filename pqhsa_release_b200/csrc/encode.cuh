@@ -90,6 +90,37 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
     if (pos >= seq_len || slot >= a.cap || n_tail >= a.tail_cap) break;
     const long long off = a.kv.offset(req, head, pos);
 
+    // Everything that does not depend on the key is requested before the key is looked at: the
+    // first batch of centroids (4 lanes per list, 32 dims each, kept as raw 16-byte vectors), the
+    // thread's code word and the value row.
+    const int sub = tid & 3, grp = tid >> 2;  // groups of 4 lanes
+    constexpr int kGroups = kEncThreads / 4;
+    constexpr int kVecs = 32 * (int)sizeof(E) / 16;     // 16-byte vectors per 32 dims
+    constexpr int kBatch = sizeof(E) == 2 ? 4 : 2;      // lists per thread in flight
+    uint4 raw[kBatch][kVecs];
+    auto load_batch = [&](int l0) {
+#pragma unroll
+      for (int h = 0; h < kBatch; ++h) {
+        const int l = l0 + h * kGroups + grp;
+        if (l < nl) {
+          const uint4* src = reinterpret_cast<const uint4*>(coarse + (size_t)l * kD + sub * 32);
+#pragma unroll
+          for (int j = 0; j < kVecs; ++j) raw[h][j] = __ldg(src + j);
+        }
+      }
+    };
+    load_batch(0);
+    float cwv[kSub];
+    if (tid < kM * kC) {
+      float x[8], y[8];
+      load8(books + (size_t)tid * kSub, x);
+      load8(books + (size_t)tid * kSub + 8, y);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) { cwv[d] = x[d]; cwv[8 + d] = y[d]; }
+    }
+    float vval = 0.f;
+    if (tid < kD) vval = to_f(vb[off + tid]);
+
     // |k| and the unit direction
     float kval = 0.f;
     if (tid < kD) kval = to_f(kb[off + tid]);
@@ -110,35 +141,35 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
     float bd = __builtin_huge_valf();
     int bl = 0x7fffffff;
     {
-      const int sub = tid & 3, grp = tid >> 2;  // 64 groups of 4 lanes
-      constexpr int kGroups = kEncThreads / 4;
       float uq[32];
 #pragma unroll
       for (int d = 0; d < 32; ++d) uq[d] = unit[sub * 32 + d];
-      for (int l0 = 0; l0 < nl; l0 += 2 * kGroups) {
-        float c[2][32];
+      for (int l0 = 0; l0 < nl; l0 += kBatch * kGroups) {
+        if (l0 > 0) load_batch(l0);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int l = l0 + h * kGroups + grp;
-          if (l < nl) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float t[8];
-              load8(coarse + (size_t)l * kD + sub * 32 + j * 8, t);
-#pragma unroll
-              for (int d = 0; d < 8; ++d) c[h][j * 8 + d] = t[d];
-            }
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < kBatch; ++h) {
           const int l = l0 + h * kGroups + grp;
           float dist = 0.f;
           if (l < nl) {
 #pragma unroll
-            for (int d = 0; d < 32; ++d) {
-              const float df = uq[d] - c[h][d];
-              dist = fmaf(df, df, dist);
+            for (int j = 0; j < kVecs; ++j) {
+              if constexpr (sizeof(E) == 2) {
+                float c8[8];
+                unpack8(raw[h][j], static_cast<const E*>(nullptr), c8);
+#pragma unroll
+                for (int d = 0; d < 8; ++d) {
+                  const float df = uq[j * 8 + d] - c8[d];
+                  dist = fmaf(df, df, dist);
+                }
+              } else {
+                const float c4[4] = {__uint_as_float(raw[h][j].x), __uint_as_float(raw[h][j].y),
+                                     __uint_as_float(raw[h][j].z), __uint_as_float(raw[h][j].w)};
+#pragma unroll
+                for (int d = 0; d < 4; ++d) {
+                  const float df = uq[j * 4 + d] - c4[d];
+                  dist = fmaf(df, df, dist);
+                }
+              }
             }
           }
           dist += __shfl_xor_sync(0xffffffffu, dist, 1);
@@ -184,11 +215,10 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
     // nearest code word per subspace: thread (m, c) for tid < 128, 16 lanes per subspace
     if (tid < kM * kC) {
       const int m = tid / kC, c = tid % kC;
-      const E* cw = books + (size_t)tid * kSub;
       float dist = 0.f;
 #pragma unroll
       for (int d = 0; d < kSub; ++d) {
-        const float df = resid[m * kSub + d] - to_f(cw[d]);
+        const float df = resid[m * kSub + d] - cwv[d];
         dist = fmaf(df, df, dist);
       }
       int bc = c;
@@ -216,7 +246,7 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
     // running value mean of the list
     if (tid < kD) {
       const size_t vi = ((size_t)s * a.num_lists + lid) * kD + tid;
-      const float nsum = a.vsum[vi] + to_f(vb[off + tid]);
+      const float nsum = a.vsum[vi] + vval;
       const int ncnt = a.vcnt[(size_t)s * a.num_lists + lid] + 1;
       a.vsum[vi] = nsum;
       static_cast<E*>(a.vmeans)[vi] = from_f<E>(nsum / (float)ncnt);

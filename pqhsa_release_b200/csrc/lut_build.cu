@@ -1,7 +1,7 @@
-// First kernel of a decode step: per-query, per-head table construction and the
-// candidate-threshold estimate, optionally fused with the step's token append (raw K/V row
+// First kernel of a decode step: per-query, per-head table construction, optionally fused with the step's token append (raw K/V row
 // write) and the incremental encode of the key that left the local window.  The CTAs of a
-// stream take roles by blockIdx.y - tables, list scores (64 lists each), encode - and run
+// stream take roles by blockIdx.y - list scores (176 lists each; the first also publishes the
+// tables and writes the K/V row), encode - and run
 // side by side; nobody changes a stream counter before every CTA of the stream has arrived,
 // so all roles see the same state.
 //
@@ -13,22 +13,26 @@
 // into the tables (benchmarks/e2e_pq_param_sweep.py:228-249,
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:2975-3051), as is done here, in fp32.
 //
-// Threshold estimate.  The exact top-K needs the K-th largest of N logits, which
-// is not known before the scan.  The CTA of a stream that finishes last (arrival
-// counter, no waiting) scores a stratified sample of 4096 slots of the
-// list-sorted region, histograms the sample per row and takes as threshold tau
-// the logit below which all but r sample keys lie, r = f n + margin * sqrt(f n) + 1
-// with f = K / N.  The scan then keeps only keys with logit >= tau as candidates
-// (about 2 K of them) and the selection kernel takes the exact top K among them.
-// tau is only a filter: if fewer than K candidates turn up (probability ~1e-9 at
-// the default margin of 6 sigma) the selection kernel falls back to all keys, so
-// the result is exact either way.
+// The table CTA also folds the 8 nibble tables into the 4 byte-pair tables the scan looks
+// codes up in.
+//
+// Threshold estimate.  The exact top-K needs the K-th largest of N logits, which is not
+// known before the scan.  A stratified sample of 4096 slots of the list-sorted region
+// (contiguous records made when the layout was made) is scored by the list CTAs - each the
+// sample keys of its own 64 lists, whose scores it has just computed - and counted into
+// per-row histograms in global memory.  The CTA of a stream that arrives last (arrival
+// counter, no waiting) walks the histograms from the top and takes as threshold tau the
+// logit below which all but r sample keys lie, r = f n + margin * sqrt(f n) + 1 with
+// f = K / N.  The scan then marks the keys with logit >= tau (about 1.7 K of them) and the
+// selection kernel takes the exact top K among them.  tau is only a filter: if fewer than K
+// candidates turn up (probability ~1e-9 at the default margin of 6 sigma) the selection
+// kernel falls back to all keys, so the result is exact either way.
 #include "encode.cuh"
 
 namespace pqhsa {
 
 constexpr int kLutThreads = 512;
-constexpr int kListsPerCta = 64;  // 16 warps x 4 lists
+constexpr int kListsPerCta = 176;  // 16 warps x 11 lists: 3 list CTAs + 1 encode CTA per stream, 128 CTAs for 32 streams - one wave
 
 struct LutArgs {
   const void* q;
@@ -40,6 +44,9 @@ struct LutArgs {
   const void* norms;
   const uint16_t* list_ids;
   const int4* sample;  // [S, kSample] (code, norm as float bits, list, slot) of the stratified sample, or null
+  const int32_t* sample_start;  // [S, kLMax + 1] first sample record of every list
+  float* slog;         // [R, kSample] logits of the sample keys, or null: no threshold wanted
+  float* norm_max_rw;
   float* lut;
   float* pair_tab;  // [S, G / GP, 4, 256, GP] byte-pair sums of the tables for the scan, GP = min(G, 4); or null
   float* list_scores;
@@ -65,46 +72,33 @@ struct LutArgs {
 
 template <typename E, int G>
 __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a) {
-  extern __shared__ uint32_t hist[];  // [G][kBins], used by the last CTA of a stream only
   __shared__ float qs[G][kD];
-  __shared__ float sub_max[G][kM];
   __shared__ float lut_s[G][kM * kC];
-  __shared__ uint32_t wsum[kLutThreads / 32];
+  __shared__ float lsc_s[G][kListsPerCta];
+  extern __shared__ uint32_t hist[];  // [min(G, 4)][kBins], used by the last CTA of a stream only
+  __shared__ uint32_t wsum[kLutThreads / 32], wmin[kLutThreads / 32], wmax[kLutThreads / 32];
   __shared__ int is_last;
-  __shared__ float bin_s[G][2];
   const int s = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const E* q = static_cast<const E*>(a.q);
   const bool append = a.new_k != nullptr;
-  const int seq_old = a.state[(size_t)s * kST + PQHSA_ST_SEQ_LEN];
+  int32_t* st = a.state + (size_t)s * kST;
+  const int seq_old = st[PQHSA_ST_SEQ_LEN];
+  const int n_sorted = st[PQHSA_ST_N_SORTED];
+  const bool sampling = a.slog != nullptr && n_sorted > kSample;  // shorter streams: every key is a candidate
+  const bool is_encode = (int)blockIdx.y >= a.list_ctas;
 
-  if ((int)blockIdx.y > a.list_ctas) {
-    // encode role: the token just appended counts as part of the stream
+  if (is_encode) {
+    // encode role: the token just appended counts as part of the stream.  A larger norm is parked in
+    // norm_pend and folded into norm_max by the last CTA, like the counters.
+    if (tid == 0) a.enc.norm_max[s] = a.norm_max[s];
+    __syncthreads();
     const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old + (append ? 1 : 0));
-    if (tid == 0) a.state[(size_t)s * kST + PQHSA_ST_N_TAIL] = n_tail;
+    if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail;
   } else {
     for (int i = tid; i < G * kD; i += kLutThreads) qs[i / kD][i % kD] = to_f(q[(size_t)s * G * kD + i]) * a.scale;
     __syncthreads();
-  }
-
-  if (blockIdx.y == 0) {
-    if (a.sample != nullptr) {  // the last CTA of the stream will want the sample: start it towards L2
-      const char* sp = reinterpret_cast<const char*>(a.sample + (size_t)s * kSample) + (size_t)tid * 128;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(sp));
-    }
-    if (append && tid < 2 * kD / 8) {
-      // the step's K/V row, 16 bytes per thread (elements are 2 or 4 bytes: 8 or 4 per vector)
-      constexpr int kVec = 16 / (int)sizeof(E);
-      const int32_t* st = a.state + (size_t)s * kST;
-      const long long off = a.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], seq_old);
-      for (int i = tid; i < 2 * kD / kVec; i += 2 * kD / 8) {
-        const bool isv = i >= kD / kVec;
-        const int e = (isv ? i - kD / kVec : i) * kVec;
-        const E* src = static_cast<const E*>(isv ? a.new_v : a.new_k) + (size_t)s * kD + e;
-        E* dst = static_cast<E*>(isv ? a.v_base : a.k_base) + off + e;
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-      }
-    }
+    // the tables (every table and list CTA: the list CTAs score their share of the sample with them)
     if (tid < kM * kC) {
       const int m = tid / kC;
       const E* cw = static_cast<const E*>(a.codebooks) + ((size_t)s * kM * kC + tid) * kSub;
@@ -121,15 +115,26 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         float acc = 0.f;
 #pragma unroll
         for (int d = 0; d < kSub; ++d) acc = fmaf(qs[g][m * kSub + d], w[d], acc);
-        a.lut[((size_t)s * G + g) * kM * kC + tid] = acc;
+        if (blockIdx.y == 0) a.lut[((size_t)s * G + g) * kM * kC + tid] = acc;
         lut_s[g][tid] = acc;
-        float mx = fabsf(acc);  // max over the 16 code words of this subspace (16 consecutive lanes)
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if ((tid & (kC - 1)) == 0) sub_max[g][m] = mx;
       }
     }
     __syncthreads();
+  }
+
+  if (blockIdx.y == 0) {
+    if (append && tid < 2 * kD / 8) {
+      // the step's K/V row, 16 bytes per thread (elements are 2 or 4 bytes: 8 or 4 per vector)
+      constexpr int kVec = 16 / (int)sizeof(E);
+      const long long off = a.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], seq_old);
+      for (int i = tid; i < 2 * kD / kVec; i += 2 * kD / 8) {
+        const bool isv = i >= kD / kVec;
+        const int e = (isv ? i - kD / kVec : i) * kVec;
+        const E* src = static_cast<const E*>(isv ? a.new_v : a.new_k) + (size_t)s * kD + e;
+        E* dst = static_cast<E*>(isv ? a.v_base : a.k_base) + off + e;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+      }
+    }
     if (a.pair_tab != nullptr) {
       // the scan looks codes up a byte (two subspaces) at a time: entry (p, byte) = lut[2p][byte & 15] + lut[2p+1][byte >> 4]
       constexpr int GP = G < 4 ? G : 4;
@@ -140,19 +145,10 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         dst[i] = pair_entry(lut_s[pass * GP + g], e >> 8, (uint32_t)(e & 255));
       }
     }
-    if (tid < G) {
-      // |logit| <= (scale |q| max_l |c_l| + sum_m max_c |lut[m][c]|) * max |k|, |c_l| <= 1: the part
-      // that does not depend on the norms is parked here; the last CTA multiplies max |k| in
-      // (the encode role may still be raising it)
-      float qq = 0.f, pm = 0.f;
-      for (int d = 0; d < kD; ++d) qq = fmaf(qs[tid][d], qs[tid][d], qq);
-#pragma unroll
-      for (int m = 0; m < kM; ++m) pm += sub_max[tid][m];
-      a.row_bin[((size_t)s * G + tid) * 2] = sqrtf(qq) + pm;
-    }
-  } else if ((int)blockIdx.y <= a.list_ctas) {
+  }
+  if (!is_encode) {
     // list scores: one warp per list, a lane owns 4 dims
-    const int l0 = (blockIdx.y - 1) * kListsPerCta;
+    const int l0 = blockIdx.y * kListsPerCta;
     float qr[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -166,6 +162,13 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
       const int l = l0 + warp * kPerWarp + i;
       if (l < a.num_lists) load4(coarse + (size_t)l * kD + lane * 4, c[i]);
     }
+    // this CTA's slice of the stream's sample records (sorted by list), requested early
+    int i0 = 0, i1 = 0;
+    if (sampling && a.sample != nullptr) {
+      const int32_t* ss = a.sample_start + (size_t)s * (kLMax + 1);
+      i0 = ss[min(l0, a.num_lists)];
+      i1 = ss[min(l0 + kListsPerCta, a.num_lists)];
+    }
 #pragma unroll
     for (int i = 0; i < kPerWarp; ++i) {
       const int l = l0 + warp * kPerWarp + i;
@@ -177,149 +180,159 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         acc = fmaf(c[i][2], qr[g][2], acc);
         acc = fmaf(c[i][3], qr[g][3], acc);
         acc = warp_sum(acc);
-        if (lane == 0) a.list_scores[((size_t)s * G + g) * kLMax + l] = acc;
+        if (lane == 0) {
+          a.list_scores[((size_t)s * G + g) * kLMax + l] = acc;
+          lsc_s[g][l - l0] = acc;
+        }
       }
+    }
+    __syncthreads();
+    // Threshold estimate, first half: the sample keys of this CTA's lists are scored (same arithmetic
+    // as the scan); the logits go to the rows' sample arrays.
+    for (int i = i0 + tid; i < i1; i += kLutThreads) {
+      const int4 v = __ldg(a.sample + (size_t)s * kSample + i);
+      const uint32_t code = (uint32_t)v.x;
+      const float kn = __int_as_float(v.y);
+      const int l = v.z - l0;
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        a.slog[((size_t)s * G + g) * kSample + i] = finish_logit(pq_sum_row(lut_s[g], code), lsc_s[g][l], kn);
     }
   }
 
-  // ---- the CTA of this stream that arrives last places the candidate thresholds ----
+  // ---- the CTA of the stream that arrives last changes the counters and places the thresholds ----
   // (the barrier makes the CTA's stores visible to thread 0, whose fence then publishes them
   //  device-wide before the ticket; the last CTA reads the others' results through L2)
+  if (a.slog == nullptr && !append && !a.encode) return;  // tables only: nothing left to do
   __syncthreads();
   if (tid == 0) {
     __threadfence();
     const int t = atomicAdd(a.ticket + s, 1);
     is_last = (t == (int)gridDim.y - 1);
-    if (is_last) {
-      __threadfence();
-      a.ticket[s] = 0;  // ready for the next launch
-    }
+    if (is_last) a.ticket[s] = 0;  // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
 
-  // every CTA of the stream is done: counters may change now; what other CTAs wrote is read through L2
-  int32_t* st = a.state + (size_t)s * kST;
-  if (append && tid == 0) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
-  const int n_sorted = st[PQHSA_ST_N_SORTED];
+  // every CTA of the stream is done reading the counters: the token written above now counts
+  if (tid == 0) {
+    if (append) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
+    if (a.encode) {
+      const float pend = __ldcg(a.enc.norm_max + s);
+      if (pend > a.norm_max[s]) a.norm_max_rw[s] = pend;
+    }
+  }
+  if (a.slog == nullptr) return;
   const int n = n_sorted + __ldcg(st + PQHSA_ST_N_TAIL);
   const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
-  if (tid < G) {
-    float lo = a.fixed_lo, inv_w = a.fixed_inv_w;
-    if (!(a.fixed_inv_w > 0.f)) {
-      const float bound = __ldcg(a.row_bin + ((size_t)s * G + tid) * 2) * __ldcg(a.norm_max + s) * 1.0001f;
-      lo = -bound;
-      inv_w = bound > 1e-30f ? (float)(kBins / 2) / bound : 1.f;
-    }
-    a.row_bin[((size_t)s * G + tid) * 2] = lo;
-    a.row_bin[((size_t)s * G + tid) * 2 + 1] = inv_w;
-    bin_s[tid][0] = lo;
-    bin_s[tid][1] = inv_w;
-    int32_t* ri = a.row_info + ((size_t)s * G + tid) * kRI;
-    ri[PQHSA_RI_K] = K;
-    ri[PQHSA_RI_N] = n;
-    ri[PQHSA_RI_NCAND] = 0;
-    ri[PQHSA_RI_NSEL] = 0;
-    ri[PQHSA_RI_FALLBACK] = 0;
-  }
   const int ns = min(kSample, n_sorted);
   const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
   const float margin = a.margin != 0.f ? a.margin : 6.f;
   const int r = (int)ceilf(expect + margin * sqrtf(expect) + 1.f);
-  if (K == 0 || n_sorted <= kSample || r >= ns || r < 1) {
+  const bool trivial = K == 0 || n_sorted <= kSample || r >= ns || r < 1;
+  if (!sampling) {
     // nothing to select, or a context so short that every key is a candidate
     if (tid < G) a.row_tau[(size_t)s * G + tid] = (K == 0) ? __builtin_huge_valf() : kNegInf;
     return;
   }
-  for (int i = tid; i < G * kM * kC; i += kLutThreads)
-    lut_s[i / (kM * kC)][i % (kM * kC)] = __ldcg(a.lut + (size_t)s * G * kM * kC + i);
-  for (int i = tid; i < G * kBins; i += kLutThreads) hist[i] = 0u;
-  __syncthreads();
-  float lo[G], iw[G];
+  float* slog = a.slog + (size_t)s * G * kSample;
+  if (a.sample == nullptr) {
+    // no sample records: this CTA gathers and scores all sample slots itself (slow path)
+    if (is_encode)  // this CTA made no tables: take them from the table CTA
+      for (int i = tid; i < G * kM * kC; i += kLutThreads)
+        lut_s[i / (kM * kC)][i % (kM * kC)] = __ldcg(a.lut + (size_t)s * G * kM * kC + i);
+    __syncthreads();
+    const uint32_t* codes = a.codes + (size_t)s * a.cap;
+    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+    for (int i = tid; i < ns; i += kLutThreads) {
+      const int slot = (int)((long long)i * n_sorted / ns);
+      const uint32_t code = __ldg(codes + slot);
+      const float kn = to_f(norms[slot]);
+      const int l = lids[slot];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    lo[g] = bin_s[g][0];
-    iw[g] = bin_s[g][1];
-  }
-  const uint32_t* codes = a.codes + (size_t)s * a.cap;
-  const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
-  const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-  // the 4096 / 512 = 8 samples of a thread: all index loads first, then all list scores
-  constexpr int kPer = kSample / kLutThreads;
-  uint32_t code[kPer];
-  float kn[kPer];
-  int li[kPer];
-  if (a.sample != nullptr) {
-    const int4* rec = a.sample + (size_t)s * kSample;  // the same slots, gathered when the layout was made
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int4 v = __ldg(rec + tid + j * kLutThreads);
-      code[j] = (uint32_t)v.x;
-      kn[j] = __int_as_float(v.y);
-      li[j] = v.z;
+      for (int g = 0; g < G; ++g)
+        slog[(size_t)g * kSample + i] =
+            finish_logit(pq_sum_row(lut_s[g], code), __ldcg(a.list_scores + ((size_t)s * G + g) * kLMax + l), kn);
     }
-  } else {
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int i = tid + j * kLutThreads;
-      const int slot = (int)((long long)(i < ns ? i : 0) * n_sorted / ns);
-      code[j] = __ldg(codes + slot);
-      kn[j] = to_f(norms[slot]);
-      li[j] = lids[slot];
-    }
+    __threadfence();
+    __syncthreads();
   }
-  float lsv[kPer][G];
+  if (trivial) {
+    if (tid < G) a.row_tau[(size_t)s * G + tid] = (K == 0) ? __builtin_huge_valf() : kNegInf;
+    return;
+  }
+  // Second half, GP rows at a time, kTPR threads per row: the r-th largest of the row's 4096 sample
+  // logits, to the resolution of a 2048-bin histogram over the sample's own range; tau is the lower
+  // edge of the bin where the count from the top reaches r (so at least r sample keys pass).
+  constexpr int GP = G < 4 ? G : 4;
+  constexpr int kTPR = kLutThreads / GP;  // threads per row (a multiple of 32)
+  constexpr int kVPT = kSample / kTPR;    // sample logits per thread
+  constexpr int kBPT = kBins / kTPR;      // bins per thread
+  constexpr int kWPR = kTPR / 32;         // warps per row
+  const int gl = tid / kTPR, j = tid % kTPR;
+  for (int gb = 0; gb < G; gb += GP) {
+    const int g = gb + gl;
+    uint32_t key[kVPT];
 #pragma unroll
-  for (int j = 0; j < kPer; ++j)
+    for (int i = 0; i < kVPT; ++i) key[i] = float_key(__ldcg(slog + (size_t)g * kSample + j + i * kTPR));
+    uint32_t mn = key[0], mx = key[0];
 #pragma unroll
-    for (int g = 0; g < G; ++g) lsv[j][g] = __ldcg(a.list_scores + ((size_t)s * G + g) * kLMax + li[j]);
+    for (int i = 1; i < kVPT; ++i) {
+      mn = min(mn, key[i]);
+      mx = max(mx, key[i]);
+    }
+    mn = __reduce_min_sync(0xffffffffu, mn);
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    __syncthreads();  // the previous round is done with the shared arrays
+    if (lane == 0) {
+      wmin[warp] = mn;
+      wmax[warp] = mx;
+    }
+    for (int i = tid; i < GP * kBins; i += kLutThreads) hist[i] = 0u;
+    __syncthreads();
 #pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    if (tid + j * kLutThreads < ns) {
+    for (int w = 0; w < kWPR; ++w) {
+      mn = min(mn, wmin[gl * kWPR + w]);
+      mx = max(mx, wmax[gl * kWPR + w]);
+    }
+    // linear bins over the row's own range [min, max]
+    const float lo = key_float(mn), hi = key_float(mx);
+    const float inv_w = hi > lo ? (float)kBins / (hi - lo) : 1.f;
+    uint32_t* h = hist + gl * kBins;
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float x = finish_logit(pq_sum_row(lut_s[g], code[j]), lsv[j][g], kn[j]);
-        atomicAdd(&hist[g * kBins + logit_bin(x, lo[g], iw[g])], 1u);
+    for (int i = 0; i < kVPT; ++i) atomicAdd(&h[logit_bin(key_float(key[i]), lo, inv_w)], 1u);
+    __syncthreads();
+    const int top = kBins - kBPT * j;  // thread j owns the kBPT bins just below
+    uint32_t c[kBPT], sum = 0;
+#pragma unroll
+    for (int b = 0; b < kBPT; ++b) {
+      c[b] = h[top - 1 - b];
+      sum += c[b];
+    }
+    uint32_t incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0;
+    for (int i = gl * kWPR; i < warp; ++i) before += wsum[i];
+    incl += before;
+    const uint32_t excl = incl - sum, need = (uint32_t)r;
+    if (excl < need && need <= incl) {
+      uint32_t cum = excl;
+#pragma unroll
+      for (int b = 0; b < kBPT; ++b) {
+        if (cum < need && need <= cum + c[b]) {
+          // one bin of slack for the rounding of the edge; bins 0 and 1 mean "everything"
+          const int bin = top - 1 - b;
+          a.row_tau[(size_t)s * G + g] = bin <= 1 ? kNegInf : lo + (float)(bin - 1) / inv_w;
+        }
+        cum += c[b];
       }
-    }
-  }
-  __syncthreads();
-  // All rows at once: row g is walked by kLutThreads / G threads, thread j of a row owns the
-  // kBins / (kLutThreads / G) bins just below 4096 - j * that; find the bin where the count
-  // from the top reaches r.
-  constexpr int kTPR = kLutThreads / G;  // threads per row (a multiple of 32)
-  constexpr int kBPT = kBins / kTPR;     // bins per thread
-  const int g = tid / kTPR, j = tid % kTPR;
-  const uint32_t* h = hist + g * kBins;
-  const int top = kBins - kBPT * j;
-  uint32_t sum = 0;
-#pragma unroll 8
-  for (int b = 0; b < kBPT; ++b) sum += h[top - 1 - b];
-  uint32_t incl = sum;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += v;
-  }
-  if (lane == 31) wsum[warp] = incl;
-  __syncthreads();
-  uint32_t before = 0;
-  for (int i = g * (kTPR / 32); i < warp; ++i) before += wsum[i];
-  incl += before;
-  const uint32_t excl = incl - sum, need = (uint32_t)r;
-  if (excl < need && need <= incl) {
-    uint32_t cum = excl;
-    float lo_g = lo[0], iw_g = iw[0];
-#pragma unroll
-    for (int gg = 1; gg < G; ++gg)
-      if (gg == g) { lo_g = lo[gg]; iw_g = iw[gg]; }
-    for (int b = top - 1; b >= top - kBPT; --b) {
-      const uint32_t c = h[b];
-      if (cum < need && need <= cum + c) {
-        // one bin of slack for the rounding of the edge; bins 0 and 1 mean "everything"
-        a.row_tau[(size_t)s * G + g] = b <= 1 ? kNegInf : lo_g + (float)(b - 1) / iw_g;
-      }
-      cum += c;
     }
   }
 }
@@ -352,6 +365,9 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.fixed_inv_w = p.hist_inv_width;
   a.margin = p.select_margin;
   a.sample = static_cast<const int4*>(p.sample);
+  a.sample_start = static_cast<const int32_t*>(p.sample_start);
+  a.slog = w.slog == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.slog);
+  a.norm_max_rw = static_cast<float*>(p.norm_max);
   a.list_ctas = (p.num_lists + kListsPerCta - 1) / kListsPerCta;
   a.k_base = const_cast<void*>(p.k_base);
   a.v_base = const_cast<void*>(p.v_base);
@@ -360,13 +376,10 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.new_v = ap ? ap->new_v : nullptr;
   a.encode = (ap && (ap->enc_count != nullptr || ap->uniform_count > 0)) ? 1 : 0;
   a.enc = make_encode_args(p, ap ? ap->enc_count : nullptr, ap ? ap->uniform_count : 0);
-  const size_t smem = (size_t)G * kBins * sizeof(uint32_t);
+  a.enc.norm_max = reinterpret_cast<float*>(ws + w.norm_pend);  // folded into norm_max once all CTAs are done
+  const size_t smem = (size_t)(G < 4 ? G : 4) * kBins * sizeof(uint32_t);
   auto kern = lut_build_kernel<E, G>;
-  if (smem > 40 * 1024) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return check_launch("lut_build: shared memory opt-in");
-  }
-  const dim3 grid(p.num_streams, 1 + a.list_ctas + a.encode);
+  const dim3 grid(p.num_streams, a.list_ctas + a.encode);
   kern<<<grid, kLutThreads, smem, st>>>(a);
   return check_launch("lut_build");
 }

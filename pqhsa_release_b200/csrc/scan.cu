@@ -276,10 +276,10 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
               }
             }
           }
+          const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
           float tau[GP];
 #pragma unroll
           for (int g = 0; g < GP; ++g) tau[g] = a.row_tau[row0 + g];
-          const float* mytab = tab + (lane & (PS::REP - 1)) * GP;
 
           for (int h0 = u0; h0 < u1; h0 += kHdr) {
             const int cnt = min(kHdr, u1 - h0);

@@ -51,11 +51,14 @@ struct FinishArgs {
   float* tail_logit;
   KvAddr kv;
   int G, cap, ucap, tail_cap, kcap;
+  double top_fraction;
+  int topk_fixed;
 };
 
 template <typename E>
 __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a) {
-  extern __shared__ uint32_t cslot[];  // [kCandCap] candidates as slot | list << kSlotBits
+  extern __shared__ uint32_t cslot[];  // [kCandCap] candidates as slot | list << kSlotBits, then their units
+  uint16_t* cunit = reinterpret_cast<uint16_t*>(cslot + kCandCap);
   __shared__ float lut_s[kM * kC];
   __shared__ float lsc_s[kLMax];
   __shared__ RadixShared rsh;
@@ -65,11 +68,20 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
   const int row = blockIdx.x, s = row / a.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int32_t* ri = a.row_info + (size_t)row * kRI;
-  const int K = ri[PQHSA_RI_K];
-  if (K <= 0) return;
   const int32_t* st = a.state + (size_t)s * kST;
   const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
   const int N = n_sorted + n_tail;
+  const int K = resolve_topk(N, a.top_fraction, a.topk_fixed);
+  if (K <= 0) {
+    if (threadIdx.x == 0) {
+      ri[PQHSA_RI_K] = 0;
+      ri[PQHSA_RI_N] = N;
+      ri[PQHSA_RI_NCAND] = 0;
+      ri[PQHSA_RI_NSEL] = 0;
+      ri[PQHSA_RI_FALLBACK] = 0;
+    }
+    return;
+  }
   const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
   const uint32_t* codes = a.codes + (size_t)s * a.cap;
   const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
@@ -82,10 +94,35 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
   if (tid == 0) emit_count = 0;
 
   // ---- the set bits of the row's hit words become a candidate list ----
+  // A thread owns the words tid, tid + 1024, ...; the first kWords of them stay in registers together
+  // with their units' first slot and list, requested in the same round trip.
   const uint32_t* hm = a.hitmap + (size_t)row * a.ucap * (kUnit / 32);
   const int nw = (n_units + (n_tail + kUnit - 1) / kUnit) * (kUnit / 32);
+  constexpr int kWords = 8;
+  uint32_t wbits[kWords];
+  int wfirst[kWords];
+  uint32_t wlist[kWords];
   int mine = 0;
-  for (int w = tid; w < nw; w += kFinThreads) mine += __popc(hm[w]);
+#pragma unroll
+  for (int j = 0; j < kWords; ++j) {
+    const int w = tid + j * kFinThreads;
+    wbits[j] = 0u;
+    wfirst[j] = 0;
+    wlist[j] = 0xFFFFu;
+    if (w < nw) {
+      const int u = w / (kUnit / 32), it = w % (kUnit / 32);
+      wbits[j] = hm[w];
+      if (u < n_units) {
+        wfirst[j] = uoff[u] + it * 32;
+        wlist[j] = ulist[u];
+      } else {
+        wfirst[j] = n_sorted + (u - n_units) * kUnit + it * 32;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kWords; ++j) mine += __popc(wbits[j]);
+  for (int w = tid + kWords * kFinThreads; w < nw; w += kFinThreads) mine += __popc(hm[w]);
   int incl = mine;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -105,18 +142,21 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
   const bool fallback = C < K || C > kCandCap;
   if (!fallback) {
     int o = before + incl - mine;
-    for (int w = tid; w < nw; w += kFinThreads) {
-      uint32_t bits = hm[w];
-      if (bits == 0u) continue;
-      const int u = w / (kUnit / 32), it = w % (kUnit / 32);
-      const bool sorted = u < n_units;
-      const int first = (sorted ? uoff[u] : n_sorted + (u - n_units) * kUnit) + it * 32;
-      const uint32_t l = sorted ? ulist[u] : 0u;
+    auto expand = [&](uint32_t bits, int first, uint32_t l, int u) {
       while (bits) {
         const int slot = first + __ffs((int)bits) - 1;
         bits &= bits - 1u;
-        cslot[o++] = (uint32_t)slot | ((sorted ? l : (uint32_t)lids[slot]) << kSlotBits);
+        cslot[o] = (uint32_t)slot | ((l != 0xFFFFu ? l : (uint32_t)lids[slot]) << kSlotBits);
+        cunit[o] = (uint16_t)u;
+        ++o;
       }
+    };
+#pragma unroll
+    for (int j = 0; j < kWords; ++j) expand(wbits[j], wfirst[j], wlist[j], (tid + j * kFinThreads) / (kUnit / 32));
+    for (int w = tid + kWords * kFinThreads; w < nw; w += kFinThreads) {
+      const int u = w / (kUnit / 32), it = w % (kUnit / 32);
+      const bool sorted = u < n_units;
+      expand(hm[w], (sorted ? uoff[u] : n_sorted + (u - n_units) * kUnit) + it * 32, sorted ? (uint32_t)ulist[u] : 0xFFFFu, u);
     }
   } else {
     C = N;
@@ -136,6 +176,7 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
   const bool take_all = K >= C;
   uint32_t T = 0u, T2 = 0u;
   int t = 0;
+  bool regs_path = false;
   if (!fallback && C <= kFinThreads * kFinPer) {
     // normal path: the candidates sit in registers, kFinPer per thread
     uint32_t kreg[kFinPer];
@@ -160,22 +201,48 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
         block_radix_threshold<kFinThreads>(tie_key, C, t, rsh, T2, t2);
       }
     }
+    // Emit: a taken key gets its place in the selection (one shared-memory atomic per warp), the
+    // element offset of its K/V row, and leaves the approximate side of the softmax - its unit's
+    // exp-sum loses exactly the term the scan added (a tail slot's stored logit becomes -inf).
+    const size_t sb = (size_t)s * a.cap;
 #pragma unroll
-    for (int j = 0; j < kFinPer; ++j) {
-      if (j * kFinThreads >= C) break;  // block-uniform
-      const uint32_t k = kreg[j];
-      const bool take = k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2));
-      const unsigned m = __ballot_sync(0xffffffffu, take);  // one shared-memory atomic per warp, not per key
-      if (m != 0u) {
-        int o = 0;
-        if (lane == 0) o = atomicAdd(&emit_count, __popc(m));
-        o = __shfl_sync(0xffffffffu, o, 0) + __popc(m & ((1u << lane) - 1u));
-        if (take && o < a.kcap) {
-          sel[o] = sreg[j];
-          soff[o] = (long long)__float_as_uint(key_float(k));
+    for (int j0 = 0; j0 < kFinPer; j0 += 4) {
+      if (j0 * kFinThreads >= C) break;  // block-uniform
+      int o[4], pos[4], u[4];
+      float um[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        const uint32_t k = kreg[j];
+        const bool take = k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2));
+        const unsigned m = __ballot_sync(0xffffffffu, take);
+        int base = 0;
+        if (m != 0u && lane == 0) base = atomicAdd(&emit_count, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0) + __popc(m & ((1u << lane) - 1u));
+        o[jj] = take && base < a.kcap ? base : -1;
+        pos[jj] = 0;
+        u[jj] = 0;
+        um[jj] = 0.f;
+        if (o[jj] >= 0) {
+          pos[jj] = a.slot_pos[sb + sreg[j]];
+          const int i = j * kFinThreads + tid;
+          u[jj] = cunit[i];
+          if (sreg[j] < n_sorted) um[jj] = a.unit_max[(size_t)row * a.ucap + u[jj]];
         }
       }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        if (o[jj] < 0) continue;
+        sel[o[jj]] = sreg[j];
+        soff[o[jj]] = a.kv.offset(req, head, pos[jj]);
+        if (sreg[j] < n_sorted)
+          atomicAdd(a.unit_sum + (size_t)row * a.ucap + u[jj], -unit_term(key_float(kreg[j]), unit_ref(um[jj])));
+        else
+          a.tail_logit[(size_t)row * a.tail_cap + (sreg[j] - n_sorted)] = kNegInf;
+      }
     }
+    regs_path = true;
   } else {
     // all N keys (the threshold estimate failed) or an oversized candidate list: keys are
     // recomputed on every pass
@@ -200,7 +267,7 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     }
   }
   __syncthreads();
-  const int nsel = min(emit_count, a.kcap);
+  const int nsel = regs_path ? 0 : min(emit_count, a.kcap);  // the register path has finished its keys already
   // pass 2: four selected keys per thread at a time, every level of dependent loads issued
   // together: slot -> (position, unit) -> (cache offset, unit max) -> stores
   constexpr int kB = 4;
@@ -234,6 +301,8 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     }
   }
   if (tid == 0) {
+    ri[PQHSA_RI_K] = K;
+    ri[PQHSA_RI_N] = N;
     ri[PQHSA_RI_NCAND] = ncand;
     ri[PQHSA_RI_NSEL] = emit_count;
     ri[PQHSA_RI_FALLBACK] = fallback ? 1 : 0;
@@ -267,7 +336,9 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
   a.kcap = w.kcap;
-  const size_t smem = (size_t)kCandCap * sizeof(uint32_t);
+  a.top_fraction = p.top_fraction;
+  a.topk_fixed = p.topk_fixed;
+  const size_t smem = (size_t)kCandCap * (sizeof(uint32_t) + sizeof(uint16_t));
   PQHSA_DISPATCH_E(p.dtype, {
     auto kern = finish_kernel<E>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
