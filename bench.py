@@ -182,7 +182,7 @@ class StepRunner:
         self.out = torch.zeros(S, G, D, dtype=wl.dtype, device=dev)
         self.gathered = torch.zeros(world, S, G, D, dtype=wl.dtype, device=dev) if world > 1 else None
         self.graph = None
-        self.launches_per_step = 5  # tables + append + encode, scan, select, attend, merge
+        self.launches_per_step = 4  # tables + append + encode, scan, select, attend + background + merge
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture

@@ -161,7 +161,9 @@ typedef struct pqhsa_ws_layout {
   size_t hitmap;       /* uint32 [R, unit_capacity, 4]  bit b of word (u, i): slot first(u) + 32 i + b reached the threshold */
   size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */
   size_t sel_off;      /* int64  [R, kcap]  element offset of their K/V rows in the cache  */
-  size_t partial;      /* float  [R, chunks, 130]  split-K partials (max, sum, acc)        */
+  size_t partial;      /* float  [R, chunks + 1, 130]  split-K partials (max, sum, acc): exact chunks, then the background */
+  size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
+  size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
   int32_t kcap;        /* row stride of sel_* */
   int32_t tail_cap;    /* row stride of tail_logit */
   int32_t chunks;      /* split-K partials per row */
@@ -222,8 +224,8 @@ enum pqhsa_stage {
   PQHSA_STAGE_LUT = 0,      /* table construction + threshold estimate */
   PQHSA_STAGE_SCAN = 1,     /* code scan                               */
   PQHSA_STAGE_SELECT = 2,   /* exact selection among the candidates    */
-  PQHSA_STAGE_ATTEND = 3,   /* exact attention partials (the gather)   */
-  PQHSA_STAGE_MERGE = 4     /* background + final merge                */
+  PQHSA_STAGE_ATTEND = 3,   /* exact attention (the gather), background, merge */
+  PQHSA_STAGE_MERGE = 4     /* nothing: kept for numbering, the merge runs inside stage 3 */
 };
 
 /* A whole decode step including the token append, in five launches:

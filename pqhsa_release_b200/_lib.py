@@ -51,7 +51,7 @@ class WsLayout(C.Structure):
         ("row_bin", C.c_size_t),
         ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
-        ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t),
+        ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t), ("row_ticket", C.c_size_t), ("work_counter", C.c_size_t),
         ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]
 

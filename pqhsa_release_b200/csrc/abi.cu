@@ -74,7 +74,9 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->hitmap = take(R * (size_t)p->unit_capacity * (kUnit / 32) * sizeof(uint32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
   o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
-  o->partial = take(R * (size_t)o->chunks * kPartial * sizeof(float));
+  o->partial = take(R * (size_t)(o->chunks + 1) * kPartial * sizeof(float));
+  o->row_ticket = take(R * sizeof(int32_t));
+  o->work_counter = take(2 * sizeof(unsigned long long));
   o->total_bytes = off;
 }
 
@@ -174,8 +176,7 @@ int pqhsa_attend_merge(const pqhsa_params* p, void* stream) {
   if (int rc = check_params(p, true, true, true)) return rc;
   pqhsa_ws_layout w;
   layout_of(p, &w);
-  if (int rc = launch_attend(*p, w, (cudaStream_t)stream)) return rc;
-  return launch_merge(*p, w, (cudaStream_t)stream);
+  return launch_attend(*p, w, (cudaStream_t)stream);
 }
 
 int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
@@ -186,8 +187,7 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
   if (int rc = launch_lut_build(*p, w, nullptr, st)) return rc;
   if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
   if (int rc = launch_select(*p, w, st)) return rc;
-  if (int rc = launch_attend(*p, w, st)) return rc;
-  return launch_merge(*p, w, st);
+  return launch_attend(*p, w, st);
 }
 
 int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const void* new_v, const int32_t* enc_count,
@@ -212,8 +212,7 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
   }
   if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
   if (int rc = launch_select(*p, w, st)) return rc;
-  if (int rc = launch_attend(*p, w, st)) return rc;
-  return launch_merge(*p, w, st);
+  return launch_attend(*p, w, st);
 }
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
@@ -228,7 +227,7 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
     case PQHSA_STAGE_SCAN: return launch_scan(*p, w, nullptr, st);
     case PQHSA_STAGE_SELECT: return launch_select(*p, w, st);
     case PQHSA_STAGE_ATTEND: return launch_attend(*p, w, st);
-    case PQHSA_STAGE_MERGE: return launch_merge(*p, w, st);
+    case PQHSA_STAGE_MERGE: return PQHSA_OK;  // the merge runs inside the attend kernel
     default: return set_error(PQHSA_E_SHAPE, "unknown stage %d", stage);
   }
 }

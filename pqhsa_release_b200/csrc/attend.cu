@@ -1,5 +1,6 @@
 // Exact attention over sink + local-window rows and the selected keys, read in
-// place from the (paged or contiguous) KV cache: split-K partials.
+// place from the (paged or contiguous) KV cache, the per-list background of the
+// unselected keys, and the merge of all of it into one softmax.
 //
 // Replaces pq_attend_partial_nw(_paged)_kernel
 // (pq_hsa/kernels/cuda/pq_fused_h20.cu:1225-1753); the arithmetic is the
@@ -18,6 +19,17 @@
 //      are requested before the first is consumed;
 //   3. online softmax in the base-2 domain per half-warp; halves and warps are
 //      merged at the end and one (max, sum, acc[128]) partial is written.
+//
+// Background.  One more item per query row turns the scan's per-unit (max, sum exp) pairs -
+// selected keys already taken out by the selection kernel - and the tail logits into list
+// masses and multiplies them with the lists' value means ([1 x L] x [L x 128]): a partial of
+// the same form.  This is the centroid-mode background of
+// pq_hsa/attention/sparse_attention.py:887-1012 in the list-space form argued for at
+// pq_hsa/kernels/cuda/pq_fused_h20.cu:2043-2058 (it replaces pq_attend_bg, :2150-2242).
+//
+// Merge.  Every finished item takes a ticket of its row; the CTA that takes the last one (no
+// waiting) folds the row's partials - out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M) - and
+// writes the output row (pq_attend_reduce_mw, :2244-2402).
 #include "common.cuh"
 
 namespace pqhsa {
@@ -35,9 +47,20 @@ struct AttendArgs {
   const int32_t* state;
   const int32_t* row_info;
   const long long* sel_off;
-  float* partial;
+  float* partial;  // [R, chunks + 1, kPartial]: the exact chunks, then the background
   int R, G, kcap, chunks, sink;
   float scale;
+  // background and merge
+  void* out;
+  const void* vmeans;
+  const uint16_t* list_ids;
+  const uint16_t* unit_list;
+  const float* unit_max;
+  const float* unit_sum;
+  const float* tail_logit;
+  int32_t* row_ticket;  // [R], zero between launches
+  unsigned long long* work_counter;  // [2]: next item, CTAs that have left; zero between launches
+  int cap, ucap, tail_cap, num_lists;
 };
 
 template <typename E> struct RawRow;  // 8 elements of a K/V row as loaded
@@ -68,26 +91,138 @@ __device__ __forceinline__ void cvt_row(const RawRow<__half>& r, float (&v)[8]) 
   unpack8(r.a, static_cast<const __half*>(nullptr), v);
 }
 
+constexpr int kBgGroups = kAttThreads / 16;  // 16 threads x 8 dims cover one value-mean row
+
+// The background partial of one query row (all kAttThreads threads): list masses from the per-unit
+// (max, sum) pairs and the unselected tail logits, then mass x value means.
+template <typename E>
+__device__ __forceinline__ void background_item(const AttendArgs& a, int row, int s, const StreamGeom& geo, float* pout,
+                                                float* mass, float (*gacc)[kD], float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* umax = a.unit_max + (size_t)row * a.ucap;
+  const float* usum = a.unit_sum + (size_t)row * a.ucap;
+  const float* tl = a.tail_logit + (size_t)row * a.tail_cap;
+  for (int i = tid; i < kLMax; i += kAttThreads) mass[i] = 0.f;
+  // reference of the partial: the largest unit maximum / tail logit, base-2 domain
+  float m = kNegInf;
+  for (int u = tid; u < geo.n_units; u += kAttThreads) m = fmaxf(m, umax[u]);
+  for (int t = tid; t < geo.n_tail; t += kAttThreads) m = fmaxf(m, tl[t]);
+  m = warp_max(m * kLog2e);
+  __syncthreads();  // also: the previous item is done with the shared arrays, mass[] is zero
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  float M = red[0];
+#pragma unroll
+  for (int w = 1; w < kAttWarps; ++w) M = fmaxf(M, red[w]);
+  float tot = 0.f;
+  if (M != kNegInf) {
+    for (int u = tid; u < geo.n_units; u += kAttThreads) {
+      const float v = usum[u] * ex2(fmaf(umax[u], kLog2e, -M));
+      atomicAdd(&mass[a.unit_list[(size_t)s * a.ucap + u]], v);
+      tot += v;
+    }
+    for (int t = tid; t < geo.n_tail; t += kAttThreads) {
+      const float x = tl[t];
+      if (x != kNegInf) {  // -inf marks a selected tail slot
+        const float v = ex2(fmaf(x, kLog2e, -M));
+        atomicAdd(&mass[a.list_ids[(size_t)s * a.cap + geo.n_sorted + t]], v);
+        tot += v;
+      }
+    }
+  }
+  tot = warp_sum(tot);
+  __syncthreads();  // red[] has been read; mass[] is complete after the next barrier
+  if (lane == 0) red[warp] = tot;
+  __syncthreads();
+  float L = 0.f;
+#pragma unroll
+  for (int w = 0; w < kAttWarps; ++w) L += red[w];
+  // sum_l mass[l] * vmean[l][:]: list = lg + kBgGroups * i, dims d8*8 .. d8*8+7, 8 rows in flight
+  const int d8 = tid & 15, lg = tid >> 4;
+  const E* vm = static_cast<const E*>(a.vmeans) + (size_t)s * a.num_lists * kD + d8 * 8;
+  float acc[8];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) acc[d] = 0.f;
+  for (int l0 = lg; l0 < a.num_lists; l0 += kBgGroups * 8) {
+    RawRow<E> vr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int l = l0 + kBgGroups * i;
+      if (l < a.num_lists) ld_row(vm + (size_t)l * kD, vr[i]); else zero_row(vr[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int l = l0 + kBgGroups * i;
+      float v[8];
+      cvt_row(vr[i], v);
+      const float w = l < a.num_lists ? mass[l] : 0.f;
+#pragma unroll
+      for (int d = 0; d < 8; ++d) acc[d] = fmaf(w, v[d], acc[d]);
+    }
+  }
+#pragma unroll
+  for (int d = 0; d < 8; ++d) gacc[lg][d8 * 8 + d] = acc[d];
+  __syncthreads();
+  float o = gacc[0][tid];
+#pragma unroll
+  for (int j = 1; j < kBgGroups; ++j) o += gacc[j][tid];
+  pout[2 + tid] = o;
+  if (tid == 0) {
+    pout[0] = M;
+    pout[1] = L;
+  }
+}
+
 template <typename E>
 __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs a) {
   __shared__ float wm[kAttWarps], wl[kAttWarps];
   __shared__ float wacc[kAttWarps][kD];
+  __shared__ float mass[kLMax];
+  __shared__ float gacc[kBgGroups][kD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int half = lane >> 4, l16 = lane & 15;
   const E* kb = static_cast<const E*>(a.k_base);
   const E* vb = static_cast<const E*>(a.v_base);
-  const long long items = (long long)a.R * a.chunks;
+  const int slots = a.chunks + 1;  // partials per row
+  const long long items = (long long)a.R * slots;
 
-  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-    const int c = (int)(item / a.R);
+  // Items are handed out by a counter (a CTA that drew a long item draws fewer): first the rows'
+  // background items (long dependent chains), then the chunks row by row, so that rows finish - and
+  // get merged - one after the other instead of all at the very end.  A CTA asks for its next item
+  // before it works on the current one.
+  __shared__ long long item_s;
+  if (tid == 0) item_s = (long long)atomicAdd(a.work_counter, 1ull);
+  __syncthreads();
+  long long item = item_s;
+  while (item < items) {
+    __syncthreads();  // everybody has read item_s
+    long long nxt = 0;
+    if (tid == 0) nxt = (long long)atomicAdd(a.work_counter, 1ull);  // used at the end of the item: the round trip is hidden
+    const bool is_bg = item < a.R;
     const int row = (int)(item % a.R);
+    const int c = is_bg ? a.chunks : (int)(item / a.R) - 1;
     const int s = row / a.G;
     const int32_t* st = a.state + (size_t)s * kST;
     const StreamGeom geo = stream_geom(st, a.sink);
     const int F = geo.full;
     const int K = a.row_info[(size_t)row * kRI + PQHSA_RI_K];
     const int total = F + K;
-    if (c * kChunk >= total) continue;  // uniform per block
+    const int nchunks = (total + kChunk - 1) / kChunk;
+    float* pout = a.partial + ((size_t)row * slots + c) * kPartial;
+    if (c < a.chunks && c >= nchunks) {  // uniform per block: an empty chunk
+      if (tid == 0) {
+        pout[0] = kNegInf;
+        pout[1] = 0.f;
+        item_s = nxt;
+      }
+      __syncthreads();
+      item = item_s;
+      continue;
+    }
+
+    if (c == a.chunks) {
+      background_item<E>(a, row, s, geo, pout, mass, gacc, wm);
+    } else {
 
     // 1. element offset of this lane's entry
     const int e = c * kChunk + warp * 32 + lane;
@@ -195,14 +330,68 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
         L = fmaf(wl[w], f, L);
         A = fmaf(wacc[w][tid], f, A);
       }
-      float* out = a.partial + ((size_t)row * a.chunks + c) * kPartial;
-      out[2 + tid] = A;
+      pout[2 + tid] = A;
       if (tid == 0) {
-        out[0] = M;  // base-2 domain: scale * log2(e) * q.k
-        out[1] = L;
+        pout[0] = M;  // base-2 domain: scale * log2(e) * q.k
+        pout[1] = L;
       }
     }
+    }  // chunk item
+
+    if (tid == 0) item_s = nxt;
+    __syncthreads();
+    item = item_s;
   }
+  // the CTA that leaves last puts the counters back to zero for the next launch
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(a.work_counter + 1, 1ull) == (unsigned long long)gridDim.x - 1) {
+      a.work_counter[0] = 0ull;
+      a.work_counter[1] = 0ull;
+    }
+  }
+}
+
+// One CTA per query row folds the row's partials (exact chunks + background) into the output row:
+// out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M)  (pq_attend_reduce_mw,
+// pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).
+template <typename E>
+__global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int slots = a.chunks + 1;  // <= kD, checked at launch; empty chunks carry (-inf, 0)
+  const float* pp = a.partial + (size_t)row * slots * kPartial;
+  __shared__ float fs[kD], red[kD / 32];
+  // thread p takes partial p's (max, sum): one round trip for all of them
+  const float mp = tid < slots ? pp[(size_t)tid * kPartial] : kNegInf;
+  const float lp = tid < slots ? pp[(size_t)tid * kPartial + 1] : 0.f;
+  float M = warp_max(mp);
+  if ((tid & 31) == 0) red[tid >> 5] = M;
+  __syncthreads();
+  M = red[0];
+#pragma unroll
+  for (int w = 1; w < kD / 32; ++w) M = fmaxf(M, red[w]);
+  const float f = (mp == kNegInf) ? 0.f : ex2(mp - M);
+  fs[tid] = f;
+  float L = warp_sum(lp * f);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = L;
+  __syncthreads();
+  L = red[0];
+#pragma unroll
+  for (int w = 1; w < kD / 32; ++w) L += red[w];
+  // ... and one for the accumulators (32 partials per batch)
+  float A = 0.f;
+  for (int p0 = 0; p0 < slots; p0 += 32) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int p = p0 + i;
+      v[i] = (p < slots && fs[p] != 0.f) ? pp[(size_t)p * kPartial + 2 + tid] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) A = fmaf(v[i], p0 + i < slots ? fs[p0 + i] : 0.f, A);
+  }
+  static_cast<E*>(a.out)[(size_t)row * kD + tid] = from_f<E>(A / fmaxf(L, 1.17549435e-38f));
 }
 
 template <typename E>
@@ -214,12 +403,15 @@ static int launch_attend_t(const AttendArgs& a, cudaStream_t st) {
       n = 4;
     per_sm = n;
   }
-  const long long items = (long long)a.R * a.chunks;
+  const long long items = (long long)a.R * (a.chunks + 1);
   long long grid = (long long)sm_count() * per_sm;
   if (grid > items) grid = items;
   if (grid < 1) grid = 1;
   attend_kernel<E><<<(unsigned)grid, kAttThreads, 0, st>>>(a);
-  return check_launch("attend");
+  if (int rc = check_launch("attend")) return rc;
+  if (a.chunks + 1 > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + 1, kD);
+  combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
+  return check_launch("combine");
 }
 
 int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
@@ -239,6 +431,19 @@ int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.chunks = w.chunks;
   a.sink = p.sink_tokens;
   a.scale = p.scale;
+  a.out = p.out;
+  a.vmeans = p.vmeans;
+  a.list_ids = static_cast<const uint16_t*>(p.list_ids);
+  a.unit_list = static_cast<const uint16_t*>(p.unit_list);
+  a.unit_max = reinterpret_cast<const float*>(ws + w.unit_max);
+  a.unit_sum = reinterpret_cast<const float*>(ws + w.unit_sum);
+  a.tail_logit = reinterpret_cast<const float*>(ws + w.tail_logit);
+  a.row_ticket = reinterpret_cast<int32_t*>(ws + w.row_ticket);
+  a.work_counter = reinterpret_cast<unsigned long long*>(ws + w.work_counter);
+  a.cap = p.slot_capacity;
+  a.ucap = p.unit_capacity;
+  a.tail_cap = w.tail_cap;
+  a.num_lists = p.num_lists;
   PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E>(a, st)));
   return PQHSA_OK;
 }

@@ -181,17 +181,33 @@ __global__ void __launch_bounds__(kFinThreads) finish_kernel(const FinishArgs a)
     // normal path: the candidates sit in registers, kFinPer per thread
     uint32_t kreg[kFinPer];
     int sreg[kFinPer];
+    // four candidates per thread at a time: their gathers (code, norm) travel together, then the arithmetic
 #pragma unroll
-    for (int j = 0; j < kFinPer; ++j) {
-      const int i = j * kFinThreads + tid;
-      kreg[j] = 0u;
-      sreg[j] = 0;
-      if (j * kFinThreads < C) {  // block-uniform: rounds past the list cost nothing
+    for (int j0 = 0; j0 < kFinPer; j0 += 4) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        kreg[j0 + jj] = 0u;
+        sreg[j0 + jj] = 0;
+      }
+      if (j0 * kFinThreads >= C) continue;  // block-uniform: rounds past the list cost nothing
+      uint32_t code[4], ent[4];
+      float kn[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int i = (j0 + jj) * kFinThreads + tid;
+        ent[jj] = i < C ? cslot[i] : 0xFFFFFFFFu;
+        code[jj] = 0u;
+        kn[jj] = 0.f;
         if (i < C) {
-          kreg[j] = key(i);
-          sreg[j] = slot_of(i);
+          sreg[j0 + jj] = (int)(ent[jj] & kSlotMask);
+          code[jj] = __ldg(codes + sreg[j0 + jj]);
+          kn[jj] = to_f(norms[sreg[j0 + jj]]);
         }
       }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+        if (ent[jj] != 0xFFFFFFFFu)
+          kreg[j0 + jj] = float_key(finish_logit(pq_sum_row(lut_s, code[jj]), lsc_s[ent[jj] >> kSlotBits], kn[jj]));
     }
     if (!take_all) {
       const int ties = block_radix_threshold_regs<kFinThreads, kFinPer>(kreg, K, rsh2, T, t);
