@@ -323,7 +323,13 @@ def run_b200(args):
     hl = wl.kv_heads // world
     e = 4 if wl.dtype == torch.float32 else 2
     f_rows = wl.context - wl.retrieval_len()
-    attend_bytes = wl.batch * (hl * wl.group * wl.topk() + hl * f_rows) * 2 * wl.head_dim * e
+    # the attend kernel's algorithmic bytes: K selected + F sink/local K and V rows (sink/local rows once per
+    # KV head) and the value means of the background
+    attend_bytes = wl.batch * (hl * wl.group * wl.topk() + hl * f_rows) * 2 * wl.head_dim * e \
+        + wl.batch * hl * wl.num_lists * wl.head_dim * e
+    # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the ncu capture summarised in
+    # profiles/attend_kernel_c2_ncu.md (same workload, one GPU); no capture exists for other shapes
+    traffic = 165_636_096 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
     attend_s = stage_ms[3] / 1e3
     achieved = attend_bytes / attend_s / 1e9
     line = {
@@ -342,7 +348,7 @@ def run_b200(args):
                           "peak_gbs": peak, "frac": step_bytes / world / (total_ms / K / 1e3) / 1e9 / peak,
                           "of": peak_kind},
         "roofline": {"kernel": "attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "of": peak_kind,
+                     "frac": achieved / peak, "traffic": traffic, "of": peak_kind,
                      "algorithmic_bytes_per_launch": attend_bytes},
         "stages_us": {n: round(1e3 * m, 2) for n, m in zip(stage_names, stage_ms)},
         "e2e": {"value": e2e_value, "unit": UNIT, "us_per_layer_step": 1e3 * e2e_ms / K,

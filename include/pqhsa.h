@@ -188,15 +188,18 @@ const char* pqhsa_last_error_string(void);
 size_t pqhsa_workspace_bytes(const pqhsa_params* p);
 int pqhsa_workspace_layout(const pqhsa_params* p, pqhsa_ws_layout* out);
 
-/* (1) Per-query, per-head table construction: lut and list_scores in the
- * workspace, plus the per-row candidate threshold estimated from a stratified
- * sample of the stream's keys.  Replaces pq_lut_prep
- * (pq_fused_h20.cu:2975-3051) and ProductQuantizer.compute_lut + the coarse
- * bias (pq_hsa/index/pq.py:190-217, pq_hsa/index/ivfpq.py:1179-1190).  Also
- * clears the per-step counters and resolves K per row. */
+/* (1) Per-query, per-head table construction: lut, its byte-pair form and
+ * list_scores in the workspace, plus the per-row candidate threshold estimated
+ * from a stratified sample of the stream's keys (p->sample, or gathered from the
+ * index when that is NULL).  Replaces pq_lut_prep (pq_fused_h20.cu:2975-3051),
+ * _build_pair_tables (pq_hsa/kernels/triton_lut_scan_h20.py:127-171) and
+ * ProductQuantizer.compute_lut + the coarse bias (pq_hsa/index/pq.py:190-217,
+ * pq_hsa/index/ivfpq.py:1179-1190).  The workspace must be all zero before its
+ * first use (the kernels keep their counters in it and leave them at zero). */
 int pqhsa_lut_build(const pqhsa_params* p, void* stream);
 
-/* (2)+(3)+(5a) Code scan with per-unit log-sum-exp and exact top-K selection.
+/* (2)+(3)+(5a) Code scan with per-unit log-sum-exp, one bit per (row, slot) for
+ * "logit reached the threshold", and exact top-K selection among those slots.
  * Needs pqhsa_lut_build first.  Leaves sel_slot / sel_off / row_info / unit_*
  * in the workspace.  Replaces the pair-fused Triton scan
  * (pq_hsa/kernels/triton_lut_scan_h20.py:1197-1291), list_exp_sums_sorted
@@ -224,11 +227,11 @@ enum pqhsa_stage {
   PQHSA_STAGE_LUT = 0,      /* table construction + threshold estimate */
   PQHSA_STAGE_SCAN = 1,     /* code scan                               */
   PQHSA_STAGE_SELECT = 2,   /* exact selection among the candidates    */
-  PQHSA_STAGE_ATTEND = 3,   /* exact attention (the gather), background, merge */
-  PQHSA_STAGE_MERGE = 4     /* nothing: kept for numbering, the merge runs inside stage 3 */
+  PQHSA_STAGE_ATTEND = 3,   /* exact attention partials (the gather) and the background partial */
+  PQHSA_STAGE_MERGE = 4     /* fold of the partials into the output rows              */
 };
 
-/* A whole decode step including the token append, in five launches:
+/* A whole decode step including the token append, in the five launches of pqhsa_decode_step:
  *   pqhsa_append_kv(new_k, new_v) + pqhsa_append_encode(enc_count, uniform_count) + pqhsa_decode_step
  * with the row write, the encode and the table construction running side by side in the first
  * kernel (they touch disjoint data; the stream counters change once all three are done).  Same

@@ -176,7 +176,8 @@ int pqhsa_attend_merge(const pqhsa_params* p, void* stream) {
   if (int rc = check_params(p, true, true, true)) return rc;
   pqhsa_ws_layout w;
   layout_of(p, &w);
-  return launch_attend(*p, w, (cudaStream_t)stream);
+  if (int rc = launch_attend(*p, w, (cudaStream_t)stream)) return rc;
+  return launch_merge(*p, w, (cudaStream_t)stream);
 }
 
 int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
@@ -187,7 +188,8 @@ int pqhsa_decode_step(const pqhsa_params* p, void* stream) {
   if (int rc = launch_lut_build(*p, w, nullptr, st)) return rc;
   if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
   if (int rc = launch_select(*p, w, st)) return rc;
-  return launch_attend(*p, w, st);
+  if (int rc = launch_attend(*p, w, st)) return rc;
+  return launch_merge(*p, w, st);
 }
 
 int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const void* new_v, const int32_t* enc_count,
@@ -212,7 +214,8 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
   }
   if (int rc = launch_scan(*p, w, nullptr, st)) return rc;
   if (int rc = launch_select(*p, w, st)) return rc;
-  return launch_attend(*p, w, st);
+  if (int rc = launch_attend(*p, w, st)) return rc;
+  return launch_merge(*p, w, st);
 }
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
@@ -227,7 +230,7 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
     case PQHSA_STAGE_SCAN: return launch_scan(*p, w, nullptr, st);
     case PQHSA_STAGE_SELECT: return launch_select(*p, w, st);
     case PQHSA_STAGE_ATTEND: return launch_attend(*p, w, st);
-    case PQHSA_STAGE_MERGE: return PQHSA_OK;  // the merge runs inside the attend kernel
+    case PQHSA_STAGE_MERGE: return launch_merge(*p, w, st);
     default: return set_error(PQHSA_E_SHAPE, "unknown stage %d", stage);
   }
 }

@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
 }
 
 template <typename E>
-static int launch_attend_t(const AttendArgs& a, cudaStream_t st) {
+static int launch_attend_t(const AttendArgs& a, bool combine, cudaStream_t st) {
   static int per_sm = 0;  // resident CTAs per SM of this instantiation
   if (per_sm == 0) {
     int n = 0;
@@ -407,14 +407,16 @@ static int launch_attend_t(const AttendArgs& a, cudaStream_t st) {
   long long grid = (long long)sm_count() * per_sm;
   if (grid > items) grid = items;
   if (grid < 1) grid = 1;
+  if (combine) {
+    if (a.chunks + 1 > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + 1, kD);
+    combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
+    return check_launch("combine");
+  }
   attend_kernel<E><<<(unsigned)grid, kAttThreads, 0, st>>>(a);
-  if (int rc = check_launch("attend")) return rc;
-  if (a.chunks + 1 > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + 1, kD);
-  combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
-  return check_launch("combine");
+  return check_launch("attend");
 }
 
-int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
+static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout& w, bool combine, cudaStream_t st) {
   char* ws = static_cast<char*>(p.workspace);
   AttendArgs a;
   a.q = p.q;
@@ -444,8 +446,15 @@ int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
   a.num_lists = p.num_lists;
-  PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E>(a, st)));
+  PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E>(a, combine, st)));
   return PQHSA_OK;
+}
+
+int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
+  return launch_attend_or_combine(p, w, false, st);
+}
+int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
+  return launch_attend_or_combine(p, w, true, st);
 }
 
 }  // namespace pqhsa

@@ -100,3 +100,69 @@ def test_forced_fallback_is_still_exact():
     pool, _, _ = pool_from_case(case, select_margin=-9.0)
     info = _check_case(case, pool)
     assert int(info[:, 4].sum()) >= 1, "expected at least one row to take the fallback"
+
+
+def test_full_context_properties_against_the_dumped_scores():
+    """BASELINE's full context (131072 keys, 512 lists, G = 4, bf16) on two streams, too large for
+    the CPU oracle: size-independent properties instead.  The selected set must be exactly the K
+    largest of the logits the library itself dumps (same floats, ties to the lower slot), every
+    row's candidate count must lie between K and a small multiple of it without the fallback, and
+    the output must equal a plain fp32 softmax over [exact sink/local/selected rows, per-list
+    background] rebuilt here from those logits."""
+    import math
+
+    from pqhsa_release_b200 import workloads
+    from pqhsa_release_b200.config import paper_index_config
+    from pqhsa_release_b200.device_index import DeviceIndexPool
+    from pqhsa_release_b200.index_build import build_index_batch
+
+    wl = workloads.WORKLOADS["c2"]
+    dev, ctx, H, G, D = "cuda", wl.context, 2, wl.group, 128
+    n0 = wl.retrieval_len()
+    sink = wl.sink_tokens
+    pool = DeviceIndexPool(num_streams=H, group=G, dtype=wl.dtype, device=dev, slot_capacity=n0 + 64,
+                           num_lists=wl.num_lists, sink_tokens=sink, local_window=wl.local_window,
+                           scale=1.0 / math.sqrt(D), top_fraction=wl.top_fraction, tail_capacity=64)
+    kc = torch.zeros(1, H, ctx + 8, D, dtype=wl.dtype, device=dev)
+    vc = torch.zeros_like(kc)
+    for h in range(H):
+        k, v = workloads.mixture_kv(4242 + h, 1, ctx, dtype=wl.dtype, device=dev)
+        kc[0, h, :ctx], vc[0, h, :ctx] = k[0], v[0]
+    idx = build_index_batch(kc[0, :, sink : sink + n0], vc[0, :, sink : sink + n0], paper_index_config(num_lists=wl.num_lists))
+    for h in range(H):
+        pool.load_stream(h, idx[h], seq_len=ctx, req=0, kv_head=h)
+    pool.bind_kv_contiguous(kc, vc)
+    q = workloads.planted_queries(99, kc[0, :, :ctx], G).reshape(H, G, D).contiguous()
+    out = pool.decode_step(q).float()
+    torch.cuda.synchronize()
+    info = pool.ws_view("row_info").clone()
+    scores = pool.scan_scores(q)
+    K = wl.topk()
+    assert int(info[:, 4].sum()) == 0 and (info[:, 0] == K).all() and (info[:, 3] == K).all()
+    assert (info[:, 2] >= K).all() and (info[:, 2] <= 3 * K).all()
+    scale = 1.0 / math.sqrt(D)
+    for h in range(H):
+        pos = pool.slot_pos[h, :n0].long()
+        lists = pool.list_ids[h, :n0].long() & 0xFFFF
+        keys, vals = kc[0, h].float(), vc[0, h].float()
+        vm = pool.vmeans[h].float()
+        for g in range(G):
+            row = h * G + g
+            x = scores[row, :n0]
+            # exact top-K of the same floats: ties at the boundary go to the lower slot
+            order = torch.sort(x, descending=True, stable=True).indices[:K]
+            want = torch.sort(pos[order]).values
+            got = pool.selected_positions(row)
+            assert torch.equal(got, want), f"row {row}: selected set differs from the top-K of the dumped logits"
+            sel = torch.zeros(n0, dtype=torch.bool, device=dev)
+            sel[order] = True
+            full = torch.cat([torch.arange(sink, device=dev), torch.arange(sink + n0, ctx, device=dev), pos[order]])
+            qv = q[h, g].float()
+            exact = (keys[full] @ qv) * scale
+            m = torch.maximum(exact.max(), x.max())
+            w_exact = torch.exp(exact - m)
+            w_bg = torch.exp(x - m) * (~sel)
+            mass = torch.zeros(wl.num_lists, device=dev).index_add_(0, lists, w_bg)
+            ref = (w_exact @ vals[full] + mass @ vm) / (w_exact.sum() + mass.sum())
+            err = float((out[h, g] - ref).norm() / ref.norm())
+            assert err <= 4e-3, f"row {row}: output differs from the rebuilt softmax by {err:.2e}"
