@@ -294,7 +294,10 @@ def run_b200(args):
     h2d = sum(t[0].numel() * t[0].element_size() for t in (hq, hk, hv))
     d2h = hout.numel() * hout.element_size()
 
-    # ---- per-stage breakdown (one pass, L2 flushed before every stage) -----
+    # ---- per-kernel durations inside a step --------------------------------
+    # The five launches of a step are issued one by one with an event between them, right behind the L2
+    # flush: the flush is still running while they are enqueued, so every event pair brackets exactly
+    # one kernel as it runs inside the step (cold L2 at the start, what the step itself left in L2 after).
     from pqhsa_release_b200 import _lib
 
     stage_names = ["lut_build", "scan", "select", "attend", "merge"]
@@ -302,12 +305,15 @@ def run_b200(args):
     stage_ms = [0.0] * 5
     for r in range(reps):
         load_inputs(r)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        flush_l2()
+        evs[0].record()
         for sidx in range(5):
-            flush_l2()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); pool.run_stage(sidx, runner.q, runner.out); b.record()
-            torch.cuda.synchronize()
-            stage_ms[sidx] += a.elapsed_time(b) / reps
+            pool.run_stage(sidx, runner.q, runner.out)
+            evs[sidx + 1].record()
+        torch.cuda.synchronize()
+        for sidx in range(5):
+            stage_ms[sidx] += evs[sidx].elapsed_time(evs[sidx + 1]) / reps
     barrier()
 
     # ---- aggregate ----------------------------------------------------------
@@ -328,7 +334,7 @@ def run_b200(args):
     attend_bytes = wl.batch * (hl * wl.group * wl.topk() + hl * f_rows) * 2 * wl.head_dim * e \
         + wl.batch * hl * wl.num_lists * wl.head_dim * e
     # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the ncu capture summarised in
-    # profiles/attend_kernel_c2_ncu.md (same workload, one GPU); no capture exists for other shapes
+    # profiles/decode_step_c2_ncu_full.md (same workload, one GPU); no capture exists for other shapes
     traffic = 165_636_096 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
     attend_s = stage_ms[3] / 1e3
     achieved = attend_bytes / attend_s / 1e9
