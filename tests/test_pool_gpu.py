@@ -190,3 +190,77 @@ def test_fused_step_equals_the_three_calls(dtype):
             assert torch.equal(a.selected_positions(row), b.selected_positions(row))
         assert float((got.float() - want.float()).abs().max()) <= 2e-3 * float(want.float().abs().max())
         assert n == 5000 - 4 - 128 + step + 1
+
+
+def test_paged_ragged_batch_64_decode_steps():
+    """The shape of the plugin workload (16-token pages, permuted block table, requests of different
+    lengths, 64 consecutive decode steps each appending one K/V row per head and encoding the key
+    that leaves the local window), contexts scaled down so that the CPU oracle can follow every step.
+    The library writes the new rows into the pages itself (fused step).  Codes and list ids of every
+    encoded key bit for bit (a differing assignment must be a rare numerical tie), outputs against
+    the oracle every 8 steps and at the end."""
+    from helpers import round_to
+    from pqhsa_release_b200.device_index import DeviceIndexPool, StreamIndexTensors
+    from oracle.pqhsa_oracle import list_value_means
+
+    dtype, Hkv, G, bs, steps = torch.bfloat16, 2, 4, 16, 64
+    ctxs = [5200, 6900, 4700]
+    B, smax = len(ctxs), max(ctxs)
+    case = make_case(B=B, Hkv=Hkv, G=G, S=smax, L=128, dtype=dtype, seed=41, interval=1, strategy="incremental",
+                     contexts=ctxs)
+    dev = "cuda"
+    blocks_per_req = (smax + steps + bs - 1) // bs
+    nblk = B * blocks_per_req + 7
+    gen = torch.Generator().manual_seed(3)
+    table = torch.randperm(nblk, generator=gen)[: B * blocks_per_req].to(torch.int32).reshape(B, blocks_per_req).to(dev)
+    kv_cache = torch.zeros(2, nblk, bs, Hkv, 128, dtype=dtype, device=dev)
+    for b, n in enumerate(ctxs):
+        t = torch.arange(n, device=dev)
+        blk, off = table[b, t // bs].long(), t % bs
+        kv_cache[0, blk, off] = case.keys[b, :, :n].to(dev).permute(1, 0, 2)
+        kv_cache[1, blk, off] = case.values[b, :, :n].to(dev).permute(1, 0, 2)
+    pool = DeviceIndexPool(num_streams=B * Hkv, group=G, dtype=dtype, device=dev, slot_capacity=smax + steps + 64,
+                           num_lists=case.L, sink_tokens=case.sink, local_window=case.local, scale=1.0 / 128 ** 0.5,
+                           top_fraction=case.frac, tail_capacity=steps + 8)
+    pool.bind_kv_paged(kv_cache, table)
+    for b in range(B):
+        for h in range(Hkv):
+            st = case.streams[b * Hkv + h]
+            ix = st.index
+            s0, r0 = st.bounds()
+            _, vsum, vcnt = list_value_means(ix.list_ids, st.values[s0:r0], ix.coarse.shape[0])
+            pool.load_stream(b * Hkv + h, StreamIndexTensors(ix.packed, ix.list_ids, ix.norms, ix.coarse, ix.codebooks,
+                                                              st.value_means, vsum, vcnt),
+                             seq_len=st.length, req=b, kv_head=h)
+    S = B * Hkv
+    q0 = case.queries.reshape(S, G, 128)
+    mism = total = 0
+    for step in range(steps):
+        nk = (torch.randn(S, 128, generator=gen) * 1.5).to(dtype)
+        nv = torch.randn(S, 128, generator=gen).to(dtype)
+        q = (q0.float() * (1.0 + 0.01 * step) + 0.02 * torch.randn(S, G, 128, generator=gen)).to(dtype)
+        out = pool.decode_step_append(q.to(dev).contiguous(), nk.to(dev).contiguous(), nv.to(dev).contiguous(), encode=1)
+        torch.cuda.synchronize()
+        for s, st in enumerate(case.streams):
+            st.append(nk[s].float(), nv[s].float())
+            st.index.norms[-1] = round_to(st.index.norms[-1:], dtype)[0]
+            d = pool.export_stream(s)
+            total += 1
+            if int(d["list_ids"][-1]) != int(st.index.list_ids[-1]) or not torch.equal(d["packed_codes"][-1].cpu(), st.index.packed[-1]):
+                mism += 1
+                st.index.list_ids[-1] = int(d["list_ids"][-1])
+                st.index.packed[-1] = d["packed_codes"][-1].cpu()
+            lists = st.index.coarse.shape[0]
+            st.value_means = pool.vmeans[s, :lists].float().cpu().clone()
+            assert int(pool.state[s, 2]) == st.length  # SEQ_LEN on the device
+        if step % 8 == 7 or step == steps - 1:
+            o = out.float().cpu()
+            for s, st in enumerate(case.streams):
+                det = st.forward_detail(q[s].float())
+                for g in range(G):
+                    assert_output_close(o[s, g], det.output[g], dtype, f"step {step} stream {s} row {g}")
+    assert mism <= max(1, total // 20), f"{mism} of {total} encodes differ from the oracle"
+    # the rows the library wrote are in the pages
+    b, n = 1, ctxs[1] + steps
+    t = torch.arange(ctxs[1], n, device=dev)
+    assert bool((kv_cache[0, table[b, t // bs].long(), t % bs].float().abs().sum(-1) > 0).all())
