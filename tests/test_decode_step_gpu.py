@@ -102,8 +102,10 @@ def test_forced_fallback_is_still_exact():
     assert int(info[:, 4].sum()) >= 1, "expected at least one row to take the fallback"
 
 
-def test_full_context_properties_against_the_dumped_scores():
-    """BASELINE's full context (131072 keys, 512 lists, G = 4, bf16) on two streams, too large for
+@pytest.mark.parametrize("name, H", [("c2", 2), ("c4", 1)])
+def test_full_context_properties_against_the_dumped_scores(name, H):
+    """BASELINE's full contexts (c2: 131072 keys, G = 4; c4: 262144 keys, G = 8, where a row has
+    more candidates than the selection kernel keeps in registers; 512 lists, bf16), too large for
     the CPU oracle: size-independent properties instead.  The selected set must be exactly the K
     largest of the logits the library itself dumps (same floats, ties to the lower slot), every
     row's candidate count must lie between K and a small multiple of it without the fallback, and
@@ -116,8 +118,8 @@ def test_full_context_properties_against_the_dumped_scores():
     from pqhsa_release_b200.device_index import DeviceIndexPool
     from pqhsa_release_b200.index_build import build_index_batch
 
-    wl = workloads.WORKLOADS["c2"]
-    dev, ctx, H, G, D = "cuda", wl.context, 2, wl.group, 128
+    wl = workloads.WORKLOADS[name]
+    dev, ctx, G, D = "cuda", wl.context, wl.group, 128
     n0 = wl.retrieval_len()
     sink = wl.sink_tokens
     pool = DeviceIndexPool(num_streams=H, group=G, dtype=wl.dtype, device=dev, slot_capacity=n0 + 64,
