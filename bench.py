@@ -183,11 +183,21 @@ class StepRunner:
         self.nv = self.inbuf[S * G * D + S * D :].view(S, D)
         self.out = torch.zeros(S, G, D, dtype=wl.dtype, device=dev)
         self.gathered = torch.zeros(world, S, G, D, dtype=wl.dtype, device=dev) if world > 1 else None
+        self.exchange, self.steps_done = None, 0
+        if world > 1 and os.environ.get("PQHSA_EXCHANGE", "peer") == "peer":
+            try:  # rows stored straight into every rank's buffer by the combine kernel; NCCL otherwise
+                from pqhsa_release_b200.parallel import PeerExchange
+
+                self.exchange = PeerExchange(pool)
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench] peer exchange unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
+                self.exchange = None
         self.graph = None
         self.launches_per_step = 4  # tables + append + encode, scan, select, attend + background + merge
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture
+            self.steps_done += 1
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
@@ -197,7 +207,9 @@ class StepRunner:
     def _body(self):
         p = self.pool
         p.decode_step_append(self.q, self.nk, self.nv, encode=1, out=self.out)
-        if self.gathered is not None:
+        if self.exchange is not None:
+            self.exchange.wait()
+        elif self.gathered is not None:
             torch.distributed.all_gather_into_tensor(self.gathered, self.out)
 
     def step(self):
@@ -206,6 +218,13 @@ class StepRunner:
         else:
             self.graph.replay()
             self.pool.note_replayed(appends=1, encodes=1)
+        self.steps_done += 1
+
+    def result(self):
+        """The step's output on this rank: all ranks' rows when sharded."""
+        if self.exchange is not None:
+            return self.exchange.result(self.steps_done)
+        return self.gathered if self.gathered is not None else self.out
 
 
 def run_b200(args):
@@ -259,6 +278,13 @@ def run_b200(args):
     for i in range(W):
         load_inputs(i); flush_l2(); runner.step()
     barrier()
+    if runner.exchange is not None:
+        # once, outside the timed region: what arrived through the peer stores equals an NCCL all-gather
+        check = torch.empty(world, *runner.out.shape, dtype=runner.out.dtype, device=device)
+        torch.distributed.all_gather_into_tensor(check.view(world * runner.out.shape[0], *runner.out.shape[1:]), runner.out)
+        torch.cuda.synchronize()
+        if runner.exchange.timed_out() or not torch.equal(check.view(world, -1, wl.head_dim), runner.result()):
+            raise SystemExit("peer exchange check failed: rows differ from the NCCL all-gather (or the flag wait ran out)")
     n_start = int(pool.h_sorted[0] + pool.h_tail[0])
     sampler = ClockSampler(physical_gpu_index(local_rank))
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
@@ -274,7 +300,7 @@ def run_b200(args):
 
     # ---- end to end through the public call with host buffers --------------
     hin = [torch.cat([qs[i].reshape(-1), nks[i].reshape(-1), nvs[i].reshape(-1)]).cpu().pin_memory() for i in range(nq)]
-    res_t = runner.gathered if world > 1 else runner.out
+    res_t = runner.result()
     hout = torch.empty(res_t.shape, dtype=res_t.dtype).pin_memory()
     ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     for i in range(3):
@@ -285,7 +311,7 @@ def run_b200(args):
         ev2[i][0].record()
         runner.inbuf.copy_(hin[i % nq], non_blocking=True)  # q, new K rows, new V rows of the step
         runner.step()
-        hout.copy_(res_t, non_blocking=True)
+        hout.copy_(runner.result(), non_blocking=True)
         ev2[i][1].record()
     barrier()
     e2e_ms = sum(a.elapsed_time(b) for a, b in ev2)
@@ -345,7 +371,9 @@ def run_b200(args):
             "workload": wl.name, "batch": wl.batch, "kv_heads": wl.kv_heads, "group": wl.group,
             "context": wl.context, "indexed_keys_per_stream": n_start, "topk": wl.topk(), "lists": wl.num_lists,
             "kv_layout": "contiguous", "index_update": "incremental, 1 key per step",
-            "parallelism": f"kv-head shard x{world}", "l2": f"flushed between timed steps ({args.flush} of 256 MiB)",
+            "parallelism": f"kv-head shard x{world}",
+            "exchange": "none" if world == 1 else ("peer stores from the combine kernel + flag wait" if runner.exchange is not None
+                                                   else "nccl all-gather"), "l2": f"flushed between timed steps ({args.flush} of 256 MiB)",
             "cuda_graph": not args.no_graph,
         },
         "step_roofline": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / world / (total_ms / K / 1e3) / 1e9,

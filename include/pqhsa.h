@@ -135,6 +135,19 @@ typedef struct pqhsa_params {
   int32_t block_size;
   int64_t stride_block, stride_head, stride_row;
 
+  /* Output exchange between the GPUs of a node (all zero / NULL on one GPU).  With peer_world > 1 the
+   * combine kernel also stores every output row into the gather buffer of every rank, row r of this
+   * rank at element ((parity * peer_world + peer_rank) * R + r) * 128 of that rank's buffer (parity =
+   * step count & 1: two buffers, so a rank that is one step ahead never overwrites what a peer still
+   * reads), and then raises this rank's flag on every rank.  pqhsa_wait_peers makes the stream wait
+   * for the flags of all ranks.  All ranks must run the same sequence of steps. */
+  const void *peer_out;    /* device array of peer_world pointers: every rank's gather buffer,
+                              E [2, peer_world, R, 128], mapped into this process (peer memory) */
+  const void *peer_flags;  /* device array of peer_world pointers: every rank's int32 [peer_world] flags */
+  void *peer_seq;          /* device int32 [2] of this rank: steps exchanged so far, error flag */
+  int32_t peer_world;
+  int32_t peer_rank;
+
   const void *q;           /* E [S, G, 128]: query heads h*G .. h*G+G-1 of KV head h */
   void *out;               /* E [S, G, 128] */
   void *workspace;         /* >= pqhsa_workspace_bytes(), 256-byte aligned */
@@ -164,6 +177,7 @@ typedef struct pqhsa_ws_layout {
   size_t partial;      /* float  [R, chunks + 1, 130]  split-K partials (max, sum, acc): exact chunks, then the background */
   size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
   size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
+  size_t combine_ticket; /* int32 [1]     finished CTAs of the combine kernel (0 between launches)          */
   int32_t kcap;        /* row stride of sel_* */
   int32_t tail_cap;    /* row stride of tail_logit */
   int32_t chunks;      /* split-K partials per row */
@@ -243,6 +257,15 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
                              const int32_t* enc_count, int32_t uniform_count, void* stream);
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
+
+/* Multi-GPU: make `stream` wait until every rank's flag in this rank's flag array has reached this
+ * rank's step count, i.e. until all output rows of the last step have arrived in this rank's gather
+ * buffer (the buffer of parity (steps - 1) & 1).  One warp polls with a limit of about a second;
+ * when it runs out, peer_seq[1] is set to 1 and the kernel returns (the context stays usable).
+ * Replaces the NCCL all-gather that would otherwise follow the step: the rows travel as plain
+ * stores over NVLink from inside the combine kernel.  The reference has no counterpart (it runs
+ * under vLLM's own tensor parallelism). */
+int pqhsa_wait_peers(const pqhsa_params* p, void* stream);
 
 /* Write one new K/V row per stream into the cache at position seq_len and bump
  * seq_len (contiguous or paged addressing as above).  new_k/new_v: E [S, 128].

@@ -39,6 +39,8 @@ class Params(C.Structure):
         ("k_base", C.c_void_p), ("v_base", C.c_void_p), ("block_table", C.c_void_p),
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
+        ("peer_out", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_seq", C.c_void_p),
+        ("peer_world", C.c_int32), ("peer_rank", C.c_int32),
         ("q", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
@@ -51,7 +53,7 @@ class WsLayout(C.Structure):
         ("row_bin", C.c_size_t),
         ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
-        ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t), ("row_ticket", C.c_size_t), ("work_counter", C.c_size_t),
+        ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t), ("row_ticket", C.c_size_t), ("work_counter", C.c_size_t), ("combine_ticket", C.c_size_t),
         ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]
 
@@ -65,6 +67,7 @@ EXPORTS = {
     "pqhsa_scan_select": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_attend_merge": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "pqhsa_wait_peers": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step_append": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_run_stage": (C.c_int, [C.POINTER(Params), C.c_int, C.c_void_p]),
     "pqhsa_append_kv": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p]),

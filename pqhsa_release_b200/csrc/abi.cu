@@ -77,6 +77,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->partial = take(R * (size_t)(o->chunks + 1) * kPartial * sizeof(float));
   o->row_ticket = take(R * sizeof(int32_t));
   o->work_counter = take(2 * sizeof(unsigned long long));
+  o->combine_ticket = take(sizeof(int32_t));
   o->total_bytes = off;
 }
 
@@ -117,6 +118,12 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
       return set_error(PQHSA_E_SHAPE, "KV strides must keep rows 16-byte aligned");
     if (((uintptr_t)p->k_base | (uintptr_t)p->v_base) & 15)
       return set_error(PQHSA_E_SHAPE, "k_base / v_base must be 16-byte aligned");
+  }
+  if (p->peer_world > 1) {
+    if (!p->peer_out || !p->peer_flags || !p->peer_seq)
+      return set_error(PQHSA_E_NULL, "peer_out / peer_flags / peer_seq is null with peer_world > 1");
+    if (p->peer_rank < 0 || p->peer_rank >= p->peer_world || p->peer_world > 32)
+      return set_error(PQHSA_E_SHAPE, "peer_rank %d / peer_world %d out of range", p->peer_rank, p->peer_world);
   }
   if (need_io) {
     if (!p->q || !p->out) return set_error(PQHSA_E_NULL, "q / out is null");
@@ -216,6 +223,15 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
   if (int rc = launch_select(*p, w, st)) return rc;
   if (int rc = launch_attend(*p, w, st)) return rc;
   return launch_merge(*p, w, st);
+}
+
+int pqhsa_wait_peers(const pqhsa_params* p, void* stream) {
+  if (p == nullptr) return set_error(PQHSA_E_NULL, "params is null");
+  if (p->peer_world <= 1) return PQHSA_OK;
+  if (!p->peer_flags || !p->peer_seq) return set_error(PQHSA_E_NULL, "peer_flags / peer_seq is null");
+  if (p->peer_rank < 0 || p->peer_rank >= p->peer_world || p->peer_world > 32)
+    return set_error(PQHSA_E_SHAPE, "peer_rank %d / peer_world %d out of range", p->peer_rank, p->peer_world);
+  return launch_wait_peers(*p, (cudaStream_t)stream);
 }
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {

@@ -58,6 +58,12 @@ struct AttendArgs {
   const float* unit_max;
   const float* unit_sum;
   const float* tail_logit;
+  // output exchange between GPUs (peer_world <= 1: none)
+  void* const* peer_out;
+  int32_t* const* peer_flags;
+  int32_t* peer_seq;
+  int32_t* combine_ticket;
+  int peer_world, peer_rank;
   int32_t* row_ticket;  // [R], zero between launches
   unsigned long long* work_counter;  // [2]: next item, CTAs that have left; zero between launches
   int cap, ucap, tail_cap, num_lists;
@@ -391,7 +397,55 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) A = fmaf(v[i], p0 + i < slots ? fs[p0 + i] : 0.f, A);
   }
-  static_cast<E*>(a.out)[(size_t)row * kD + tid] = from_f<E>(A / fmaxf(L, 1.17549435e-38f));
+  const E res = from_f<E>(A / fmaxf(L, 1.17549435e-38f));
+  static_cast<E*>(a.out)[(size_t)row * kD + tid] = res;
+  if (a.peer_world > 1) {
+    // The row also goes into every rank's gather buffer (plain stores over NVLink into peer memory; the
+    // buffer of this step's parity).  The CTA that finishes last raises this rank's flag on every rank.
+    __shared__ int last_s;
+    const int seq0 = a.peer_seq[0];  // steps before this one: only the last CTA changes it, after all have read it
+    const size_t slot = ((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row;
+    for (int r = 0; r < a.peer_world; ++r) static_cast<E*>(a.peer_out[r])[slot * kD + tid] = res;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      const int t = atomicAdd(a.combine_ticket, 1);
+      last_s = (t == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (last_s) {
+      if (tid == 0) {
+        a.combine_ticket[0] = 0;
+        a.peer_seq[0] = seq0 + 1;
+      }
+      __threadfence_system();  // the other CTAs' rows (seen through the ticket) go out before the flag
+      if (tid < a.peer_world) {
+        volatile int32_t* f = a.peer_flags[tid] + a.peer_rank;
+        *f = seq0 + 1;
+      }
+    }
+  }
+}
+
+// One warp: lane r waits for rank r's flag in this rank's flag array to reach this rank's step count.
+// The wait is bounded: when the limit runs out the error flag is set and the kernel returns.
+__global__ void __launch_bounds__(32) wait_peers_kernel(int32_t* const* peer_flags, int32_t* peer_seq, int world, int rank) {
+  const int lane = threadIdx.x;
+  const int target = peer_seq[0];
+  bool ok = true;
+  if (lane < world) {
+    volatile const int32_t* f = peer_flags[rank] + lane;
+    ok = false;
+    for (int it = 0; it < (1 << 22); ++it) {  // about a second
+      if (*f - target >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();  // the rows that preceded the flags are visible to what follows in the stream
+  if (!ok) peer_seq[1] = 1;
 }
 
 template <typename E>
@@ -440,6 +494,12 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
   a.unit_max = reinterpret_cast<const float*>(ws + w.unit_max);
   a.unit_sum = reinterpret_cast<const float*>(ws + w.unit_sum);
   a.tail_logit = reinterpret_cast<const float*>(ws + w.tail_logit);
+  a.peer_out = static_cast<void* const*>(p.peer_out);
+  a.peer_flags = static_cast<int32_t* const*>(p.peer_flags);
+  a.peer_seq = static_cast<int32_t*>(p.peer_seq);
+  a.combine_ticket = reinterpret_cast<int32_t*>(ws + w.combine_ticket);
+  a.peer_world = p.peer_world;
+  a.peer_rank = p.peer_rank;
   a.row_ticket = reinterpret_cast<int32_t*>(ws + w.row_ticket);
   a.work_counter = reinterpret_cast<unsigned long long*>(ws + w.work_counter);
   a.cap = p.slot_capacity;
@@ -453,6 +513,12 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
 int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
   return launch_attend_or_combine(p, w, false, st);
 }
+int launch_wait_peers(const pqhsa_params& p, cudaStream_t st) {
+  wait_peers_kernel<<<1, 32, 0, st>>>(static_cast<int32_t* const*>(p.peer_flags), static_cast<int32_t*>(p.peer_seq),
+                                      p.peer_world, p.peer_rank);
+  return check_launch("wait_peers");
+}
+
 int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
   return launch_attend_or_combine(p, w, true, st);
 }

@@ -45,6 +45,7 @@ int launch_scan(const pqhsa_params& p, const pqhsa_ws_layout& w, float* dump, cu
 int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
 int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
 int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st);
+int launch_wait_peers(const pqhsa_params& p, cudaStream_t st);
 int launch_append_kv(const pqhsa_params& p, const void* k, const void* v, cudaStream_t st);
 int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni, cudaStream_t st);
 int launch_topk(const float* scores, int rows, int n, int64_t stride, int k, int32_t* oi, float* ov,

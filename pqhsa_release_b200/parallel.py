@@ -44,3 +44,53 @@ def gather_context(local: torch.Tensor, out: torch.Tensor | None = None, group=N
     # the output is the ranks' tensors concatenated along dim 0
     dist.all_gather_into_tensor(out.view(world * b, hl, d), local, group=group)
     return out.permute(1, 0, 2, 3).reshape(b, world * hl, d)
+
+
+class PeerExchange:
+    """The output exchange without a collective call: symmetric gather buffers and flag arrays of
+    the ranks of one node, mapped into every process (``torch.distributed._symmetric_memory``), and
+    their addresses installed in a pool's parameters.  The combine kernel of every step then stores
+    its output rows into every rank's buffer and raises a flag; :meth:`wait` enqueues the bounded
+    wait for all ranks' flags.  All ranks must run the same number of steps.
+
+    Layout of a rank's buffer: ``[2, world, R, 128]`` - parity of the step, source rank, the source
+    rank's query rows."""
+
+    def __init__(self, pool, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        self.pool, self._lib = pool, _lib
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        R = pool.S * pool.G
+        self.buf = symm.empty(2, self.world, R, _lib.HEAD_DIM, dtype=pool.dtype, device=pool.device)
+        self.flags = symm.empty(max(self.world, 8), dtype=torch.int32, device=pool.device)
+        hb = symm.rendezvous(self.buf, group)
+        hf = symm.rendezvous(self.flags, group)
+        self.buf.zero_()
+        self.flags.zero_()
+        self.ptr_out = torch.tensor([int(x) for x in hb.buffer_ptrs], dtype=torch.int64, device=pool.device)
+        self.ptr_flags = torch.tensor([int(x) for x in hf.buffer_ptrs], dtype=torch.int64, device=pool.device)
+        self.seq = torch.zeros(2, dtype=torch.int32, device=pool.device)  # steps exchanged, error flag
+        p = pool.p
+        p.peer_out, p.peer_flags, p.peer_seq = self.ptr_out.data_ptr(), self.ptr_flags.data_ptr(), self.seq.data_ptr()
+        p.peer_world, p.peer_rank = self.world, self.rank
+        self._handles = (hb, hf)
+        torch.cuda.synchronize(pool.device)
+        dist.barrier(group)  # nobody stores into a buffer that its owner has not cleared yet
+
+    def wait(self) -> None:
+        """Make the current stream wait for the rows of the last step from every rank."""
+        import ctypes as C
+
+        self._lib.call("pqhsa_wait_peers", C.byref(self.pool.p), self.pool._stream())
+
+    def result(self, steps_done: int) -> torch.Tensor:
+        """Rows of all ranks after ``steps_done`` steps: ``[world, R, 128]`` (a view, valid until the
+        step after next)."""
+        return self.buf[(steps_done - 1) & 1]
+
+    def timed_out(self) -> bool:
+        return bool(int(self.seq[1].item()) != 0)
