@@ -405,10 +405,18 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
     __shared__ int last_s;
     const int seq0 = a.peer_seq[0];  // steps before this one: only the last CTA changes it, after all have read it
     const size_t slot = ((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row;
-    for (int r = 0; r < a.peer_world; ++r) static_cast<E*>(a.peer_out[r])[slot * kD + tid] = res;
-    __threadfence_system();
+    // the row is staged in shared memory and leaves as 16-byte stores, one half-warp (or warp) per rank
+    __shared__ __align__(16) E rowbuf[kD];
+    rowbuf[tid] = res;
     __syncthreads();
+    constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
+    for (int i = tid; i < a.peer_world * kVecs; i += kD) {
+      const int r = i / kVecs, v = i % kVecs;
+      reinterpret_cast<uint4*>(static_cast<E*>(a.peer_out[r]) + slot * kD)[v] = reinterpret_cast<const uint4*>(rowbuf)[v];
+    }
+    __syncthreads();  // the CTA's stores are ordered before thread 0's fence, which publishes them system-wide
     if (tid == 0) {
+      __threadfence_system();
       const int t = atomicAdd(a.combine_ticket, 1);
       last_s = (t == (int)gridDim.x - 1);
     }
@@ -418,8 +426,8 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
         a.combine_ticket[0] = 0;
         a.peer_seq[0] = seq0 + 1;
       }
-      __threadfence_system();  // the other CTAs' rows (seen through the ticket) go out before the flag
       if (tid < a.peer_world) {
+        __threadfence_system();  // the other CTAs' rows (seen through the ticket) go out before the flag
         volatile int32_t* f = a.peer_flags[tid] + a.peer_rank;
         *f = seq0 + 1;
       }
