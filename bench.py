@@ -303,16 +303,56 @@ def run_b200(args):
     res_t = runner.result()
     hout = torch.empty(res_t.shape, dtype=res_t.dtype).pin_memory()
     ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    # One graph per step also here when possible: [host-to-device copy of the step's inputs from a pinned
+    # staging buffer] + [the five launches] + [device-to-host copy of the result into a pinned buffer].  The
+    # host fills the staging buffer before every replay.
+    from pqhsa_release_b200 import _lib
+
+    e2e_graph = None
+    hstage = torch.empty_like(hin[0]).pin_memory()
+    if runner.graph is not None and world == 1:
+        hstage.copy_(hin[0])
+        e2e_graph = torch.cuda.CUDAGraph()
+        # the result needs no copy node: the step's last kernel stores its output rows straight into the
+        # pinned host buffer (mapped into the device's address space), 32 KB of posted writes over PCIe
+        hview = hout.view(runner.out.shape)
+        # ... and the inputs come in through a copy kernel that reads the pinned staging buffer over PCIe
+        # (49 KB: quicker than a copy-engine node)
+        with torch.cuda.graph(e2e_graph):
+            _lib.call("pqhsa_copy_small", runner.inbuf.data_ptr(), hstage.data_ptr(), hstage.numel() * hstage.element_size(),
+                      torch.cuda.current_stream().cuda_stream)
+            pool.decode_step_append(runner.q, runner.nk, runner.nv, encode=1, out=hview)
+        pool.note_replayed(appends=-1, encodes=-1)  # the capture pass ran no kernels
+
+    def e2e_step(i):
+        if e2e_graph is not None:
+            torch.cuda.current_stream().synchronize()  # the previous replay has read the staging buffer
+            hstage.copy_(hin[i % nq])
+            flush_l2()
+            ev2[i % K][0].record()
+            e2e_graph.replay()
+            pool.note_replayed(appends=1, encodes=1)
+            runner.steps_done += 1
+            ev2[i % K][1].record()
+        else:
+            flush_l2()
+            ev2[i % K][0].record()
+            runner.inbuf.copy_(hin[i % nq], non_blocking=True)  # q, new K rows, new V rows of the step
+            runner.step()
+            hout.copy_(runner.result(), non_blocking=True)
+            ev2[i % K][1].record()
+
     for i in range(3):
-        runner.inbuf.copy_(hin[i % nq], non_blocking=True); runner.step()
+        e2e_step(i)
     barrier()
+    # once, outside the timed region: what arrived in the host buffer is the step's output (the same
+    # query over the state the step left behind gives the same rows, up to summation order)
+    got = hout.clone().view(-1, wl.head_dim).float()
+    want = (runner.result() if world > 1 else pool.decode_step(runner.q)).reshape(-1, wl.head_dim).float().cpu()
+    if not bool(torch.isfinite(got).all()) or float((got - want).abs().max()) > 2e-2 * float(want.abs().max()):
+        raise SystemExit("end-to-end check failed: the host buffer does not hold the step's output")
     for i in range(K):
-        flush_l2()
-        ev2[i][0].record()
-        runner.inbuf.copy_(hin[i % nq], non_blocking=True)  # q, new K rows, new V rows of the step
-        runner.step()
-        hout.copy_(runner.result(), non_blocking=True)
-        ev2[i][1].record()
+        e2e_step(i)
     barrier()
     e2e_ms = sum(a.elapsed_time(b) for a, b in ev2)
     h2d = hin[0].numel() * hin[0].element_size()

@@ -258,6 +258,13 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
 
 int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
 
+/* Copy `bytes` (a multiple of 16, both pointers 16-byte aligned) with a kernel instead of a copy-engine
+ * transfer.  Meant for a step's inputs (queries, new K/V rows: tens of KB) sitting in pinned host memory
+ * that is mapped into the device's address space: for such sizes a kernel reading over PCIe finishes
+ * several microseconds before a cudaMemcpyAsync node would.  No counterpart in the reference (its inputs
+ * are already on the device inside vLLM). */
+int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream);
+
 /* Multi-GPU: make `stream` wait until every rank's flag in this rank's flag array has reached this
  * rank's step count, i.e. until all output rows of the last step have arrived in this rank's gather
  * buffer (the buffer of parity (steps - 1) & 1).  One warp polls with a limit of about a second;

@@ -225,6 +225,21 @@ int pqhsa_decode_step_append(const pqhsa_params* p, const void* new_k, const voi
   return launch_merge(*p, w, st);
 }
 
+__global__ void __launch_bounds__(256) copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream) {
+  if (!dst || !src) return set_error(PQHSA_E_NULL, "dst / src is null");
+  if ((bytes & 15) || (((uintptr_t)dst | (uintptr_t)src) & 15))
+    return set_error(PQHSA_E_SHAPE, "pqhsa_copy_small needs 16-byte aligned pointers and a multiple of 16 bytes");
+  if (bytes == 0) return PQHSA_OK;
+  const size_t n = bytes / 16;
+  const unsigned grid = (unsigned)((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024);
+  copy16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), n);
+  return check_launch("copy_small");
+}
+
 int pqhsa_wait_peers(const pqhsa_params* p, void* stream) {
   if (p == nullptr) return set_error(PQHSA_E_NULL, "params is null");
   if (p->peer_world <= 1) return PQHSA_OK;
