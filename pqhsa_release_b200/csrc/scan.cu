@@ -46,6 +46,7 @@ namespace pqhsa {
 
 constexpr int kScanThreads = 1024;  // 32 warps of 64 registers: the loop is issue-bound and needs the warps
 constexpr int kHdr = 512;     // unit headers staged in shared memory at a time
+constexpr int kSegCost = 32;  // cost of entering a stream, in units of scanning work (share balancing)
 constexpr int kIter = kUnit / 32;
 
 template <int G> struct PairShape {
@@ -181,9 +182,13 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* wring = ring + (size_t)warp * D * RG::kStageBytes;
 
+  // Length of a stream on the axis the shares are cut from: its units plus kSegCost, the price (in
+  // units of scanning work) of entering a stream - tables, list scores, headers.  A CTA whose share
+  // runs across the start of a stream pays for a second entry and gets that many units less.
   auto units_of = [&](int s) -> int {
     const int32_t* st = a.state + (size_t)s * kST;
-    return st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
+    const int u = st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
+    return u > 0 ? u + kSegCost : 0;
   };
 
   // total number of units (all streams), one load per thread
@@ -230,11 +235,14 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
       const int tend = min(T, a.S - base);
       for (int t = s_first; t < tend; ++t) {
         const long long sb = carry + s_pref[t];
-        const int u_tot = s_ut[t];
+        const int len = s_ut[t];  // units + kSegCost
         if (sb >= g1) break;
-        if (u_tot == 0 || sb + u_tot <= g0) continue;
+        if (len == 0 || sb + len <= g0) continue;
         const int s = base + t;
-        const int u0 = (int)((sb > g0 ? sb : g0) - sb), u1 = (int)((sb + u_tot < g1 ? sb + u_tot : g1) - sb);
+        const int u_tot = len - kSegCost;
+        const int u0 = max((int)((sb > g0 ? sb : g0) - sb) - kSegCost, 0);
+        const int u1 = max((int)((sb + len < g1 ? sb + len : g1) - sb) - kSegCost, 0);
+        if (u0 >= u1) continue;
 
         const int32_t* st = a.state + (size_t)s * kST;
         const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
