@@ -46,7 +46,7 @@ namespace pqhsa {
 
 constexpr int kScanThreads = 1024;  // 32 warps of 64 registers: the loop is issue-bound and needs the warps
 constexpr int kHdr = 512;     // unit headers staged in shared memory at a time
-constexpr int kSegCost = 32;  // cost of entering a stream, in units of scanning work (share balancing)
+constexpr int kSegCost = 48;  // cost of entering a stream, in units of scanning work (share balancing)
 constexpr int kIter = kUnit / 32;
 
 template <int G> struct PairShape {
