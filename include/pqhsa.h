@@ -164,7 +164,7 @@ typedef struct pqhsa_ws_layout {
   size_t pair_tab;     /* float  [S, G/GP, 4, 256, GP], GP = min(G, 4): byte-pair sums of lut for the scan */
   size_t row_bin;      /* float  [R, 2]   sample histogram origin and 1 / bin width       */
   size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
-  size_t ticket;       /* int32  [S]      arrival counter of the table kernel's CTAs (0 between launches) */
+  size_t ticket;       /* int32  [S, 2]   arrival counters of the table kernel's CTAs (0 between launches) */
   size_t slog;         /* float  [R, PQHSA_SAMPLE_KEYS]  approximate logits of the sample keys           */
   size_t norm_pend;    /* float  [S]      norm of a key encoded in the current launch                    */
   size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit                   */

@@ -64,7 +64,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->pair_tab = take(S * G * 1024 * sizeof(float));
   o->row_bin = take(R * 2 * sizeof(float));
   o->row_tau = take(R * sizeof(float));
-  o->ticket = take(S * sizeof(int32_t));
+  o->ticket = take(2 * S * sizeof(int32_t));
   o->slog = take(R * kSample * sizeof(float));
   o->norm_pend = take(S * sizeof(float));
   o->unit_max = take(R * (size_t)p->unit_capacity * sizeof(float));

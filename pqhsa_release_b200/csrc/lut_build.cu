@@ -19,10 +19,11 @@
 // Threshold estimate.  The exact top-K needs the K-th largest of N logits, which is not
 // known before the scan.  A stratified sample of 4096 slots of the list-sorted region
 // (contiguous records made when the layout was made) is scored by the list CTAs - each the
-// sample keys of its own 64 lists, whose scores it has just computed - and counted into
-// per-row histograms in global memory.  The CTA of a stream that arrives last (arrival
-// counter, no waiting) walks the histograms from the top and takes as threshold tau the
-// logit below which all but r sample keys lie, r = f n + margin * sqrt(f n) + 1 with
+// sample keys of its own 176 lists, whose scores it has just computed - and their logits go to
+// the rows' sample arrays.  The list CTA of a stream that arrives last among the list CTAs
+// (arrival counter, no waiting) histograms a row's sample logits over their own range, walks
+// the histogram from the top and takes as threshold tau the logit below which all but r
+// sample keys lie, r = f n + margin * sqrt(f n) + 1 with
 // f = K / N.  The scan then marks the keys with logit >= tau (about 1.7 K of them) and the
 // selection kernel takes the exact top K among them.  tau is only a filter: if fewer than K
 // candidates turn up (probability ~1e-9 at the default margin of 6 sigma) the selection
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   int32_t* st = a.state + (size_t)s * kST;
   const int seq_old = st[PQHSA_ST_SEQ_LEN];
   const int n_sorted = st[PQHSA_ST_N_SORTED];
+  const int n_tail_old = st[PQHSA_ST_N_TAIL];
   const bool sampling = a.slog != nullptr && n_sorted > kSample;  // shorter streams: every key is a candidate
   const bool is_encode = (int)blockIdx.y >= a.list_ctas;
 
@@ -200,30 +202,20 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
     }
   }
 
-  // ---- the CTA of the stream that arrives last changes the counters and places the thresholds ----
-  // (the barrier makes the CTA's stores visible to thread 0, whose fence then publishes them
-  //  device-wide before the ticket; the last CTA reads the others' results through L2)
-  if (a.slog == nullptr && !append && !a.encode) return;  // tables only: nothing left to do
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    const int t = atomicAdd(a.ticket + s, 1);
-    is_last = (t == (int)gridDim.y - 1);
-    if (is_last) a.ticket[s] = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  if (!is_last) return;
-
-  // every CTA of the stream is done reading the counters: the token written above now counts
-  if (tid == 0) {
-    if (append) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
+  // ---- thresholds: the list CTA of the stream that arrives last among the list CTAs (arrival counter, no
+  // waiting; the barrier makes the CTA's stores visible to thread 0, whose fence then publishes them
+  // device-wide before the ticket; the last CTA reads the others' results through L2) ----
+  auto place_thresholds = [&]() {
+    // the encode role may still be running: its effect on the key count follows from the counters as they
+    // were when the kernel started (tau is only a filter: the selection kernel takes K from the final counters)
+    int added = 0;
     if (a.encode) {
-      const float pend = __ldcg(a.enc.norm_max + s);
-      if (pend > a.norm_max[s]) a.norm_max_rw[s] = pend;
+      const int want = a.enc.enc_count ? a.enc.enc_count[s] : a.enc.uniform_count;
+      const int seq_new = seq_old + (append ? 1 : 0);
+      const int room_seq = seq_new - (min(a.enc.sink, seq_new) + n_sorted + n_tail_old);
+      added = max(0, min(min(want, room_seq), min(a.enc.cap - (n_sorted + n_tail_old), a.enc.tail_cap - n_tail_old)));
     }
-  }
-  if (a.slog == nullptr) return;
-  const int n = n_sorted + __ldcg(st + PQHSA_ST_N_TAIL);
+    const int n = n_sorted + n_tail_old + added;
   const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
   const int ns = min(kSample, n_sorted);
   const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
@@ -238,10 +230,6 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   float* slog = a.slog + (size_t)s * G * kSample;
   if (a.sample == nullptr) {
     // no sample records: this CTA gathers and scores all sample slots itself (slow path)
-    if (is_encode)  // this CTA made no tables: take them from the table CTA
-      for (int i = tid; i < G * kM * kC; i += kLutThreads)
-        lut_s[i / (kM * kC)][i % (kM * kC)] = __ldcg(a.lut + (size_t)s * G * kM * kC + i);
-    __syncthreads();
     const uint32_t* codes = a.codes + (size_t)s * a.cap;
     const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
     const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
@@ -332,6 +320,35 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
           a.row_tau[(size_t)s * G + g] = bin <= 1 ? kNegInf : lo + (float)(bin - 1) / inv_w;
         }
         cum += c[b];
+      }
+    }
+  }
+  };
+  if (!is_encode && a.slog != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      const int t = atomicAdd(a.ticket + 2 * s, 1);
+      is_last = (t == a.list_ctas - 1);
+      if (is_last) a.ticket[2 * s] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (is_last) place_thresholds();
+  }
+
+  // ---- counters: the CTA of the stream that arrives last of all.  Every CTA of the stream is then done
+  // reading the counters: the token written above now counts, a larger norm becomes the stream's bound ----
+  if (!append && !a.encode) return;
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int t = atomicAdd(a.ticket + 2 * s + 1, 1);
+    if (t == (int)gridDim.y - 1) {
+      a.ticket[2 * s + 1] = 0;
+      if (append) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
+      if (a.encode) {
+        const float pend = __ldcg(a.enc.norm_max + s);
+        if (pend > a.norm_max[s]) a.norm_max_rw[s] = pend;
       }
     }
   }
