@@ -397,8 +397,8 @@ def run_b200(args):
     # KV head) and the value means of the background
     attend_bytes = wl.batch * (hl * wl.group * wl.topk() + hl * f_rows) * 2 * wl.head_dim * e \
         + wl.batch * hl * wl.num_lists * wl.head_dim * e
-    # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the ncu capture summarised in
-    # profiles/decode_step_c2_ncu_full.md (same workload, one GPU); no capture exists for other shapes
+    # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the committed ncu capture summary of this
+    # workload under profiles/ (one GPU); no capture exists for other shapes
     traffic = 165_225_216 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
     attend_s = stage_ms[3] / 1e3
     achieved = attend_bytes / attend_s / 1e9

@@ -17,6 +17,7 @@ needed at test time except the .npz files.
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -112,4 +113,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])  # a checkout of the reference

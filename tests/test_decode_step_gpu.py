@@ -104,7 +104,7 @@ def test_forced_fallback_is_still_exact():
 
 @pytest.mark.parametrize("name, H", [("c2", 2), ("c4", 1)])
 def test_full_context_properties_against_the_dumped_scores(name, H):
-    """BASELINE's full contexts (c2: 131072 keys, G = 4; c4: 262144 keys, G = 8, where a row has
+    """The full contexts of the benchmark configurations (c2: 131072 keys, G = 4; c4: 262144 keys, G = 8, where a row has
     more candidates than the selection kernel keeps in registers; 512 lists, bf16), too large for
     the CPU oracle: size-independent properties instead.  The selected set must be exactly the K
     largest of the logits the library itself dumps (same floats, ties to the lower slot), every
