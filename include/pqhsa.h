@@ -174,7 +174,7 @@ typedef struct pqhsa_ws_layout {
   size_t hitmap;       /* uint32 [R, unit_capacity, 4]  bit b of word (u, i): slot first(u) + 32 i + b reached the threshold */
   size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */
   size_t sel_off;      /* int64  [R, kcap]  element offset of their K/V rows in the cache  */
-  size_t partial;      /* float  [R, chunks + 1, 130]  split-K partials (max, sum, acc): exact chunks, then the background */
+  size_t partial;      /* float  [R, chunks + 5, 130]  split-K partials (max, sum, acc): exact chunks, then up to 5 background parts */
   size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
   size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
   size_t combine_ticket; /* int32 [1]     finished CTAs of the combine kernel (0 between launches)          */

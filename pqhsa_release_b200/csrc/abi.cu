@@ -74,7 +74,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->hitmap = take(R * (size_t)p->unit_capacity * (kUnit / 32) * sizeof(uint32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
   o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
-  o->partial = take(R * (size_t)(o->chunks + 1) * kPartial * sizeof(float));
+  o->partial = take(R * (size_t)(o->chunks + kBgParts) * kPartial * sizeof(float));
   o->row_ticket = take(R * sizeof(int32_t));
   o->work_counter = take(2 * sizeof(unsigned long long));
   o->combine_ticket = take(sizeof(int32_t));

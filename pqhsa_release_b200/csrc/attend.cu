@@ -67,6 +67,7 @@ struct AttendArgs {
   int32_t* row_ticket;  // [R], zero between launches
   unsigned long long* work_counter;  // [2]: next item, CTAs that have left; zero between launches
   int cap, ucap, tail_cap, num_lists;
+  int bg_parts;  // background items per query row in this launch (1 .. kBgParts)
 };
 
 template <typename E> struct RawRow;  // 8 elements of a K/V row as loaded
@@ -99,20 +100,36 @@ __device__ __forceinline__ void cvt_row(const RawRow<__half>& r, float (&v)[8]) 
 
 constexpr int kBgGroups = kAttThreads / 16;  // 16 threads x 8 dims cover one value-mean row
 
-// The background partial of one query row (all kAttThreads threads): list masses from the per-unit
-// (max, sum) pairs and the unselected tail logits, then mass x value means.
+// One of the background partials of a query row (all kAttThreads threads): list masses from the
+// per-unit (max, sum) pairs of a share of the row's units - consecutive units, hence a contiguous
+// range of lists - times those lists' value means.  The unselected keys of the unsorted tail, whose
+// lists are arbitrary, are a part of their own (range = all lists, lists without mass are skipped);
+// with a single unit part they ride along with it.
 template <typename E>
-__device__ __forceinline__ void background_item(const AttendArgs& a, int row, int s, const StreamGeom& geo, float* pout,
-                                                float* mass, float (*gacc)[kD], float* red) {
+__device__ __forceinline__ void background_item(const AttendArgs& a, int row, int s, int part, const StreamGeom& geo,
+                                                float* pout, float* mass, float (*gacc)[kD], float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* umax = a.unit_max + (size_t)row * a.ucap;
   const float* usum = a.unit_sum + (size_t)row * a.ucap;
   const float* tl = a.tail_logit + (size_t)row * a.tail_cap;
-  for (int i = tid; i < kLMax; i += kAttThreads) mass[i] = 0.f;
-  // reference of the partial: the largest unit maximum / tail logit, base-2 domain
+  const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
+  const uint16_t* tlist = a.list_ids + (size_t)s * a.cap + geo.n_sorted;
+  // unit parts 0 .. bg_units - 1; the tail rides with part 0 when there is one unit part, else it is a part of its own
+  const int bg_units = a.bg_parts > 1 ? a.bg_parts - 1 : 1;
+  const bool unit_part = part < bg_units;
+  const int u_lo = unit_part ? (int)((long long)geo.n_units * part / bg_units) : 0;
+  const int u_hi = unit_part ? (int)((long long)geo.n_units * (part + 1) / bg_units) : 0;
+  const int n_tail = (a.bg_parts == 1 || !unit_part) ? geo.n_tail : 0;
+  int l_lo = u_lo < u_hi ? (int)ulist[u_lo] : 0, l_hi = u_lo < u_hi ? (int)ulist[u_hi - 1] + 1 : 0;
+  if (n_tail > 0) {
+    l_lo = 0;
+    l_hi = a.num_lists;
+  }
+  for (int i = l_lo + tid; i < l_hi; i += kAttThreads) mass[i] = 0.f;
+  // reference of the partial: the largest unit maximum / tail logit of the part, base-2 domain
   float m = kNegInf;
-  for (int u = tid; u < geo.n_units; u += kAttThreads) m = fmaxf(m, umax[u]);
-  for (int t = tid; t < geo.n_tail; t += kAttThreads) m = fmaxf(m, tl[t]);
+  for (int u = u_lo + tid; u < u_hi; u += kAttThreads) m = fmaxf(m, umax[u]);
+  for (int t = tid; t < n_tail; t += kAttThreads) m = fmaxf(m, tl[t]);
   m = warp_max(m * kLog2e);
   __syncthreads();  // also: the previous item is done with the shared arrays, mass[] is zero
   if (lane == 0) red[warp] = m;
@@ -122,16 +139,16 @@ __device__ __forceinline__ void background_item(const AttendArgs& a, int row, in
   for (int w = 1; w < kAttWarps; ++w) M = fmaxf(M, red[w]);
   float tot = 0.f;
   if (M != kNegInf) {
-    for (int u = tid; u < geo.n_units; u += kAttThreads) {
+    for (int u = u_lo + tid; u < u_hi; u += kAttThreads) {
       const float v = usum[u] * ex2(fmaf(umax[u], kLog2e, -M));
-      atomicAdd(&mass[a.unit_list[(size_t)s * a.ucap + u]], v);
+      atomicAdd(&mass[ulist[u]], v);
       tot += v;
     }
-    for (int t = tid; t < geo.n_tail; t += kAttThreads) {
+    for (int t = tid; t < n_tail; t += kAttThreads) {
       const float x = tl[t];
       if (x != kNegInf) {  // -inf marks a selected tail slot
         const float v = ex2(fmaf(x, kLog2e, -M));
-        atomicAdd(&mass[a.list_ids[(size_t)s * a.cap + geo.n_sorted + t]], v);
+        atomicAdd(&mass[tlist[t]], v);
         tot += v;
       }
     }
@@ -143,27 +160,27 @@ __device__ __forceinline__ void background_item(const AttendArgs& a, int row, in
   float L = 0.f;
 #pragma unroll
   for (int w = 0; w < kAttWarps; ++w) L += red[w];
-  // sum_l mass[l] * vmean[l][:]: list = lg + kBgGroups * i, dims d8*8 .. d8*8+7, 8 rows in flight
+  // sum_l mass[l] * vmean[l][:]: list = l_lo + lg + kBgGroups * i, dims d8*8 .. d8*8+7, 8 rows in flight
   const int d8 = tid & 15, lg = tid >> 4;
   const E* vm = static_cast<const E*>(a.vmeans) + (size_t)s * a.num_lists * kD + d8 * 8;
   float acc[8];
 #pragma unroll
   for (int d = 0; d < 8; ++d) acc[d] = 0.f;
-  for (int l0 = lg; l0 < a.num_lists; l0 += kBgGroups * 8) {
+  for (int l0 = l_lo + lg; l0 < l_hi; l0 += kBgGroups * 8) {
     RawRow<E> vr[8];
+    float w[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int l = l0 + kBgGroups * i;
-      if (l < a.num_lists) ld_row(vm + (size_t)l * kD, vr[i]); else zero_row(vr[i]);
+      w[i] = l < l_hi ? mass[l] : 0.f;
+      if (w[i] != 0.f) ld_row(vm + (size_t)l * kD, vr[i]); else zero_row(vr[i]);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int l = l0 + kBgGroups * i;
       float v[8];
       cvt_row(vr[i], v);
-      const float w = l < a.num_lists ? mass[l] : 0.f;
 #pragma unroll
-      for (int d = 0; d < 8; ++d) acc[d] = fmaf(w, v[d], acc[d]);
+      for (int d = 0; d < 8; ++d) acc[d] = fmaf(w[i], v[d], acc[d]);
     }
   }
 #pragma unroll
@@ -189,8 +206,8 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
   const int half = lane >> 4, l16 = lane & 15;
   const E* kb = static_cast<const E*>(a.k_base);
   const E* vb = static_cast<const E*>(a.v_base);
-  const int slots = a.chunks + 1;  // partials per row
-  const long long items = (long long)a.R * slots;
+  const int slots = a.chunks + kBgParts;  // partial slots per row (a.bg_parts of the background slots are used)
+  const long long items = (long long)a.R * (a.chunks + a.bg_parts);
 
   // Items are handed out by a counter (a CTA that drew a long item draws fewer): first the rows'
   // background items (long dependent chains), then the chunks row by row, so that rows finish - and
@@ -204,9 +221,9 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
     __syncthreads();  // everybody has read item_s
     long long nxt = 0;
     if (tid == 0) nxt = (long long)atomicAdd(a.work_counter, 1ull);  // used at the end of the item: the round trip is hidden
-    const bool is_bg = item < a.R;
+    const bool is_bg = item < (long long)a.R * a.bg_parts;
     const int row = (int)(item % a.R);
-    const int c = is_bg ? a.chunks : (int)(item / a.R) - 1;
+    const int c = is_bg ? a.chunks + (int)(item / a.R) : (int)(item / a.R) - a.bg_parts;
     const int s = row / a.G;
     const int32_t* st = a.state + (size_t)s * kST;
     const StreamGeom geo = stream_geom(st, a.sink);
@@ -226,8 +243,8 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
       continue;
     }
 
-    if (c == a.chunks) {
-      background_item<E>(a, row, s, geo, pout, mass, gacc, wm);
+    if (c >= a.chunks) {
+      background_item<E>(a, row, s, c - a.chunks, geo, pout, mass, gacc, wm);
     } else {
 
     // 1. element offset of this lane's entry
@@ -364,8 +381,8 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
 template <typename E>
 __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
   const int row = blockIdx.x, tid = threadIdx.x;
-  const int slots = a.chunks + 1;  // <= kD, checked at launch; empty chunks carry (-inf, 0)
-  const float* pp = a.partial + (size_t)row * slots * kPartial;
+  const int slots = a.chunks + a.bg_parts;  // <= kD, checked at launch; empty chunks carry (-inf, 0)
+  const float* pp = a.partial + (size_t)row * (a.chunks + kBgParts) * kPartial;
   __shared__ float fs[kD], red[kD / 32];
   // thread p takes partial p's (max, sum): one round trip for all of them
   const float mp = tid < slots ? pp[(size_t)tid * kPartial] : kNegInf;
@@ -465,12 +482,12 @@ static int launch_attend_t(const AttendArgs& a, bool combine, cudaStream_t st) {
       n = 4;
     per_sm = n;
   }
-  const long long items = (long long)a.R * (a.chunks + 1);
+  const long long items = (long long)a.R * (a.chunks + a.bg_parts);
   long long grid = (long long)sm_count() * per_sm;
   if (grid > items) grid = items;
   if (grid < 1) grid = 1;
   if (combine) {
-    if (a.chunks + 1 > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + 1, kD);
+    if (a.chunks + kBgParts > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + kBgParts, kD);
     combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
     return check_launch("combine");
   }
@@ -514,6 +531,9 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
   a.ucap = p.unit_capacity;
   a.tail_cap = w.tail_cap;
   a.num_lists = p.num_lists;
+  // Few rows: the background of a row is a long chain and would be the kernel's critical path, so it is cut
+  // into parts.  Many rows: the parts only add items, and one item per row hides behind the chunk items.
+  a.bg_parts = a.R >= 96 ? 1 : kBgParts;  // kBgParts - 1 unit parts + the tail part
   PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E>(a, combine, st)));
   return PQHSA_OK;
 }

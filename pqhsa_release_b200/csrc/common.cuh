@@ -22,6 +22,7 @@ constexpr int kRI = PQHSA_RI_INTS;      // ints of row_info per row
 constexpr int kST = PQHSA_STATE_INTS;   // ints of state per stream
 constexpr int kChunk = 128;             // attend entries per split-K chunk
 constexpr int kPartial = kD + 2;        // floats per split-K partial (max, sum, acc[D])
+constexpr int kBgParts = 5;             // background partial slots per query row (4 unit parts + the tail)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kNegInf = -__builtin_huge_valf();
 

@@ -466,7 +466,7 @@ class DeviceIndexPool:
             "hitmap": (torch.int32, (R, self.ucap, _lib.UNIT_KEYS // 32)),
             "sel_slot": (torch.int32, (R, lay.kcap)),
             "sel_off": (torch.int64, (R, lay.kcap)),
-            "partial": (torch.float32, (R, lay.chunks + 1, _lib.HEAD_DIM + 2)),
+            "partial": (torch.float32, (R, lay.chunks + 5, _lib.HEAD_DIM + 2)),
         }[name]
         dt, shape = spec
         nbytes = int(np.prod(shape)) * torch.empty(0, dtype=dt).element_size()
