@@ -185,13 +185,24 @@ class StepRunner:
         self.gathered = torch.zeros(world, S, G, D, dtype=wl.dtype, device=dev) if world > 1 else None
         self.exchange, self.steps_done = None, 0
         if world > 1 and os.environ.get("PQHSA_EXCHANGE", "peer") == "peer":
-            try:  # rows stored straight into every rank's buffer by the combine kernel; NCCL otherwise
+            # rows stored straight into every rank's buffer by the combine kernel; NCCL otherwise.  The ranks
+            # agree on the outcome: one rank without symmetric memory sends all of them to the NCCL form.
+            why = ""
+            try:
                 from pqhsa_release_b200.parallel import PeerExchange
 
                 self.exchange = PeerExchange(pool)
             except Exception as e:  # noqa: BLE001
-                print(f"[bench] peer exchange unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
+                why = f"{type(e).__name__}: {e}"
                 self.exchange = None
+            ok = torch.tensor([1 if self.exchange is not None else 0], dtype=torch.int32, device=dev)
+            torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if self.exchange is not None or why:
+                    print(f"[bench] peer exchange unavailable on some rank ({why or 'elsewhere'}); using the NCCL all-gather",
+                          file=sys.stderr)
+                self.exchange = None
+                pool.p.peer_world = 0
         self.graph = None
         self.launches_per_step = 4  # tables + append + encode, scan, select, attend + background + merge
         pool.graph_headroom = headroom
