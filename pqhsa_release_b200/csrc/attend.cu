@@ -417,34 +417,33 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
   const E res = from_f<E>(A / fmaxf(L, 1.17549435e-38f));
   static_cast<E*>(a.out)[(size_t)row * kD + tid] = res;
   if (a.peer_world > 1) {
-    // The row also goes into every rank's gather buffer (plain stores over NVLink into peer memory; the
-    // buffer of this step's parity).  The CTA that finishes last raises this rank's flag on every rank.
+    // The CTA that finishes last sends this rank's rows to every rank's gather buffer (16-byte stores into
+    // peer memory over NVLink; the buffer of this step's parity), fences once at system scope and raises
+    // this rank's flag on every rank.
     __shared__ int last_s;
     const int seq0 = a.peer_seq[0];  // steps before this one: only the last CTA changes it, after all have read it
-    const size_t slot = ((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row;
-    // the row is staged in shared memory and leaves as 16-byte stores, one half-warp (or warp) per rank
-    __shared__ __align__(16) E rowbuf[kD];
-    rowbuf[tid] = res;
-    __syncthreads();
-    constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
-    for (int i = tid; i < a.peer_world * kVecs; i += kD) {
-      const int r = i / kVecs, v = i % kVecs;
-      reinterpret_cast<uint4*>(static_cast<E*>(a.peer_out[r]) + slot * kD)[v] = reinterpret_cast<const uint4*>(rowbuf)[v];
-    }
-    __syncthreads();  // the CTA's stores are ordered before thread 0's fence, which publishes them system-wide
+    __syncthreads();                 // the CTA's row is written ...
     if (tid == 0) {
-      __threadfence_system();
+      __threadfence();               // ... and visible device-wide before the ticket
       const int t = atomicAdd(a.combine_ticket, 1);
       last_s = (t == (int)gridDim.x - 1);
     }
     __syncthreads();
     if (last_s) {
+      constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
+      const size_t base = ((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R * kVecs;
+      const uint4* src = reinterpret_cast<const uint4*>(a.out);
+      for (int i = tid; i < a.R * kVecs; i += kD) {
+        const uint4 v = __ldcg(src + i);  // the other CTAs' rows, through L2
+        for (int r = 0; r < a.peer_world; ++r) reinterpret_cast<uint4*>(a.peer_out[r])[base + i] = v;
+      }
+      __threadfence_system();
+      __syncthreads();
       if (tid == 0) {
         a.combine_ticket[0] = 0;
         a.peer_seq[0] = seq0 + 1;
       }
       if (tid < a.peer_world) {
-        __threadfence_system();  // the other CTAs' rows (seen through the ticket) go out before the flag
         volatile int32_t* f = a.peer_flags[tid] + a.peer_rank;
         *f = seq0 + 1;
       }
