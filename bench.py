@@ -204,7 +204,7 @@ class StepRunner:
                 self.exchange = None
                 pool.p.peer_world = 0
         self.graph = None
-        self.launches_per_step = 4  # tables + append + encode, scan, select, attend + background + merge
+        self.launches_per_step = 5  # tables + append + encode, scan, select, attend + background, combine (+ the peer wait when sharded)
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture
@@ -268,6 +268,8 @@ def run_b200(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     flush_rd = torch.zeros(64 << 20, dtype=torch.int32, device=device)
 
+    align_t = torch.zeros(1, dtype=torch.int32, device=device)
+
     def flush_l2():
         # evict everything: write 256 MiB, then read another 256 MiB so that the L2 is left
         # holding clean lines (a cold cache without a write-back storm under the next kernel)
@@ -275,6 +277,11 @@ def run_b200(args):
             flush.zero_()
         if args.flush in ("read", "write+read"):
             flush_rd.sum()
+        if world > 1:
+            # The flush is part of the measurement, not of the workload: line the ranks up again behind it
+            # (a 4-byte all-reduce on the same stream, outside the timed region), so that a step's time does
+            # not include waiting for a rank whose flush ran a little longer.
+            torch.distributed.all_reduce(align_t)
     nq = len(qs)
 
     def load_inputs(i):
@@ -436,7 +443,7 @@ def run_b200(args):
         "stages_us": {n: round(1e3 * m, 2) for n, m in zip(stage_names, stage_ms)},
         "e2e": {"value": e2e_value, "unit": UNIT, "us_per_layer_step": 1e3 * e2e_ms / K,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": runner.launches_per_step * K,
+        "gpu_launches": (runner.launches_per_step + (1 if runner.exchange is not None else 0)) * K,
         "clocks": clocks,
         "wall_s_timed_region": wall, "setup_s": setup_s,
     }
