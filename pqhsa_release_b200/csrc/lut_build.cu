@@ -71,6 +71,22 @@ struct LutArgs {
   EncodeArgs enc;
 };
 
+// Sums 32 values per lane across the warp; lane j returns the total of v[j].  Each step exchanges one
+// half of the remaining values with the lane `o` away and keeps the other half.
+__device__ __forceinline__ float warp_reduce_scatter32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {  // o values stay after this step
+      const float keep = up ? v[i + o] : v[i];
+      const float send = up ? v[i] : v[i + o];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+  }
+  return v[0];
+}
+
 template <typename E, int G>
 __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a) {
   __shared__ float qs[G][kD];
@@ -171,20 +187,32 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
       i0 = ss[min(l0, a.num_lists)];
       i1 = ss[min(l0 + kListsPerCta, a.num_lists)];
     }
+    // kPerWarp x G partial dot products per lane; 32 of them at a time are summed across the warp with 31
+    // shuffles (halving exchange: lane j ends up with the total of value j) instead of 5 per value
+    constexpr int kVals = kPerWarp * G;
 #pragma unroll
-    for (int i = 0; i < kPerWarp; ++i) {
-      const int l = l0 + warp * kPerWarp + i;
-      if (l >= a.num_lists) break;
+    for (int b0 = 0; b0 < kVals; b0 += 32) {
+      float v[32];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float acc = c[i][0] * qr[g][0];
-        acc = fmaf(c[i][1], qr[g][1], acc);
-        acc = fmaf(c[i][2], qr[g][2], acc);
-        acc = fmaf(c[i][3], qr[g][3], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-          a.list_scores[((size_t)s * G + g) * kLMax + l] = acc;
-          lsc_s[g][l - l0] = acc;
+      for (int j = 0; j < 32; ++j) {
+        const int idx = b0 + j;
+        v[j] = 0.f;
+        if (idx < kVals) {
+          const int i = idx / G, g = idx % G;
+          float acc = c[i][0] * qr[g][0];
+          acc = fmaf(c[i][1], qr[g][1], acc);
+          acc = fmaf(c[i][2], qr[g][2], acc);
+          v[j] = fmaf(c[i][3], qr[g][3], acc);
+        }
+      }
+      const float tot = warp_reduce_scatter32(v, lane);
+      const int idx = b0 + lane;
+      if (idx < kVals) {
+        const int i = idx / G, g = idx % G;
+        const int l = l0 + warp * kPerWarp + i;
+        if (l < a.num_lists) {
+          a.list_scores[((size_t)s * G + g) * kLMax + l] = tot;
+          lsc_s[g][l - l0] = tot;
         }
       }
     }
