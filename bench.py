@@ -417,7 +417,7 @@ def run_b200(args):
         + wl.batch * hl * wl.num_lists * wl.head_dim * e
     # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the committed ncu capture summary of this
     # workload under profiles/ (one GPU); no capture exists for other shapes
-    traffic = 165_225_216 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
+    traffic = 165_806_336 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
     attend_s = stage_ms[3] / 1e3
     achieved = attend_bytes / attend_s / 1e9
     line = {
