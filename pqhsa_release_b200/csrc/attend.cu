@@ -10,7 +10,7 @@
 // This is the HBM-bound kernel of the step: K + F random 256-byte K rows and V
 // rows per query row.  Work item = (query row, chunk of 128 entries); entry e of
 // a row is the e-th row of [sink | local | selected].  A persistent grid sized to
-// the resident CTA count strides over the items.  Inside a CTA each of the 4
+// the resident CTA count draws the items from a counter.  Inside a CTA each of the 4
 // warps owns 32 entries:
 //   1. lane-parallel: entry -> element offset of its K/V row (computed for sink
 //      and local rows, read from sel_off for selected rows - one dependent load);
@@ -20,16 +20,17 @@
 //   3. online softmax in the base-2 domain per half-warp; halves and warps are
 //      merged at the end and one (max, sum, acc[128]) partial is written.
 //
-// Background.  One more item per query row turns the scan's per-unit (max, sum exp) pairs -
-// selected keys already taken out by the selection kernel - and the tail logits into list
-// masses and multiplies them with the lists' value means ([1 x L] x [L x 128]): a partial of
+// Background.  One to five more items per query row turn the scan's per-unit (max, sum exp)
+// pairs - selected keys already taken out by the selection kernel - and the tail logits into
+// list masses and multiply them with the lists' value means ([1 x L] x [L x 128]): partials of
 // the same form.  This is the centroid-mode background of
 // pq_hsa/attention/sparse_attention.py:887-1012 in the list-space form argued for at
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:2043-2058 (it replaces pq_attend_bg, :2150-2242).
+// Items are handed out by an atomic counter, background items first.
 //
-// Merge.  Every finished item takes a ticket of its row; the CTA that takes the last one (no
-// waiting) folds the row's partials - out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M) - and
-// writes the output row (pq_attend_reduce_mw, :2244-2402).
+// Merge.  combine_kernel folds a row's partials - out = sum_p acc_p 2^(m_p - M) /
+// sum_p l_p 2^(m_p - M) - and writes the output row (pq_attend_reduce_mw, :2244-2402); with
+// several GPUs it also sends the rank's rows to the peers.
 #include "common.cuh"
 
 namespace pqhsa {
@@ -47,7 +48,7 @@ struct AttendArgs {
   const int32_t* state;
   const int32_t* row_info;
   const long long* sel_off;
-  float* partial;  // [R, chunks + 1, kPartial]: the exact chunks, then the background
+  float* partial;  // [R, chunks + kBgParts, kPartial]: the exact chunks, then the background parts
   int R, G, kcap, chunks, sink;
   float scale;
   // background and merge
@@ -286,16 +287,32 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
         }
       }
       float x[kAttUnroll];
+      {
+        // the lane's share of the four dot products, then their sums over the 16 lanes of the half-warp:
+        // a halving exchange (lane bits 3, 2 pick which product a lane ends up with) and a broadcast -
+        // 9 shuffles instead of 16
+        static_assert(kAttUnroll == 4, "the reduction below is written for four rows");
+        float dp[kAttUnroll];
 #pragma unroll
-      for (int u = 0; u < kAttUnroll; ++u) {
-        float kf[8];
-        cvt_row(kr[u], kf);
-        float d0 = kf[0] * qv[0];
+        for (int u = 0; u < kAttUnroll; ++u) {
+          float kf[8];
+          cvt_row(kr[u], kf);
+          float d0 = kf[0] * qv[0];
 #pragma unroll
-        for (int d = 1; d < 8; ++d) d0 = fmaf(kf[d], qv[d], d0);
+          for (int d = 1; d < 8; ++d) d0 = fmaf(kf[d], qv[d], d0);
+          dp[u] = d0;
+        }
+        const bool b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
+        const float e0 = (b3 ? dp[2] : dp[0]) + __shfl_xor_sync(0xffffffffu, b3 ? dp[0] : dp[2], 8);
+        const float e1 = (b3 ? dp[3] : dp[1]) + __shfl_xor_sync(0xffffffffu, b3 ? dp[1] : dp[3], 8);
+        float f = (b2 ? e1 : e0) + __shfl_xor_sync(0xffffffffu, b2 ? e0 : e1, 4);
+        f += __shfl_xor_sync(0xffffffffu, f, 2);
+        f += __shfl_xor_sync(0xffffffffu, f, 1);  // lanes with (bit 3, bit 2) = (u >> 1, u & 1) hold product u
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) d0 += __shfl_xor_sync(0xffffffffu, d0, o);
-        x[u] = ok[u] ? d0 : kNegInf;
+        for (int u = 0; u < kAttUnroll; ++u) {
+          const float d0 = __shfl_sync(0xffffffffu, f, (lane & 16) | ((u >> 1) << 3) | ((u & 1) << 2));
+          x[u] = ok[u] ? d0 : kNegInf;
+        }
       }
       float mx = m;
 #pragma unroll
