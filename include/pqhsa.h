@@ -290,6 +290,19 @@ int pqhsa_append_kv(const pqhsa_params* p, const void* new_k, const void* new_v,
 int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t uniform_count,
                         void* stream);
 
+/* Bulk encode with fixed codebooks, outside any index pool: keys E [num_streams, n, 128]
+ * (stream_stride elements from one stream's first key to the next's) are split into norm and
+ * direction, assigned to the nearest of coarse E [num_streams, num_lists, 128] and
+ * residual-encoded against codebooks E [num_streams, 8, 16, 16].  Writes, in the order of the
+ * keys, codes u32 [num_streams, n] (subspace m = bits 4m..4m+3), norms E [num_streams, n] and
+ * list_ids u16 [num_streams, n].  This is the assign-and-encode-every-key pass that ends
+ * IVFPQIndex.build (pq_hsa/index/ivfpq.py:275-348) and the codebook-moving refresh
+ * (:647-707), and IVFPQIndex.add (:598-645) for a large batch; same arithmetic as
+ * pqhsa_append_encode, value for value.  The caller sorts the result into list order. */
+int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                      const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
+                      uint16_t* list_ids, void* stream);
+
 /* Test / inspection entry: approximate logits (scale * estimated q.k) of every
  * slot, float [R, cap], same arithmetic as the scan.  Counterpart of
  * score_packed_4bit_lut_multihead_list_bias

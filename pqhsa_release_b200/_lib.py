@@ -73,6 +73,11 @@ EXPORTS = {
     "pqhsa_run_stage": (C.c_int, [C.POINTER(Params), C.c_int, C.c_void_p]),
     "pqhsa_append_kv": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p]),
     "pqhsa_append_encode": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p]),
+    "pqhsa_encode_bulk": (
+        C.c_int,
+        [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+         C.c_void_p, C.c_void_p, C.c_void_p],
+    ),
     "pqhsa_scan_scores": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_scan_scores_static": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_topk_radix": (

@@ -280,6 +280,22 @@ int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t
   return launch_append_encode(*p, enc_count, uniform_count, (cudaStream_t)stream);
 }
 
+int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                      const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
+                      uint16_t* list_ids, void* stream) {
+  if (!keys || !coarse || !codebooks || !codes || !norms || !list_ids) return set_error(PQHSA_E_NULL, "null argument");
+  if (dtype < PQHSA_F32 || dtype > PQHSA_F16) return set_error(PQHSA_E_DTYPE, "unknown dtype %d", dtype);
+  if (num_streams <= 0 || num_streams > 65535) return set_error(PQHSA_E_SHAPE, "num_streams must be in 1..65535");
+  if (n < 0 || stream_stride < (int64_t)n * kD) return set_error(PQHSA_E_SHAPE, "need n >= 0 and stream_stride >= n * %d", kD);
+  if (num_lists < 1 || num_lists > kLMax) return set_error(PQHSA_E_SHAPE, "num_lists must be in 1..%d, got %d", kLMax, num_lists);
+  const int64_t esz = dtype == PQHSA_F32 ? 4 : 2;
+  if (((uintptr_t)keys | (uintptr_t)coarse | (uintptr_t)codebooks) & 15 || (stream_stride * esz) & 15)
+    return set_error(PQHSA_E_SHAPE, "keys, coarse and codebooks must be 16-byte aligned");
+  if (n == 0) return PQHSA_OK;
+  return launch_encode_bulk(keys, stream_stride, num_streams, n, dtype, coarse, num_lists, codebooks, codes, norms,
+                            list_ids, (cudaStream_t)stream);
+}
+
 int pqhsa_scan_scores(const pqhsa_params* p, float* scores, void* stream) {
   if (int rc = check_params(p, true, false, false)) return rc;
   if (!scores) return set_error(PQHSA_E_NULL, "scores is null");

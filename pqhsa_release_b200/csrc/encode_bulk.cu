@@ -1,0 +1,235 @@
+// Bulk encode against fixed codebooks: every key of [S, N, 128] is split into norm and
+// direction, assigned to its nearest list and residual-encoded to 8 nibbles.  This is the
+// "assign + encode every key" pass that ends an index build (pq_hsa/index/ivfpq.py:275-348)
+// and a codebook-moving refresh (:647-707), and IVFPQIndex.add (:598-645) for a large batch.
+//
+// The arithmetic is the incremental encoder's (encode.cuh), value for value: the squared norm
+// is four 32-dim butterfly sums added left to right, a list distance is
+// (p0 + p1) + (p2 + p3) with p_q the fmaf chain of (u_d - c_d)^2 over dims 32q .. 32q+31, a
+// code-word distance is one fmaf chain over its 16 dims, and ties go to the lower index.  A key
+// encoded here and the same key encoded by pqhsa_append_encode get the same list, code and norm.
+//
+// Shape of the work: N x L x 128 subtract-and-fma pairs per stream (fp32 pipe bound), the
+// code-word search is 1/32 of that.  One CTA takes 64 keys; their directions stay in shared
+// memory, dimension-major, while the stream's centroids pass through a second shared tile 64
+// lists at a time.  A thread owns a 4-key x 4-list block of distances, so one pair of 16-byte
+// shared loads feeds 16 subtract-fma pairs.
+#include "common.cuh"
+
+namespace pqhsa {
+
+constexpr int kBulkKeys = 64;      // keys per CTA
+constexpr int kBulkLists = 64;     // lists per centroid tile
+constexpr int kBulkThreads = 256;  // 16 key blocks x 16 list blocks
+
+struct BulkArgs {
+  const void* keys;
+  long long stream_stride;  // elements between the first keys of two streams
+  const void* coarse;
+  const void* codebooks;
+  uint32_t* codes;
+  void* norms;
+  uint16_t* list_ids;
+  int n, num_lists;
+};
+
+// rows [row0, row0 + 64) of a row-major [rows, 128] matrix of E -> dst[d][r] as fp32; rows at or
+// beyond `rows` read as zero.  Lane -> row, so the transposed stores hit 32 different banks.
+template <typename E>
+__device__ __forceinline__ void load_tile_transposed(const E* src, int row0, int rows, float (*dst)[kBulkLists]) {
+  constexpr int kPer = 16 / (int)sizeof(E);  // elements per 16-byte vector
+  constexpr int kVec = kD / kPer;            // vectors per row
+  for (int i = threadIdx.x; i < kBulkLists * kVec; i += kBulkThreads) {
+    const int r = i % kBulkLists, j = i / kBulkLists;
+    float v[kPer];
+    if (row0 + r < rows) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(row0 + r) * kD) + j);
+      if constexpr (sizeof(E) == 2) {
+        unpack8(raw, static_cast<const E*>(nullptr), v);
+      } else {
+        v[0] = __uint_as_float(raw.x);
+        v[1] = __uint_as_float(raw.y);
+        v[2] = __uint_as_float(raw.z);
+        v[3] = __uint_as_float(raw.w);
+      }
+    } else {
+#pragma unroll
+      for (int d = 0; d < kPer; ++d) v[d] = 0.f;
+    }
+#pragma unroll
+    for (int d = 0; d < kPer; ++d) dst[j * kPer + d][r] = v[d];
+  }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(kBulkThreads, 3) encode_bulk_kernel(const BulkArgs a) {
+  extern __shared__ __align__(16) float bulk_smem[];
+  float (*U)[kBulkKeys] = reinterpret_cast<float (*)[kBulkKeys]>(bulk_smem);                    // directions, then residuals
+  float (*C)[kBulkLists] = reinterpret_cast<float (*)[kBulkLists]>(bulk_smem + kD * kBulkKeys);  // centroid tile, then code words
+  __shared__ float nrm_sh[kBulkKeys];
+  __shared__ int list_sh[kBulkKeys];
+  __shared__ uint32_t code_sh[kBulkKeys];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int s = blockIdx.y, key0 = blockIdx.x * kBulkKeys;
+  const E* keys = static_cast<const E*>(a.keys) + (size_t)s * a.stream_stride;
+  const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
+  const E* books = static_cast<const E*>(a.codebooks) + (size_t)s * kM * kC * kSub;
+
+  // ---- norm and direction: a warp per key, lane -> dims lane, lane + 32, ...
+  for (int k = warp; k < kBulkKeys; k += kBulkThreads / 32) {
+    const int n = key0 + k;
+    float kv[4], tot = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      kv[q] = n < a.n ? to_f(keys[(size_t)n * kD + q * 32 + lane]) : 0.f;
+      tot += warp_sum(kv[q] * kv[q]);
+    }
+    const float nrm = fmaxf(sqrtf(tot), 1e-12f);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) U[q * 32 + lane][k] = kv[q] / nrm;
+    if (lane == 0) {
+      nrm_sh[k] = nrm;
+      code_sh[k] = 0u;
+    }
+  }
+
+  // ---- nearest list
+  const int tx = tid & 15, ty = tid >> 4;  // lists 4 tx .., keys 4 ty ..
+  float bd[4];
+  int bl[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    bd[i] = __builtin_huge_valf();
+    bl[i] = 0x7fffffff;
+  }
+  for (int l0 = 0; l0 < a.num_lists; l0 += kBulkLists) {
+    __syncthreads();  // U written (first pass) / the previous tile has been read
+    load_tile_transposed<E>(coarse, l0, a.num_lists, C);
+    __syncthreads();
+    float half01[4][4], dist[4][4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+      for (int d = q * 32; d < q * 32 + 32; ++d) {
+        const float4 u = *reinterpret_cast<const float4*>(&U[d][4 * ty]);
+        const float4 c = *reinterpret_cast<const float4*>(&C[d][4 * tx]);
+        const float uu[4] = {u.x, u.y, u.z, u.w}, cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float df = __fsub_rn(uu[i], cc[j]);
+            acc[i][j] = __fmaf_rn(df, df, acc[i][j]);
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (q == 0) half01[i][j] = acc[i][j];
+          if (q == 1) half01[i][j] = __fadd_rn(half01[i][j], acc[i][j]);
+          if (q == 2) dist[i][j] = acc[i][j];
+          if (q == 3) dist[i][j] = __fadd_rn(half01[i][j], __fadd_rn(dist[i][j], acc[i][j]));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int l = l0 + 4 * tx + j;  // ascending within a thread: strict < keeps the lowest index
+        if (l < a.num_lists && dist[i][j] < bd[i]) {
+          bd[i] = dist[i][j];
+          bl[i] = l;
+        }
+      }
+  }
+  // best over the 16 list blocks of a key: tx is the low four bits of the lane
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+      const float od = __shfl_xor_sync(0xffffffffu, bd[i], o);
+      const int ol = __shfl_xor_sync(0xffffffffu, bl[i], o);
+      if (od < bd[i] || (od == bd[i] && ol < bl[i])) {
+        bd[i] = od;
+        bl[i] = ol;
+      }
+    }
+    if (tx == 0) list_sh[4 * ty + i] = bl[i];
+  }
+  __syncthreads();
+
+  // ---- residuals in place of the directions, code words into the centroid tile
+  for (int i = tid; i < kBulkKeys * kD; i += kBulkThreads) {
+    const int k = i / kD, d = i % kD;
+    const int lid = list_sh[k];
+    if (key0 + k < a.n) U[d][k] = __fsub_rn(U[d][k], to_f(coarse[(size_t)lid * kD + d]));
+  }
+  float* cw = &C[0][0];  // [m][c][16]
+  for (int i = tid; i < kM * kC * kSub; i += kBulkThreads) cw[i] = to_f(books[i]);
+  __syncthreads();
+
+  // ---- nearest code word per subspace: thread -> (key, subspace), two subspaces each
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int k = tid & (kBulkKeys - 1), m = (tid >> 6) + 4 * h;
+    float r[kSub];
+#pragma unroll
+    for (int d = 0; d < kSub; ++d) r[d] = U[m * kSub + d][k];
+    float best = __builtin_huge_valf();
+    int bc = 0;
+    for (int c = 0; c < kC; ++c) {
+      const float* w = cw + (m * kC + c) * kSub;
+      float dist = 0.f;
+#pragma unroll
+      for (int d = 0; d < kSub; ++d) {
+        const float df = __fsub_rn(r[d], w[d]);
+        dist = __fmaf_rn(df, df, dist);
+      }
+      if (dist < best) {
+        best = dist;
+        bc = c;
+      }
+    }
+    atomicOr(&code_sh[k], (uint32_t)bc << (4 * m));
+  }
+  __syncthreads();
+
+  if (tid < kBulkKeys && key0 + tid < a.n) {
+    const size_t o = (size_t)s * a.n + key0 + tid;
+    a.codes[o] = code_sh[tid];
+    static_cast<E*>(a.norms)[o] = from_f<E>(nrm_sh[tid]);
+    a.list_ids[o] = (uint16_t)list_sh[tid];
+  }
+}
+
+int launch_encode_bulk(const void* keys, long long stream_stride, int streams, int n, int dtype, const void* coarse,
+                       int num_lists, const void* codebooks, uint32_t* codes, void* norms, uint16_t* list_ids,
+                       cudaStream_t st) {
+  BulkArgs a;
+  a.keys = keys;
+  a.stream_stride = stream_stride;
+  a.coarse = coarse;
+  a.codebooks = codebooks;
+  a.codes = codes;
+  a.norms = norms;
+  a.list_ids = list_ids;
+  a.n = n;
+  a.num_lists = num_lists;
+  const dim3 grid((n + kBulkKeys - 1) / kBulkKeys, streams);
+  constexpr int kSmem = kD * (kBulkKeys + kBulkLists) * (int)sizeof(float);  // 64 KB: above the default limit
+  PQHSA_DISPATCH_E(dtype, {
+    if (cudaFuncSetAttribute(encode_bulk_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+      return check_launch("encode_bulk: shared memory opt-in");
+    encode_bulk_kernel<E><<<grid, kBulkThreads, kSmem, st>>>(a);
+  });
+  return check_launch("encode_bulk");
+}
+
+}  // namespace pqhsa

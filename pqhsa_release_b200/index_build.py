@@ -9,8 +9,10 @@ nearest-code-word encoding (:97-115) and the per-list value means
 CPU generator with the reference's seeds, so the same rows are drawn as in the
 reference's CPU build.
 
-This is set-up work outside the per-step path and is expressed in torch tensor
-operations on the device; the per-step path never calls into it.
+This is set-up work outside the per-step path.  The k-means training steps are
+torch tensor operations on the device; the pass that assigns and encodes every key
+against the finished centroids and code words - the bulk of the arithmetic - is one
+CUDA kernel (``encode_bulk`` -> ``pqhsa_encode_bulk``) when the tensors are on a GPU.
 """
 
 from __future__ import annotations
@@ -19,6 +21,47 @@ import torch
 
 from .config import IVFPQConfig, validate_index_config
 from .device_index import StreamIndexTensors, codes_to_words, words_to_codes  # noqa: F401
+
+
+def encode_bulk(keys: torch.Tensor, coarse: torch.Tensor, codebooks: torch.Tensor):
+    """Assign and encode every key on the GPU with fixed codebooks (``pqhsa_encode_bulk``).
+
+    keys [S, N, 128] (rows contiguous; streams may be strided views of a cache), coarse
+    [S, L, 128], codebooks [S, 8, 16, 16], all of the keys' dtype.  Returns
+    ``(words int64 [S, N], list ids int64 [S, N], norms [S, N] in the keys' dtype)``: what
+    ``IVFPQIndex.add`` (pq_hsa/index/ivfpq.py:598-645) computes for the batch, in the
+    incremental encoder's arithmetic."""
+    from . import _lib
+    from .device_index import _DTYPE_CODE
+
+    if not keys.is_cuda:
+        raise RuntimeError("encode_bulk needs CUDA tensors: there is no CPU path")
+    if keys.dim() != 3 or keys.shape[-1] != 128:
+        raise ValueError("keys must be [streams, N, 128]")
+    if keys.dtype not in _DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {keys.dtype}")
+    s, n, _ = keys.shape
+    if n and (keys.stride(2) != 1 or keys.stride(1) != 128 or (s > 1 and keys.stride(0) < n * 128)):
+        keys = keys.contiguous()
+    coarse = coarse.to(keys.dtype).contiguous()
+    codebooks = codebooks.to(keys.dtype).contiguous()
+    if coarse.dim() != 3 or coarse.shape[0] != s or coarse.shape[2] != 128:
+        raise ValueError("coarse must be [streams, lists, 128]")
+    if tuple(codebooks.shape) != (s, 8, 16, 16):
+        raise ValueError("codebooks must be [streams, 8, 16, 16]")
+    words = torch.empty(s, n, dtype=torch.int32, device=keys.device)
+    norms = torch.empty(s, n, dtype=keys.dtype, device=keys.device)
+    if n == 0:
+        return words.long(), torch.empty(s, 0, dtype=torch.long, device=keys.device), norms
+    lids = torch.empty(s, n, dtype=torch.int16, device=keys.device)  # u16 bit patterns
+    stride = keys.stride(0) if s > 1 else max(n * 128, 1)
+    with torch.cuda.device(keys.device):
+        _lib.call(
+            "pqhsa_encode_bulk", keys.data_ptr(), stride, s, n, _DTYPE_CODE[keys.dtype], coarse.data_ptr(),
+            coarse.shape[1], codebooks.data_ptr(), words.data_ptr(), norms.data_ptr(), lids.data_ptr(),
+            torch.cuda.current_stream(keys.device).cuda_stream,
+        )
+    return words.long() & 0xFFFFFFFF, lids.long() & 0xFFFF, norms
 
 
 def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Tensor:
@@ -33,9 +76,11 @@ def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Te
     return out
 
 
-def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.dtype, eps: float):
+def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.dtype, eps: float,
+            final_assign: bool = True):
     """Batched seeded Lloyd iterations.  x [S, N, d] fp32 -> (centroids [S, k, d]
-    holding values representable in ``store_dtype``, assignments [S, N])."""
+    holding values representable in ``store_dtype``, assignments [S, N]; None when
+    ``final_assign`` is off and the caller assigns with the finished centroids itself)."""
     s, n, d = x.shape
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
@@ -60,7 +105,7 @@ def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.d
                     repl = torch.randint(0, n, (nd,), generator=gen).to(x.device)
                     new[i, ~live[i]] = x[i, repl]
         cent = new.to(store_dtype).float()
-    return cent, _assign(x, cent)
+    return cent, (_assign(x, cent) if final_assign else None)
 
 
 @torch.no_grad()
@@ -79,17 +124,26 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
     norms = torch.linalg.vector_norm(kf, dim=-1).to(dtype).clamp_min(cfg.eps)
     unit = kf / norms.float().unsqueeze(-1)
     lists = min(cfg.num_lists, n)
-    coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps)
+    on_gpu = keys.is_cuda and d == 128 and cfg.num_subspaces == 8 and cfg.num_bits == 4
+    coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps, final_assign=not on_gpu)
+    if on_gpu:
+        # the final assignment against the finished centroids, by the kernel (code words not known yet)
+        no_books = torch.zeros(s, 8, 16, 16, dtype=dtype, device=keys.device)
+        _, lid, norms = encode_bulk(keys, coarse, no_books)
     resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
     m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
     books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
     words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
     for j in range(m):
         chunk = resid[:, :, j * sub : (j + 1) * sub].contiguous()
-        books[:, j], _ = _kmeans(chunk, ncodes, cfg.pq_max_iter, cfg.seed + 10_000 + j, dtype, cfg.eps)
-        # encode with true squared distances (torch.cdist's small-size path)
-        d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
-        words |= d2.argmin(dim=-1) << (4 * j)
+        books[:, j], _ = _kmeans(chunk, ncodes, cfg.pq_max_iter, cfg.seed + 10_000 + j, dtype, cfg.eps,
+                                 final_assign=False)
+        if not on_gpu:
+            # encode with true squared distances (torch.cdist's small-size path)
+            d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
+            words |= d2.argmin(dim=-1) << (4 * j)
+    if on_gpu:
+        words, _, _ = encode_bulk(keys, coarse, books)  # same lists as above: the kernel is deterministic
     vf = values.float()
     vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
     vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
@@ -150,13 +204,16 @@ def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list
         chunk = ures[:, :, j * sub : (j + 1) * sub].contiguous()
         books[:, j] = ema(books[:, j], chunk, _assign(chunk, books[:, j]))
     books = books.to(dtype).float()
-    lid = _assign(unit, coarse)
-    resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
-    words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
-    for j in range(m):
-        chunk = resid[:, :, j * sub : (j + 1) * sub]
-        d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
-        words |= d2.argmin(dim=-1) << (4 * j)
+    if keys.is_cuda and d == 128 and m == 8 and cfg.num_bits == 4:
+        words, lid, norms = encode_bulk(keys, coarse, books)
+    else:
+        lid = _assign(unit, coarse)
+        resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
+        words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
+        for j in range(m):
+            chunk = resid[:, :, j * sub : (j + 1) * sub]
+            d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
+            words |= d2.argmin(dim=-1) << (4 * j)
     vf = values.float()
     vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
     vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)

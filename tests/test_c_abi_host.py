@@ -93,3 +93,24 @@ def test_null_params_and_topk_argument_checks():
     with pytest.raises(_lib.PqhsaError) as e:
         _lib.call("pqhsa_topk_radix", None, 1, 10, 10, 3, None, None, None)
     assert e.value.code == -1
+
+
+def test_bulk_encode_argument_checks():
+    """Validation happens before any CUDA call, so it can be exercised without a GPU."""
+    a = 4096  # a non-null, 16-byte aligned address that is never dereferenced
+    with pytest.raises(_lib.PqhsaError) as e:
+        _lib.call("pqhsa_encode_bulk", None, 128, 1, 1, _lib.BF16, a, 4, a, a, a, a, None)
+    assert e.value.code == -1
+    with pytest.raises(_lib.PqhsaError) as e:  # stream stride shorter than a stream's keys
+        _lib.call("pqhsa_encode_bulk", a, 64, 1, 1, _lib.BF16, a, 4, a, a, a, a, None)
+    assert e.value.code == -2
+    with pytest.raises(_lib.PqhsaError) as e:
+        _lib.call("pqhsa_encode_bulk", a, 128, 1, 1, _lib.BF16, a, _lib.MAX_LISTS + 1, a, a, a, a, None)
+    assert e.value.code == -2 and "num_lists" in str(e.value)
+    with pytest.raises(_lib.PqhsaError) as e:
+        _lib.call("pqhsa_encode_bulk", a + 2, 128, 1, 1, _lib.BF16, a, 4, a, a, a, a, None)
+    assert e.value.code == -2 and "aligned" in str(e.value)
+    with pytest.raises(_lib.PqhsaError) as e:
+        _lib.call("pqhsa_encode_bulk", a, 128, 1, 1, 7, a, 4, a, a, a, a, None)
+    assert e.value.code == -3
+    _lib.call("pqhsa_encode_bulk", a, 128, 1, 0, _lib.BF16, a, 4, a, a, a, a, None)  # nothing to do
