@@ -62,7 +62,7 @@ __device__ __forceinline__ void load_tile_transposed(const E* src, int row0, int
 }
 
 template <typename E>
-__global__ void __launch_bounds__(kBulkThreads, 3) encode_bulk_kernel(const BulkArgs a) {
+__global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const BulkArgs a) {
   extern __shared__ __align__(16) float bulk_smem[];
   float (*U)[kBulkKeys] = reinterpret_cast<float (*)[kBulkKeys]>(bulk_smem);                    // directions, then residuals
   float (*C)[kBulkLists] = reinterpret_cast<float (*)[kBulkLists]>(bulk_smem + kD * kBulkKeys);  // centroid tile, then code words
@@ -166,10 +166,27 @@ __global__ void __launch_bounds__(kBulkThreads, 3) encode_bulk_kernel(const Bulk
   __syncthreads();
 
   // ---- residuals in place of the directions, code words into the centroid tile
-  for (int i = tid; i < kBulkKeys * kD; i += kBulkThreads) {
-    const int k = i / kD, d = i % kD;
-    const int lid = list_sh[k];
-    if (key0 + k < a.n) U[d][k] = __fsub_rn(U[d][k], to_f(coarse[(size_t)lid * kD + d]));
+  // lane -> key: the shared accesses touch 32 banks; the centroid rows come from L2
+  {
+    const int k = tid & (kBulkKeys - 1);
+    const E* crow = coarse + (size_t)list_sh[k] * kD;
+    constexpr int kPer = 16 / (int)sizeof(E);
+    if (key0 + k < a.n) {
+      for (int v = tid >> 6; v < kD / kPer; v += kBulkThreads / kBulkKeys) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(crow) + v);
+        float c[kPer];
+        if constexpr (sizeof(E) == 2) {
+          unpack8(raw, static_cast<const E*>(nullptr), c);
+        } else {
+          c[0] = __uint_as_float(raw.x);
+          c[1] = __uint_as_float(raw.y);
+          c[2] = __uint_as_float(raw.z);
+          c[3] = __uint_as_float(raw.w);
+        }
+#pragma unroll
+        for (int d = 0; d < kPer; ++d) U[v * kPer + d][k] = __fsub_rn(U[v * kPer + d][k], c[d]);
+      }
+    }
   }
   float* cw = &C[0][0];  // [m][c][16]
   for (int i = tid; i < kM * kC * kSub; i += kBulkThreads) cw[i] = to_f(books[i]);
@@ -185,12 +202,17 @@ __global__ void __launch_bounds__(kBulkThreads, 3) encode_bulk_kernel(const Bulk
     float best = __builtin_huge_valf();
     int bc = 0;
     for (int c = 0; c < kC; ++c) {
-      const float* w = cw + (m * kC + c) * kSub;
+      const float4* w4 = reinterpret_cast<const float4*>(cw + (m * kC + c) * kSub);
       float dist = 0.f;
 #pragma unroll
-      for (int d = 0; d < kSub; ++d) {
-        const float df = __fsub_rn(r[d], w[d]);
-        dist = __fmaf_rn(df, df, dist);
+      for (int v = 0; v < kSub / 4; ++v) {
+        const float4 w = w4[v];
+        const float ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          const float df = __fsub_rn(r[4 * v + d], ww[d]);
+          dist = __fmaf_rn(df, df, dist);
+        }
       }
       if (dist < best) {
         best = dist;
