@@ -18,9 +18,11 @@
 
 namespace pqhsa {
 
-constexpr int kBulkKeys = 64;      // keys per CTA
+#ifndef PQHSA_BULK_NJ
+#define PQHSA_BULK_NJ 2
+#endif
 constexpr int kBulkLists = 64;     // lists per centroid tile
-constexpr int kBulkThreads = 256;  // 16 key blocks x 16 list blocks
+constexpr int kBulkThreads = 256;
 
 struct BulkArgs {
   const void* keys;
@@ -61,8 +63,12 @@ __device__ __forceinline__ void load_tile_transposed(const E* src, int row0, int
   }
 }
 
-template <typename E>
+// NJ = blocks of 4 lists per thread.  A warp spans 16 / NJ threads along the lists of a tile and
+// 2 NJ threads along the keys; a thread owns 4 keys x 4 NJ lists; a CTA takes 64 NJ keys.
+template <typename E, int NJ>
 __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const BulkArgs a) {
+  constexpr int kBulkKeys = 64 * NJ;
+  constexpr int kTx = 16 / NJ;  // threads of a warp along the lists
   extern __shared__ __align__(16) float bulk_smem[];
   float (*U)[kBulkKeys] = reinterpret_cast<float (*)[kBulkKeys]>(bulk_smem);                    // directions, then residuals
   float (*C)[kBulkLists] = reinterpret_cast<float (*)[kBulkLists]>(bulk_smem + kD * kBulkKeys);  // centroid tile, then code words
@@ -95,7 +101,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
   }
 
   // ---- nearest list
-  const int tx = tid & 15, ty = tid >> 4;  // lists 4 tx .., keys 4 ty ..
+  const int tx = lane % kTx, ty = warp * (32 / kTx) + lane / kTx;  // lists 4 tx (+ 4 kTx jb) .., keys 4 ty ..
   float bd[4];
   int bl[4];
 #pragma unroll
@@ -107,23 +113,31 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
     __syncthreads();  // U written (first pass) / the previous tile has been read
     load_tile_transposed<E>(coarse, l0, a.num_lists, C);
     __syncthreads();
-    float half01[4][4], dist[4][4];
+    float half01[4][4 * NJ], dist[4][4 * NJ];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float acc[4][4];
+      float acc[4][4 * NJ];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-#pragma unroll 8
+        for (int j = 0; j < 4 * NJ; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
       for (int d = q * 32; d < q * 32 + 32; ++d) {
         const float4 u = *reinterpret_cast<const float4*>(&U[d][4 * ty]);
-        const float4 c = *reinterpret_cast<const float4*>(&C[d][4 * tx]);
-        const float uu[4] = {u.x, u.y, u.z, u.w}, cc[4] = {c.x, c.y, c.z, c.w};
+        const float uu[4] = {u.x, u.y, u.z, u.w};
+        float cc[4 * NJ];
+#pragma unroll
+        for (int jb = 0; jb < NJ; ++jb) {
+          const float4 c = *reinterpret_cast<const float4*>(&C[d][4 * tx + 4 * kTx * jb]);
+          cc[4 * jb] = c.x;
+          cc[4 * jb + 1] = c.y;
+          cc[4 * jb + 2] = c.z;
+          cc[4 * jb + 3] = c.w;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < 4 * NJ; ++j) {
             const float df = __fsub_rn(uu[i], cc[j]);
             acc[i][j] = __fmaf_rn(df, df, acc[i][j]);
           }
@@ -131,7 +145,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 4 * NJ; ++j) {
           if (q == 0) half01[i][j] = acc[i][j];
           if (q == 1) half01[i][j] = __fadd_rn(half01[i][j], acc[i][j]);
           if (q == 2) dist[i][j] = acc[i][j];
@@ -141,19 +155,19 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int l = l0 + 4 * tx + j;  // ascending within a thread: strict < keeps the lowest index
+      for (int j = 0; j < 4 * NJ; ++j) {
+        const int l = l0 + 4 * tx + 4 * kTx * (j >> 2) + (j & 3);  // ascending within a thread: strict < keeps the lowest index
         if (l < a.num_lists && dist[i][j] < bd[i]) {
           bd[i] = dist[i][j];
           bl[i] = l;
         }
       }
   }
-  // best over the 16 list blocks of a key: tx is the low four bits of the lane
+  // best over the threads that share a key: tx is the low bits of the lane
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
 #pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {
+    for (int o = 1; o < kTx; o <<= 1) {
       const float od = __shfl_xor_sync(0xffffffffu, bd[i], o);
       const int ol = __shfl_xor_sync(0xffffffffu, bl[i], o);
       if (od < bd[i] || (od == bd[i] && ol < bl[i])) {
@@ -168,11 +182,11 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
   // ---- residuals in place of the directions, code words into the centroid tile
   // lane -> key: the shared accesses touch 32 banks; the centroid rows come from L2
   {
-    const int k = tid & (kBulkKeys - 1);
+    const int k = tid % kBulkKeys;
     const E* crow = coarse + (size_t)list_sh[k] * kD;
     constexpr int kPer = 16 / (int)sizeof(E);
     if (key0 + k < a.n) {
-      for (int v = tid >> 6; v < kD / kPer; v += kBulkThreads / kBulkKeys) {
+      for (int v = tid / kBulkKeys; v < kD / kPer; v += kBulkThreads / kBulkKeys) {
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(crow) + v);
         float c[kPer];
         if constexpr (sizeof(E) == 2) {
@@ -192,10 +206,11 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
   for (int i = tid; i < kM * kC * kSub; i += kBulkThreads) cw[i] = to_f(books[i]);
   __syncthreads();
 
-  // ---- nearest code word per subspace: thread -> (key, subspace), two subspaces each
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int k = tid & (kBulkKeys - 1), m = (tid >> 6) + 4 * h;
+  // ---- nearest code word per subspace: thread -> (key, subspace), 2 NJ subspaces each
+  constexpr int kKeyGroups = kBulkThreads / kBulkKeys;
+#pragma unroll 1
+  for (int h = 0; h < kM / kKeyGroups; ++h) {
+    const int k = tid % kBulkKeys, m = tid / kBulkKeys + kKeyGroups * h;
     float r[kSub];
 #pragma unroll
     for (int d = 0; d < kSub; ++d) r[d] = U[m * kSub + d][k];
@@ -244,12 +259,15 @@ int launch_encode_bulk(const void* keys, long long stream_stride, int streams, i
   a.list_ids = list_ids;
   a.n = n;
   a.num_lists = num_lists;
-  const dim3 grid((n + kBulkKeys - 1) / kBulkKeys, streams);
-  constexpr int kSmem = kD * (kBulkKeys + kBulkLists) * (int)sizeof(float);  // 64 KB: above the default limit
+  constexpr int NJ = PQHSA_BULK_NJ;
+  constexpr int kKeys = 64 * NJ;
+  const dim3 grid((n + kKeys - 1) / kKeys, streams);
+  constexpr int kSmem = kD * (kKeys + kBulkLists) * (int)sizeof(float);  // above the default limit
   PQHSA_DISPATCH_E(dtype, {
-    if (cudaFuncSetAttribute(encode_bulk_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+    auto kern = encode_bulk_kernel<E, NJ>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return check_launch("encode_bulk: shared memory opt-in");
-    encode_bulk_kernel<E><<<grid, kBulkThreads, kSmem, st>>>(a);
+    kern<<<grid, kBulkThreads, kSmem, st>>>(a);
   });
   return check_launch("encode_bulk");
 }
