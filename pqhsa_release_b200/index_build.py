@@ -77,10 +77,11 @@ def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Te
 
 
 def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.dtype, eps: float,
-            final_assign: bool = True):
+            final_assign: bool = True, assign_fn=None):
     """Batched seeded Lloyd iterations.  x [S, N, d] fp32 -> (centroids [S, k, d]
     holding values representable in ``store_dtype``, assignments [S, N]; None when
-    ``final_assign`` is off and the caller assigns with the finished centroids itself)."""
+    ``final_assign`` is off and the caller assigns with the finished centroids itself).
+    ``assign_fn(centroids) -> [S, N]`` replaces the torch assignment of the Lloyd steps."""
     s, n, d = x.shape
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
@@ -90,7 +91,7 @@ def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.d
         rows = torch.cat([torch.arange(n), torch.randint(0, n, (k - n,), generator=gen)])
     cent = x[:, rows.to(x.device)].to(store_dtype).float()
     for _ in range(iters):
-        a = _assign(x, cent)
+        a = _assign(x, cent) if assign_fn is None else assign_fn(cent)
         sums = torch.zeros(s, k, d, dtype=torch.float32, device=x.device)
         sums.scatter_add_(1, a.unsqueeze(-1).expand(-1, -1, d), x)
         cnt = torch.zeros(s, k, dtype=torch.float32, device=x.device)
@@ -125,11 +126,15 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
     unit = kf / norms.float().unsqueeze(-1)
     lists = min(cfg.num_lists, n)
     on_gpu = keys.is_cuda and d == 128 and cfg.num_subspaces == 8 and cfg.num_bits == 4
-    coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps, final_assign=not on_gpu)
     if on_gpu:
-        # the final assignment against the finished centroids, by the kernel (code words not known yet)
+        # every assignment against the coarse centroids - the Lloyd steps' and the final one - by the
+        # kernel (the code words are not known yet: their half of the result is ignored)
         no_books = torch.zeros(s, 8, 16, 16, dtype=dtype, device=keys.device)
+        coarse, _ = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps, final_assign=False,
+                            assign_fn=lambda cent: encode_bulk(keys, cent, no_books)[1])
         _, lid, norms = encode_bulk(keys, coarse, no_books)
+    else:
+        coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps)
     resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
     m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
     books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
