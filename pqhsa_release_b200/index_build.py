@@ -261,8 +261,30 @@ if __name__ == "__main__":
     ap.add_argument("--lists", type=int, default=512)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"])
+    ap.add_argument("--build", action="store_true", help="also time a whole build_index_batch and a refresh")
     ns = ap.parse_args()
     dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[ns.dtype]
+    if ns.build:
+        import time
+
+        from .config import paper_index_config
+
+        cfg = paper_index_config(num_lists=ns.lists)
+        kk = torch.randn(ns.streams, ns.keys + 256, 128, device="cuda").to(dt)
+        vv = torch.randn(ns.streams, ns.keys + 256, 128, device="cuda").to(dt)
+        build_index_batch(kk[:, :4096], vv[:, :4096], cfg)  # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        built = build_index_batch(kk[:, : ns.keys], vv[:, : ns.keys], cfg)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        cur = [{"coarse": b.coarse_centroids, "codebooks": b.codebooks} for b in built]
+        online_refresh_batch(kk, vv, cur, 256, cfg)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        print(f"build_index_batch streams={ns.streams} keys={ns.keys}: {(t1 - t0) * 1e3:.0f} ms; "
+              f"online_refresh_batch (+256 keys): {(t2 - t1) * 1e3:.0f} ms (wall clock around a device synchronise)")
+        del kk, vv, built, cur
     ms = _time_encode_bulk(ns.streams, ns.keys, ns.lists, ns.iters, dt)
     pairs = ns.streams * ns.keys * ns.lists * 128
     print(f"encode_bulk streams={ns.streams} keys={ns.keys} lists={ns.lists} {ns.dtype}: {ms:.3f} ms/call, "
