@@ -204,7 +204,7 @@ class StepRunner:
                 self.exchange = None
                 pool.p.peer_world = 0
         self.graph = None
-        self.launches_per_step = 5  # tables + append + encode, scan, select, attend + background, combine (+ the peer wait when sharded)
+        self.launches_per_step = 7  # tables + append + encode, thresholds, scan, candidates, emit, attend + background, combine (+ the peer wait when sharded)
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture

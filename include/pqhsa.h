@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define PQHSA_ABI_VERSION 3
+#define PQHSA_ABI_VERSION 4
 
 /* fixed shape of the index (pq_hsa/kernels/cuda/pq_fused_h20.cu:26-35 fixes the
  * same: 8 subspaces x 4 bits, at most 512 lists, head_dim 128) */
@@ -33,6 +33,7 @@ extern "C" {
 #define PQHSA_UNIT_KEYS 128     /* a scan unit = at most this many slots of one list */
 #define PQHSA_SAMPLE_KEYS 4096  /* keys scored per stream to place the candidate threshold */
 #define PQHSA_HIST_BINS 2048    /* resolution of the sample histogram */
+#define PQHSA_SELECT_BINS 1024  /* candidate bins between the threshold and its upper companion; one more above */
 
 enum pqhsa_status {
   PQHSA_OK = 0,
@@ -147,9 +148,18 @@ typedef struct pqhsa_params {
   void *peer_seq;          /* device int32 [2] of this rank: steps exchanged so far, error flag */
   int32_t peer_world;
   int32_t peer_rank;
+  int32_t peer_wait_polls; /* polls (about 200 ns apart) pqhsa_wait_peers makes before it gives up; 0 = about a second */
+  int32_t external_append; /* 1: pqhsa_decode_step_append with new_k == NULL advances every live stream's length by
+                              one without writing a row - the caller's own cache write (vLLM's
+                              reshape_and_cache_flash) has already stored this step's K/V.  0: the length stays. */
 
   const void *q;           /* E [S, G, 128]: query heads h*G .. h*G+G-1 of KV head h */
   void *out;               /* E [S, G, 128] */
+  const int32_t *io_map;   /* optional device int32 [S]: stream s reads its G query rows from block io_map[s] of q
+                              and writes block io_map[s] of out (a block = G x 128 elements), so that streams can
+                              keep their pool slot while the batch order of their requests changes from step to
+                              step; negative = the stream is idle this step (nothing is read or written for
+                              it).  NULL = block s.  The peer exchange sends rows in stream order either way. */
   void *workspace;         /* >= pqhsa_workspace_bytes(), 256-byte aligned */
   size_t workspace_bytes;
 } pqhsa_params;
@@ -162,7 +172,7 @@ typedef struct pqhsa_ws_layout {
   size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>                 */
   size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>                    */
   size_t pair_tab;     /* float  [S, G/GP, 4, 256, GP], GP = min(G, 4): byte-pair sums of lut for the scan */
-  size_t row_bin;      /* float  [R, 2]   sample histogram origin and 1 / bin width       */
+  size_t row_bin;      /* float  [R, 2]   origin (= row_tau) and 1 / width of the candidate bins of the selection */
   size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
   size_t ticket;       /* int32  [S, 2]   arrival counters of the table kernel's CTAs (0 between launches) */
   size_t slog;         /* float  [R, PQHSA_SAMPLE_KEYS]  approximate logits of the sample keys           */
@@ -172,12 +182,21 @@ typedef struct pqhsa_ws_layout {
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */
   size_t row_info;     /* int32  [R, 8]   see enum pqhsa_row_info_slot                     */
   size_t hitmap;       /* uint32 [R, unit_capacity, 4]  bit b of word (u, i): slot first(u) + 32 i + b reached the threshold */
+  size_t cand_key;     /* uint32 [R, parts, seg]  candidates of a row, listed by `parts` CTAs: order-preserving key of the logit */
+  size_t cand_slot;    /* int32  [R, parts, seg]  ... their slot                                      */
+  size_t cand_pos;     /* int32  [R, parts, seg]  ... token position                                  */
+  size_t cand_term;    /* float  [R, parts, seg]  ... the term the scan added to the unit's exp-sum   */
+  size_t cand_unit;    /* uint16 [R, parts, seg]  ... scan unit                                       */
+  size_t part_hist;    /* uint32 [R, parts, PQHSA_SELECT_BINS + 4]  candidates per bin and part        */
+  size_t part_cnt;     /* int32  [R, parts]       candidates found by each part (> seg: overflow)      */
   size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */
   size_t sel_off;      /* int64  [R, kcap]  element offset of their K/V rows in the cache  */
   size_t partial;      /* float  [R, chunks + 5, 130]  split-K partials (max, sum, acc): exact chunks, then up to 5 background parts */
   size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
   size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
   size_t combine_ticket; /* int32 [1]     finished CTAs of the combine kernel (0 between launches)          */
+  int32_t parts;       /* CTAs that share the selection of one query row */
+  int32_t seg;         /* candidates one of them can list */
   int32_t kcap;        /* row stride of sel_* */
   int32_t tail_cap;    /* row stride of tail_logit */
   int32_t chunks;      /* split-K partials per row */

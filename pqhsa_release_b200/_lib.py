@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 2048
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
@@ -40,8 +40,8 @@ class Params(C.Structure):
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
         ("peer_out", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_seq", C.c_void_p),
-        ("peer_world", C.c_int32), ("peer_rank", C.c_int32),
-        ("q", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_wait_polls", C.c_int32), ("external_append", C.c_int32),
+        ("q", C.c_void_p), ("out", C.c_void_p), ("io_map", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -53,8 +53,10 @@ class WsLayout(C.Structure):
         ("row_bin", C.c_size_t),
         ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
+        ("cand_key", C.c_size_t), ("cand_slot", C.c_size_t), ("cand_pos", C.c_size_t), ("cand_term", C.c_size_t),
+        ("cand_unit", C.c_size_t), ("part_hist", C.c_size_t), ("part_cnt", C.c_size_t),
         ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t), ("row_ticket", C.c_size_t), ("work_counter", C.c_size_t), ("combine_ticket", C.c_size_t),
-        ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
+        ("parts", C.c_int32), ("seg", C.c_int32), ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]
 
 

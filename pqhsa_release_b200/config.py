@@ -136,6 +136,9 @@ def validate_attention_config(cfg: SparseAttentionConfig) -> None:
         )
     if cfg.kv_storage != "device":
         raise ValueError("kv_storage must be 'device': there is no CPU path")
+    if getattr(cfg, "codebook_refresh_interval", None) is not None:
+        raise ValueError("codebook_refresh_interval is not supported: the B200 path has no warm-start retrain "
+                         "(pq_hsa/attention/kv_cache.py:276-314); leave it None")
 
 
 def resolve_topk(retrieval_len: int, cfg: SparseAttentionConfig) -> int:

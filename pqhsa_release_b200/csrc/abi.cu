@@ -53,6 +53,17 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->kcap = topk_capacity(p);
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
+  // The selection of a row is shared by `parts` CTAs (a power of two): enough of them to fill the GPU when
+  // there are few rows, and enough that a part's candidate list (`seg` entries, a quarter more than an even
+  // share of the candidates a row can reasonably have) fits in shared memory.
+  {
+    const size_t ccap = cap < (size_t)2 * o->kcap + 2048 ? cap : (size_t)2 * o->kcap + 2048;
+    int parts = 1;
+    while (parts < 16 && (R * parts < 296 || ccap * 5 / 4 > (size_t)parts * 8192)) parts *= 2;
+    o->parts = parts;
+    o->seg = (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
+  }
+  const size_t nrec = R * (size_t)o->parts * (size_t)o->seg;
   size_t off = 0;
   auto take = [&](size_t bytes) {
     const size_t at = off;
@@ -72,6 +83,13 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
   o->row_info = take(R * kRI * sizeof(int32_t));
   o->hitmap = take(R * (size_t)p->unit_capacity * (kUnit / 32) * sizeof(uint32_t));
+  o->cand_key = take(nrec * sizeof(uint32_t));
+  o->cand_slot = take(nrec * sizeof(int32_t));
+  o->cand_pos = take(nrec * sizeof(int32_t));
+  o->cand_term = take(nrec * sizeof(float));
+  o->cand_unit = take(nrec * sizeof(uint16_t));
+  o->part_hist = take(R * (size_t)o->parts * (PQHSA_SELECT_BINS + 4) * sizeof(uint32_t));
+  o->part_cnt = take(R * (size_t)o->parts * sizeof(int32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
   o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
   o->partial = take(R * (size_t)(o->chunks + kBgParts) * kPartial * sizeof(float));
@@ -124,12 +142,19 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
       return set_error(PQHSA_E_NULL, "peer_out / peer_flags / peer_seq is null with peer_world > 1");
     if (p->peer_rank < 0 || p->peer_rank >= p->peer_world || p->peer_world > 32)
       return set_error(PQHSA_E_SHAPE, "peer_rank %d / peer_world %d out of range", p->peer_rank, p->peer_world);
+    if (p->peer_wait_polls < 0) return set_error(PQHSA_E_SHAPE, "peer_wait_polls must be non-negative");
   }
   if (need_io) {
     if (!p->q || !p->out) return set_error(PQHSA_E_NULL, "q / out is null");
     if (((uintptr_t)p->q | (uintptr_t)p->out) & 15) return set_error(PQHSA_E_SHAPE, "q / out must be 16-byte aligned");
   }
   if (need_ws) {
+    {
+      pqhsa_ws_layout w;
+      layout_of(p, &w);
+      if (w.chunks + kBgParts > kD)
+        return set_error(PQHSA_E_SHAPE, "%d partials per query row exceed %d: lower max_full or the top-k", w.chunks + kBgParts, kD);
+    }
     if (!p->workspace) return set_error(PQHSA_E_WORKSPACE, "workspace is null");
     if ((uintptr_t)p->workspace & 255) return set_error(PQHSA_E_WORKSPACE, "workspace must be 256-byte aligned");
     pqhsa_ws_layout w;

@@ -42,6 +42,7 @@ static_assert(kAttWarps * 32 == kChunk, "one entry per lane and chunk");
 
 struct AttendArgs {
   const void* q;
+  const int32_t* io_map;  // [S] block of q / out of a stream, or null: block s
   const void* k_base;
   const void* v_base;
   KvAddr kv;
@@ -261,7 +262,13 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
     }
     // query slice of this lane, pre-multiplied by scale * log2(e)
     float qv[8];
-    load8(static_cast<const E*>(a.q) + (size_t)row * kD + l16 * 8, qv);
+    const int qb = a.io_map != nullptr ? a.io_map[s] : s;  // negative: idle stream (it has no entries either)
+    if (qb >= 0) {
+      load8(static_cast<const E*>(a.q) + ((size_t)qb * a.G + (row - s * a.G)) * kD + l16 * 8, qv);
+    } else {
+#pragma unroll
+      for (int d = 0; d < 8; ++d) qv[d] = 0.f;
+    }
 #pragma unroll
     for (int d = 0; d < 8; ++d) qv[d] *= a.scale * kLog2e;
 
@@ -394,72 +401,82 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
 
 // One CTA per query row folds the row's partials (exact chunks + background) into the output row:
 // out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M)  (pq_attend_reduce_mw,
-// pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).
+// pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).  Thread d owns output dim d.  Everything a thread needs
+// of the first 32 partials - their (max, sum) pairs, which every thread of a warp reads from the same
+// addresses, and its own dim of their accumulators - is requested at once: one round trip, no barrier.
 template <typename E>
 __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
   const int row = blockIdx.x, tid = threadIdx.x;
-  const int slots = a.chunks + a.bg_parts;  // <= kD, checked at launch; empty chunks carry (-inf, 0)
+  const int slots = a.chunks + a.bg_parts;  // <= kD, checked with the parameters; empty chunks carry (-inf, 0)
   const float* pp = a.partial + (size_t)row * (a.chunks + kBgParts) * kPartial;
-  __shared__ float fs[kD], red[kD / 32];
-  // thread p takes partial p's (max, sum): one round trip for all of them
-  const float mp = tid < slots ? pp[(size_t)tid * kPartial] : kNegInf;
-  const float lp = tid < slots ? pp[(size_t)tid * kPartial + 1] : 0.f;
-  float M = warp_max(mp);
-  if ((tid & 31) == 0) red[tid >> 5] = M;
-  __syncthreads();
-  M = red[0];
+  constexpr int kFirst = 32;
+  float m[kFirst], l[kFirst], v[kFirst];
 #pragma unroll
-  for (int w = 1; w < kD / 32; ++w) M = fmaxf(M, red[w]);
-  const float f = (mp == kNegInf) ? 0.f : ex2(mp - M);
-  fs[tid] = f;
-  float L = warp_sum(lp * f);
-  __syncthreads();
-  if ((tid & 31) == 0) red[tid >> 5] = L;
-  __syncthreads();
-  L = red[0];
-#pragma unroll
-  for (int w = 1; w < kD / 32; ++w) L += red[w];
-  // ... and one for the accumulators (32 partials per batch)
-  float A = 0.f;
-  for (int p0 = 0; p0 < slots; p0 += 32) {
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int p = p0 + i;
-      v[i] = (p < slots && fs[p] != 0.f) ? pp[(size_t)p * kPartial + 2 + tid] : 0.f;
+  for (int p = 0; p < kFirst; ++p) {
+    m[p] = kNegInf;
+    l[p] = 0.f;
+    v[p] = 0.f;
+    if (p < slots) {
+      m[p] = __ldcg(pp + (size_t)p * kPartial);
+      l[p] = __ldcg(pp + (size_t)p * kPartial + 1);
+      v[p] = __ldcg(pp + (size_t)p * kPartial + 2 + tid);
     }
+  }
+  float M = m[0];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) A = fmaf(v[i], p0 + i < slots ? fs[p0 + i] : 0.f, A);
+  for (int p = 1; p < kFirst; ++p) M = fmaxf(M, m[p]);
+  float L = 0.f, A = 0.f;
+#pragma unroll
+  for (int p = 0; p < kFirst; ++p) {
+    const float f = (m[p] == kNegInf) ? 0.f : ex2(m[p] - M);
+    L = fmaf(l[p], f, L);
+    A = fmaf(v[p], f, A);
+  }
+  for (int p = kFirst; p < slots; ++p) {  // long rows: the remaining partials one by one
+    const float mp = __ldcg(pp + (size_t)p * kPartial);
+    if (mp == kNegInf) continue;
+    const float lp = __ldcg(pp + (size_t)p * kPartial + 1), vp = __ldcg(pp + (size_t)p * kPartial + 2 + tid);
+    const float Mn = fmaxf(M, mp);
+    const float fo = (M == kNegInf) ? 0.f : ex2(M - Mn), fn = ex2(mp - Mn);
+    L = L * fo + lp * fn;
+    A = A * fo + vp * fn;
+    M = Mn;
   }
   const E res = from_f<E>(A / fmaxf(L, 1.17549435e-38f));
-  static_cast<E*>(a.out)[(size_t)row * kD + tid] = res;
+  {
+    const int s = row / a.G;
+    const int ob = a.io_map != nullptr ? a.io_map[s] : s;  // negative: idle stream, nothing to write
+    if (ob >= 0) static_cast<E*>(a.out)[((size_t)ob * a.G + (row - s * a.G)) * kD + tid] = res;
+  }
   if (a.peer_world > 1) {
-    // The CTA that finishes last sends this rank's rows to every rank's gather buffer (16-byte stores into
-    // peer memory over NVLink; the buffer of this step's parity), fences once at system scope and raises
-    // this rank's flag on every rank.
+    // Every CTA sends its own row to every rank's gather buffer (16-byte stores into peer memory over
+    // NVLink; the buffer of this step's parity) and fences at system scope; the CTA that arrives last at
+    // the ticket then raises this rank's flag on every rank.  Nobody waits.
+    __shared__ __align__(16) E row_s[kD];
     __shared__ int last_s;
     const int seq0 = a.peer_seq[0];  // steps before this one: only the last CTA changes it, after all have read it
-    __syncthreads();                 // the CTA's row is written ...
+    row_s[tid] = res;
+    __syncthreads();
+    constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
+    if (tid < kVecs) {
+      const uint4 vec = reinterpret_cast<const uint4*>(row_s)[tid];
+      const size_t at = (((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row) * kVecs + tid;
+      for (int r = 0; r < a.peer_world; ++r) reinterpret_cast<uint4*>(a.peer_out[r])[at] = vec;
+      __threadfence_system();
+    }
+    __syncthreads();  // the row's stores are fenced ...
     if (tid == 0) {
-      __threadfence();               // ... and visible device-wide before the ticket
+      __threadfence();  // ... before the ticket
       const int t = atomicAdd(a.combine_ticket, 1);
       last_s = (t == (int)gridDim.x - 1);
     }
     __syncthreads();
     if (last_s) {
-      constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
-      const size_t base = ((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R * kVecs;
-      const uint4* src = reinterpret_cast<const uint4*>(a.out);
-      for (int i = tid; i < a.R * kVecs; i += kD) {
-        const uint4 v = __ldcg(src + i);  // the other CTAs' rows, through L2
-        for (int r = 0; r < a.peer_world; ++r) reinterpret_cast<uint4*>(a.peer_out[r])[base + i] = v;
-      }
-      __threadfence_system();
-      __syncthreads();
       if (tid == 0) {
         a.combine_ticket[0] = 0;
         a.peer_seq[0] = seq0 + 1;
       }
+      __threadfence_system();
       if (tid < a.peer_world) {
         volatile int32_t* f = a.peer_flags[tid] + a.peer_rank;
         *f = seq0 + 1;
@@ -469,15 +486,17 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
 }
 
 // One warp: lane r waits for rank r's flag in this rank's flag array to reach this rank's step count.
-// The wait is bounded: when the limit runs out the error flag is set and the kernel returns.
-__global__ void __launch_bounds__(32) wait_peers_kernel(int32_t* const* peer_flags, int32_t* peer_seq, int world, int rank) {
+// The wait is bounded: when `polls` polls (about 200 ns apart) have passed the error flag is set and the
+// kernel returns.
+__global__ void __launch_bounds__(32) wait_peers_kernel(int32_t* const* peer_flags, int32_t* peer_seq, int world, int rank,
+                                                        int polls) {
   const int lane = threadIdx.x;
   const int target = peer_seq[0];
   bool ok = true;
   if (lane < world) {
     volatile const int32_t* f = peer_flags[rank] + lane;
     ok = false;
-    for (int it = 0; it < (1 << 22); ++it) {  // about a second
+    for (int it = 0; it < polls; ++it) {
       if (*f - target >= 0) {
         ok = true;
         break;
@@ -503,7 +522,6 @@ static int launch_attend_t(const AttendArgs& a, bool combine, cudaStream_t st) {
   if (grid > items) grid = items;
   if (grid < 1) grid = 1;
   if (combine) {
-    if (a.chunks + kBgParts > kD) return set_error(PQHSA_E_SHAPE, "%d partials per row exceed %d", a.chunks + kBgParts, kD);
     combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
     return check_launch("combine");
   }
@@ -515,6 +533,7 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
   char* ws = static_cast<char*>(p.workspace);
   AttendArgs a;
   a.q = p.q;
+  a.io_map = p.io_map;
   a.k_base = p.k_base;
   a.v_base = p.v_base;
   a.kv = make_kvaddr(p);
@@ -559,7 +578,7 @@ int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
 }
 int launch_wait_peers(const pqhsa_params& p, cudaStream_t st) {
   wait_peers_kernel<<<1, 32, 0, st>>>(static_cast<int32_t* const*>(p.peer_flags), static_cast<int32_t*>(p.peer_seq),
-                                      p.peer_world, p.peer_rank);
+                                      p.peer_world, p.peer_rank, p.peer_wait_polls > 0 ? p.peer_wait_polls : (1 << 22));
   return check_launch("wait_peers");
 }
 

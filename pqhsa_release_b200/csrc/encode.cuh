@@ -139,7 +139,7 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
     // 4 lanes per list (32 dims each, four 16-byte loads), 64 lists per pass, two passes of
     // loads in flight at a time: the 128 KB of centroids stream in a handful of round trips
     float bd = __builtin_huge_valf();
-    int bl = 0x7fffffff;
+    int bl = 0;  // stays in range when every distance is NaN (a key row holding NaN or Inf): argmin then gives list 0
     {
       float uq[32];
 #pragma unroll

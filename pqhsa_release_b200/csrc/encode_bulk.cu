@@ -10,10 +10,10 @@
 // encoded here and the same key encoded by pqhsa_append_encode get the same list, code and norm.
 //
 // Shape of the work: N x L x 128 subtract-and-fma pairs per stream (fp32 pipe bound), the
-// code-word search is 1/32 of that.  One CTA takes 64 keys; their directions stay in shared
+// code-word search is 1/32 of that.  One CTA takes 128 keys; their directions stay in shared
 // memory, dimension-major, while the stream's centroids pass through a second shared tile 64
-// lists at a time.  A thread owns a 4-key x 4-list block of distances, so one pair of 16-byte
-// shared loads feeds 16 subtract-fma pairs.
+// lists at a time.  A thread owns a 4-key x 8-list block of distances, so three 16-byte
+// shared loads feed 32 subtract-fma pairs.
 #include "common.cuh"
 
 namespace pqhsa {
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     bd[i] = __builtin_huge_valf();
-    bl[i] = 0x7fffffff;
+    bl[i] = 0;  // stays in range when every distance is NaN (a key row holding NaN or Inf): argmin then gives list 0
   }
   for (int l0 = 0; l0 < a.num_lists; l0 += kBulkLists) {
     __syncthreads();  // U written (first pass) / the previous tile has been read

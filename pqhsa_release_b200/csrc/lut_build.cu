@@ -1,9 +1,11 @@
-// First kernel of a decode step: per-query, per-head table construction, optionally fused with the step's token append (raw K/V row
-// write) and the incremental encode of the key that left the local window.  The CTAs of a
-// stream take roles by blockIdx.y - list scores (176 lists each; the first also publishes the
-// tables and writes the K/V row), encode - and run
-// side by side; nobody changes a stream counter before every CTA of the stream has arrived,
-// so all roles see the same state.
+// First two kernels of a decode step.
+//
+// lut_build_kernel: per-query, per-head table construction, optionally fused with the step's token
+// append (raw K/V row write) and the incremental encode of the key that left the local window.  The
+// CTAs of a stream take roles by blockIdx.y - list scores for 64 lists each (they also share out the
+// byte-pair tables; the first one writes the K/V row), encode - and run side by side; the stream's
+// length and its norm bound change once all of them are done (arrival counter, no waiting), the tail
+// count is written by the encode CTA, which is the only one that reads it after the start.
 //
 // For every stream s and query row g:
 //   lut[s][g][m][c]      = scale * <q_g restricted to subspace m, codebooks[s][m][c]>
@@ -12,31 +14,35 @@
 // (pq_hsa/index/ivfpq.py:1061-1118); production folds |q| and the softmax scale
 // into the tables (benchmarks/e2e_pq_param_sweep.py:228-249,
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:2975-3051), as is done here, in fp32.
-//
-// The table CTA also folds the 8 nibble tables into the 4 byte-pair tables the scan looks
-// codes up in.
+// The 8 nibble tables are also folded into the 4 byte-pair tables the scan looks codes up in.
 //
 // Threshold estimate.  The exact top-K needs the K-th largest of N logits, which is not
 // known before the scan.  A stratified sample of 4096 slots of the list-sorted region
 // (contiguous records made when the layout was made) is scored by the list CTAs - each the
-// sample keys of its own 176 lists, whose scores it has just computed - and their logits go to
-// the rows' sample arrays.  The list CTA of a stream that arrives last among the list CTAs
-// (arrival counter, no waiting) histograms a row's sample logits over their own range, walks
-// the histogram from the top and takes as threshold tau the logit below which all but r
-// sample keys lie, r = f n + margin * sqrt(f n) + 1 with
-// f = K / N.  The scan then marks the keys with logit >= tau (about 1.7 K of them) and the
-// selection kernel takes the exact top K among them.  tau is only a filter: if fewer than K
-// candidates turn up (probability ~1e-9 at the default margin of 6 sigma) the selection
-// kernel falls back to all keys, so the result is exact either way.
+// sample keys of its own lists, whose scores it has just computed - and their logits go to
+// the rows' sample arrays.
+//
+// tau_kernel (second launch, one CTA per query row) histograms the row's sample logits over their
+// own range, walks the histogram from the top and takes as threshold tau the logit below which all
+// but r sample keys lie, r = f n + margin * sqrt(f n) + 1 with f = K / N, and as its upper
+// companion tau_hi the logit that only f n - margin * sqrt(f n) - 1 sample keys exceed.  The scan
+// marks the keys with logit >= tau (about 1.7 K of them); the selection bins them between tau and
+// tau_hi, where the K-th largest lies.  Both are only filters: if fewer than K candidates turn up
+// (probability ~1e-9 at the default margin of 6 sigma) the selection falls back to all keys, and a
+// K-th largest outside [tau, tau_hi] only makes the boundary bin larger, so the result is exact
+// either way.
 #include "encode.cuh"
 
 namespace pqhsa {
 
-constexpr int kLutThreads = 512;
-constexpr int kListsPerCta = 176;  // 16 warps x 11 lists: 3 list CTAs + 1 encode CTA per stream, 128 CTAs for 32 streams - one wave
+constexpr int kLutThreads = 256;
+constexpr int kLutWarps = kLutThreads / 32;
+constexpr int kListsPerCta = 64;  // 8 warps x 8 lists: 8 list CTAs + 1 encode CTA per stream at 512 lists
+constexpr int kTauThreads = 256;
 
 struct LutArgs {
   const void* q;
+  const int32_t* io_map;  // [S] block of q a stream reads, or null: block s
   const void* codebooks;
   const void* coarse;
   int32_t* state;
@@ -51,21 +57,21 @@ struct LutArgs {
   float* lut;
   float* pair_tab;  // [S, G / GP, 4, 256, GP] byte-pair sums of the tables for the scan, GP = min(G, 4); or null
   float* list_scores;
-  int32_t* row_info;
   float* row_bin;
   float* row_tau;
   int32_t* ticket;
-  int num_lists, cap;
+  int num_lists, cap, G;
   float scale;
   double top_fraction;
   int topk_fixed;
-  float fixed_lo, fixed_inv_w, margin;
+  float margin;
   // fused append (all null / 0 when the kernel only builds tables)
   void* k_base;
   void* v_base;
   const void* new_k;
   const void* new_v;
   KvAddr kv;
+  int bump;       // 1: no row is written but the length of a live stream advances (the caller stored the row)
   int list_ctas;  // CTAs per stream with the list-score role
   int encode;     // 1: one more CTA per stream encodes enc.enc_count[s] / enc.uniform_count keys
   EncodeArgs enc;
@@ -88,13 +94,10 @@ __device__ __forceinline__ float warp_reduce_scatter32(float (&v)[32], int lane)
 }
 
 template <typename E, int G>
-__global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a) {
+__global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs a) {
   __shared__ float qs[G][kD];
   __shared__ float lut_s[G][kM * kC];
   __shared__ float lsc_s[G][kListsPerCta];
-  extern __shared__ uint32_t hist[];  // [min(G, 4)][kBins], used by the last CTA of a stream only
-  __shared__ uint32_t wsum[kLutThreads / 32], wmin[kLutThreads / 32], wmax[kLutThreads / 32];
-  __shared__ int is_last;
   const int s = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const E* q = static_cast<const E*>(a.q);
@@ -102,32 +105,54 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   int32_t* st = a.state + (size_t)s * kST;
   const int seq_old = st[PQHSA_ST_SEQ_LEN];
   const int n_sorted = st[PQHSA_ST_N_SORTED];
-  const int n_tail_old = st[PQHSA_ST_N_TAIL];
   const bool sampling = a.slog != nullptr && n_sorted > kSample;  // shorter streams: every key is a candidate
   const bool is_encode = (int)blockIdx.y >= a.list_ctas;
 
   if (is_encode) {
-    // encode role: the token just appended counts as part of the stream.  A larger norm is parked in
-    // norm_pend and folded into norm_max by the last CTA, like the counters.
+    // encode role.  Only tokens that were in the cache when the kernel started are encoded: the row
+    // another CTA of this launch is writing is not read.  A larger norm is parked in norm_pend and
+    // folded into norm_max by the last CTA, like the length.
     if (tid == 0) a.enc.norm_max[s] = a.norm_max[s];
     __syncthreads();
-    const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old + (append ? 1 : 0));
+    const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old);
     if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail;
   } else {
-    for (int i = tid; i < G * kD; i += kLutThreads) qs[i / kD][i % kD] = to_f(q[(size_t)s * G * kD + i]) * a.scale;
+    const int l0 = blockIdx.y * kListsPerCta;
+    // requested before anything else is looked at: this warp's centroid rows (a lane owns 4 dims) ...
+    const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
+    constexpr int kPerWarp = kListsPerCta / kLutWarps;
+    float c[kPerWarp][4];
+#pragma unroll
+    for (int i = 0; i < kPerWarp; ++i) {
+      const int l = l0 + warp * kPerWarp + i;
+#pragma unroll
+      for (int d = 0; d < 4; ++d) c[i][d] = 0.f;
+      if (l < a.num_lists) load4(coarse + (size_t)l * kD + lane * 4, c[i]);
+    }
+    // ... the thread's code word ...
+    float w[kSub];
+    if (tid < kM * kC) {
+      const E* cw = static_cast<const E*>(a.codebooks) + ((size_t)s * kM * kC + tid) * kSub;
+      float x[8], y[8];
+      load8(cw, x);
+      load8(cw + 8, y);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) { w[d] = x[d]; w[8 + d] = y[d]; }
+    }
+    // ... and this CTA's slice of the stream's sample records (sorted by list)
+    int i0 = 0, i1 = 0;
+    if (sampling && a.sample != nullptr) {
+      const int32_t* ss = a.sample_start + (size_t)s * (kLMax + 1);
+      i0 = ss[min(l0, a.num_lists)];
+      i1 = ss[min(l0 + kListsPerCta, a.num_lists)];
+    }
+    const int qb = a.io_map != nullptr ? a.io_map[s] : s;  // negative: the stream is idle this step
+    for (int i = tid; i < G * kD; i += kLutThreads)
+      qs[i / kD][i % kD] = qb >= 0 ? to_f(q[(size_t)qb * G * kD + i]) * a.scale : 0.f;
     __syncthreads();
-    // the tables (every table and list CTA: the list CTAs score their share of the sample with them)
+    // the tables (every list CTA: it scores its share of the sample with them)
     if (tid < kM * kC) {
       const int m = tid / kC;
-      const E* cw = static_cast<const E*>(a.codebooks) + ((size_t)s * kM * kC + tid) * kSub;
-      float w[kSub];
-      {
-        float x[8], y[8];
-        load8(cw, x);
-        load8(cw + 8, y);
-#pragma unroll
-        for (int d = 0; d < 8; ++d) { w[d] = x[d]; w[8 + d] = y[d]; }
-      }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float acc = 0.f;
@@ -137,15 +162,11 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         lut_s[g][tid] = acc;
       }
     }
-    __syncthreads();
-  }
-
-  if (blockIdx.y == 0) {
-    if (append && tid < 2 * kD / 8) {
+    if (blockIdx.y == 0 && append && tid >= kM * kC && tid < kM * kC + 2 * kD / 8) {
       // the step's K/V row, 16 bytes per thread (elements are 2 or 4 bytes: 8 or 4 per vector)
       constexpr int kVec = 16 / (int)sizeof(E);
       const long long off = a.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], seq_old);
-      for (int i = tid; i < 2 * kD / kVec; i += 2 * kD / 8) {
+      for (int i = tid - kM * kC; i < 2 * kD / kVec; i += 2 * kD / 8) {
         const bool isv = i >= kD / kVec;
         const int e = (isv ? i - kD / kVec : i) * kVec;
         const E* src = static_cast<const E*>(isv ? a.new_v : a.new_k) + (size_t)s * kD + e;
@@ -153,42 +174,14 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
       }
     }
-    if (a.pair_tab != nullptr) {
-      // the scan looks codes up a byte (two subspaces) at a time: entry (p, byte) = lut[2p][byte & 15] + lut[2p+1][byte >> 4]
-      constexpr int GP = G < 4 ? G : 4;
-      float* dst = a.pair_tab + (size_t)s * G * 1024;
-      for (int i = tid; i < G * 1024; i += kLutThreads) {
-        const int pass = i / (1024 * GP), rem = i % (1024 * GP);
-        const int e = rem / GP, g = rem % GP;
-        dst[i] = pair_entry(lut_s[pass * GP + g], e >> 8, (uint32_t)(e & 255));
-      }
-    }
-  }
-  if (!is_encode) {
-    // list scores: one warp per list, a lane owns 4 dims
-    const int l0 = blockIdx.y * kListsPerCta;
+    // list scores: one warp per list, kPerWarp x G partial dot products per lane; 32 of them at a time
+    // are summed across the warp with 31 shuffles (halving exchange: lane j ends up with the total of
+    // value j) instead of 5 per value
     float qr[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
       for (int d = 0; d < 4; ++d) qr[g][d] = qs[g][lane * 4 + d];
-    const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
-    constexpr int kPerWarp = kListsPerCta / (kLutThreads / 32);
-    float c[kPerWarp][4];
-#pragma unroll
-    for (int i = 0; i < kPerWarp; ++i) {
-      const int l = l0 + warp * kPerWarp + i;
-      if (l < a.num_lists) load4(coarse + (size_t)l * kD + lane * 4, c[i]);
-    }
-    // this CTA's slice of the stream's sample records (sorted by list), requested early
-    int i0 = 0, i1 = 0;
-    if (sampling && a.sample != nullptr) {
-      const int32_t* ss = a.sample_start + (size_t)s * (kLMax + 1);
-      i0 = ss[min(l0, a.num_lists)];
-      i1 = ss[min(l0 + kListsPerCta, a.num_lists)];
-    }
-    // kPerWarp x G partial dot products per lane; 32 of them at a time are summed across the warp with 31
-    // shuffles (halving exchange: lane j ends up with the total of value j) instead of 5 per value
     constexpr int kVals = kPerWarp * G;
 #pragma unroll
     for (int b0 = 0; b0 < kVals; b0 += 32) {
@@ -216,9 +209,21 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
         }
       }
     }
-    __syncthreads();
-    // Threshold estimate, first half: the sample keys of this CTA's lists are scored (same arithmetic
-    // as the scan); the logits go to the rows' sample arrays.
+    __syncthreads();  // tables and list scores of this CTA are in shared memory
+    if (a.pair_tab != nullptr) {
+      // the scan looks codes up a byte (two subspaces) at a time: entry (p, byte) = lut[2p][byte & 15] +
+      // lut[2p+1][byte >> 4]; the list CTAs of a stream write equal shares of the G x 1024 entries
+      constexpr int GP = G < 4 ? G : 4;
+      float* dst = a.pair_tab + (size_t)s * G * 1024;
+      const int per = (G * 1024 + a.list_ctas - 1) / a.list_ctas;
+      const int e1 = min(G * 1024, ((int)blockIdx.y + 1) * per);
+      for (int i = blockIdx.y * per + tid; i < e1; i += kLutThreads) {
+        const int pass = i / (1024 * GP), rem = i % (1024 * GP);
+        const int e = rem / GP, g = rem % GP;
+        dst[i] = pair_entry(lut_s[pass * GP + g], e >> 8, (uint32_t)(e & 255));
+      }
+    }
+    // the sample keys of this CTA's lists are scored (same arithmetic as the scan)
     for (int i = i0 + tid; i < i1; i += kLutThreads) {
       const int4 v = __ldg(a.sample + (size_t)s * kSample + i);
       const uint32_t code = (uint32_t)v.x;
@@ -230,150 +235,17 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
     }
   }
 
-  // ---- thresholds: the list CTA of the stream that arrives last among the list CTAs (arrival counter, no
-  // waiting; the barrier makes the CTA's stores visible to thread 0, whose fence then publishes them
-  // device-wide before the ticket; the last CTA reads the others' results through L2) ----
-  auto place_thresholds = [&]() {
-    // the encode role may still be running: its effect on the key count follows from the counters as they
-    // were when the kernel started (tau is only a filter: the selection kernel takes K from the final counters)
-    int added = 0;
-    if (a.encode) {
-      const int want = a.enc.enc_count ? a.enc.enc_count[s] : a.enc.uniform_count;
-      const int seq_new = seq_old + (append ? 1 : 0);
-      const int room_seq = seq_new - (min(a.enc.sink, seq_new) + n_sorted + n_tail_old);
-      added = max(0, min(min(want, room_seq), min(a.enc.cap - (n_sorted + n_tail_old), a.enc.tail_cap - n_tail_old)));
-    }
-    const int n = n_sorted + n_tail_old + added;
-  const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
-  const int ns = min(kSample, n_sorted);
-  const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
-  const float margin = a.margin != 0.f ? a.margin : 6.f;
-  const int r = (int)ceilf(expect + margin * sqrtf(expect) + 1.f);
-  const bool trivial = K == 0 || n_sorted <= kSample || r >= ns || r < 1;
-  if (!sampling) {
-    // nothing to select, or a context so short that every key is a candidate
-    if (tid < G) a.row_tau[(size_t)s * G + tid] = (K == 0) ? __builtin_huge_valf() : kNegInf;
-    return;
-  }
-  float* slog = a.slog + (size_t)s * G * kSample;
-  if (a.sample == nullptr) {
-    // no sample records: this CTA gathers and scores all sample slots itself (slow path)
-    const uint32_t* codes = a.codes + (size_t)s * a.cap;
-    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
-    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-    for (int i = tid; i < ns; i += kLutThreads) {
-      const int slot = (int)((long long)i * n_sorted / ns);
-      const uint32_t code = __ldg(codes + slot);
-      const float kn = to_f(norms[slot]);
-      const int l = lids[slot];
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-        slog[(size_t)g * kSample + i] =
-            finish_logit(pq_sum_row(lut_s[g], code), __ldcg(a.list_scores + ((size_t)s * G + g) * kLMax + l), kn);
-    }
-    __threadfence();
-    __syncthreads();
-  }
-  if (trivial) {
-    if (tid < G) a.row_tau[(size_t)s * G + tid] = (K == 0) ? __builtin_huge_valf() : kNegInf;
-    return;
-  }
-  // Second half, GP rows at a time, kTPR threads per row: the r-th largest of the row's 4096 sample
-  // logits, to the resolution of a 2048-bin histogram over the sample's own range; tau is the lower
-  // edge of the bin where the count from the top reaches r (so at least r sample keys pass).
-  constexpr int GP = G < 4 ? G : 4;
-  constexpr int kTPR = kLutThreads / GP;  // threads per row (a multiple of 32)
-  constexpr int kVPT = kSample / kTPR;    // sample logits per thread
-  constexpr int kBPT = kBins / kTPR;      // bins per thread
-  constexpr int kWPR = kTPR / 32;         // warps per row
-  const int gl = tid / kTPR, j = tid % kTPR;
-  for (int gb = 0; gb < G; gb += GP) {
-    const int g = gb + gl;
-    uint32_t key[kVPT];
-#pragma unroll
-    for (int i = 0; i < kVPT; ++i) key[i] = float_key(__ldcg(slog + (size_t)g * kSample + j + i * kTPR));
-    uint32_t mn = key[0], mx = key[0];
-#pragma unroll
-    for (int i = 1; i < kVPT; ++i) {
-      mn = min(mn, key[i]);
-      mx = max(mx, key[i]);
-    }
-    mn = __reduce_min_sync(0xffffffffu, mn);
-    mx = __reduce_max_sync(0xffffffffu, mx);
-    __syncthreads();  // the previous round is done with the shared arrays
-    if (lane == 0) {
-      wmin[warp] = mn;
-      wmax[warp] = mx;
-    }
-    for (int i = tid; i < GP * kBins; i += kLutThreads) hist[i] = 0u;
-    __syncthreads();
-#pragma unroll
-    for (int w = 0; w < kWPR; ++w) {
-      mn = min(mn, wmin[gl * kWPR + w]);
-      mx = max(mx, wmax[gl * kWPR + w]);
-    }
-    // linear bins over the row's own range [min, max]
-    const float lo = key_float(mn), hi = key_float(mx);
-    const float inv_w = hi > lo ? (float)kBins / (hi - lo) : 1.f;
-    uint32_t* h = hist + gl * kBins;
-#pragma unroll
-    for (int i = 0; i < kVPT; ++i) atomicAdd(&h[logit_bin(key_float(key[i]), lo, inv_w)], 1u);
-    __syncthreads();
-    const int top = kBins - kBPT * j;  // thread j owns the kBPT bins just below
-    uint32_t c[kBPT], sum = 0;
-#pragma unroll
-    for (int b = 0; b < kBPT; ++b) {
-      c[b] = h[top - 1 - b];
-      sum += c[b];
-    }
-    uint32_t incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    if (lane == 31) wsum[warp] = incl;
-    __syncthreads();
-    uint32_t before = 0;
-    for (int i = gl * kWPR; i < warp; ++i) before += wsum[i];
-    incl += before;
-    const uint32_t excl = incl - sum, need = (uint32_t)r;
-    if (excl < need && need <= incl) {
-      uint32_t cum = excl;
-#pragma unroll
-      for (int b = 0; b < kBPT; ++b) {
-        if (cum < need && need <= cum + c[b]) {
-          // one bin of slack for the rounding of the edge; bins 0 and 1 mean "everything"
-          const int bin = top - 1 - b;
-          a.row_tau[(size_t)s * G + g] = bin <= 1 ? kNegInf : lo + (float)(bin - 1) / inv_w;
-        }
-        cum += c[b];
-      }
-    }
-  }
-  };
-  if (!is_encode && a.slog != nullptr) {
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      const int t = atomicAdd(a.ticket + 2 * s, 1);
-      is_last = (t == a.list_ctas - 1);
-      if (is_last) a.ticket[2 * s] = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (is_last) place_thresholds();
-  }
-
   // ---- counters: the CTA of the stream that arrives last of all.  Every CTA of the stream is then done
-  // reading the counters: the token written above now counts, a larger norm becomes the stream's bound ----
-  if (!append && !a.encode) return;
+  // reading the length: the token written above now counts, a larger norm becomes the stream's bound ----
+  const bool bump = a.bump != 0 && seq_old > 0;
+  if (!append && !a.encode && !bump) return;
   __syncthreads();
   if (tid == 0) {
     __threadfence();
     const int t = atomicAdd(a.ticket + 2 * s + 1, 1);
     if (t == (int)gridDim.y - 1) {
       a.ticket[2 * s + 1] = 0;
-      if (append) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
+      if (append || bump) st[PQHSA_ST_SEQ_LEN] = seq_old + 1;
       if (a.encode) {
         const float pend = __ldcg(a.enc.norm_max + s);
         if (pend > a.norm_max[s]) a.norm_max_rw[s] = pend;
@@ -382,11 +254,137 @@ __global__ void __launch_bounds__(kLutThreads) lut_build_kernel(const LutArgs a)
   }
 }
 
-template <typename E, int G>
-static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st) {
+// One CTA per query row: the candidate threshold tau and the upper end tau_hi of the selection's bins from
+// the row's sample logits (see the file comment).  Runs after lut_build_kernel has ended, so the stream
+// counters are final.
+template <typename E>
+__global__ void __launch_bounds__(kTauThreads) tau_kernel(const LutArgs a) {
+  __shared__ uint32_t hist[kBins];
+  __shared__ uint32_t wsum[kTauThreads / 32], wmin[kTauThreads / 32], wmax[kTauThreads / 32];
+  __shared__ float lut_s[kM * kC];
+  __shared__ int bin_lo, bin_hi;
+  const int row = blockIdx.x, s = row / a.G;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t* st = a.state + (size_t)s * kST;
+  const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL];
+  const int n = n_sorted + n_tail;
+  const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
+  const int ns = min(kSample, n_sorted);
+  const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
+  const float margin = a.margin != 0.f ? a.margin : 6.f;
+  const int r = (int)ceilf(expect + margin * sqrtf(expect) + 1.f);
+  const int r_hi = (int)floorf(expect - fabsf(margin) * sqrtf(expect)) - 1;
+  const bool trivial = K == 0 || n_sorted <= kSample || r >= ns || r < 1;
+  if (trivial) {
+    // nothing to select, or so few keys (or so large a fraction) that every key is a candidate
+    if (tid == 0) {
+      a.row_tau[row] = (K == 0) ? __builtin_huge_valf() : kNegInf;
+      a.row_bin[2 * row] = 0.f;
+      a.row_bin[2 * row + 1] = 0.f;
+    }
+    return;
+  }
+  constexpr int kVPT = kSample / kTauThreads;  // sample logits per thread
+  constexpr int kBPT = kBins / kTauThreads;    // bins per thread
+  uint32_t key[kVPT];
+  if (a.sample != nullptr) {
+    const float* slog = a.slog + (size_t)row * kSample;
+#pragma unroll
+    for (int i = 0; i < kVPT; ++i) key[i] = float_key(__ldcg(slog + tid + i * kTauThreads));
+  } else {
+    // no sample records: the sample slots are gathered from the index and scored here
+    if (tid < kM * kC) lut_s[tid] = a.lut[(size_t)row * kM * kC + tid];
+    __syncthreads();
+    const uint32_t* codes = a.codes + (size_t)s * a.cap;
+    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+#pragma unroll
+    for (int i = 0; i < kVPT; ++i) {
+      const int slot = (int)((long long)(tid + i * kTauThreads) * n_sorted / ns);
+      key[i] = float_key(finish_logit(pq_sum_row(lut_s, __ldg(codes + slot)),
+                                      a.list_scores[(size_t)row * kLMax + lids[slot]], to_f(norms[slot])));
+    }
+  }
+  uint32_t mn = key[0], mx = key[0];
+#pragma unroll
+  for (int i = 1; i < kVPT; ++i) {
+    mn = min(mn, key[i]);
+    mx = max(mx, key[i]);
+  }
+  mn = __reduce_min_sync(0xffffffffu, mn);
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  if (lane == 0) {
+    wmin[warp] = mn;
+    wmax[warp] = mx;
+  }
+  for (int i = tid; i < kBins; i += kTauThreads) hist[i] = 0u;
+  if (tid == 0) {
+    bin_lo = -1;
+    bin_hi = -1;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kTauThreads / 32; ++w) {
+    mn = min(mn, wmin[w]);
+    mx = max(mx, wmax[w]);
+  }
+  // linear bins over the row's own range [min, max]
+  const float lo = key_float(mn), hi = key_float(mx);
+  const float inv_w = hi > lo ? (float)kBins / (hi - lo) : 1.f;
+#pragma unroll
+  for (int i = 0; i < kVPT; ++i) atomicAdd(&hist[logit_bin(key_float(key[i]), lo, inv_w)], 1u);
+  __syncthreads();
+  const int top = kBins - kBPT * tid;  // thread j owns the kBPT bins just below
+  uint32_t c[kBPT], sum = 0;
+#pragma unroll
+  for (int b = 0; b < kBPT; ++b) {
+    c[b] = hist[top - 1 - b];
+    sum += c[b];
+  }
+  uint32_t incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  uint32_t before = 0;
+  for (int i = 0; i < warp; ++i) before += wsum[i];
+  incl += before;
+  const uint32_t excl = incl - sum;
+  // the bin in which the count from the top reaches r (threshold) and r_hi (upper companion)
+  const uint32_t needs[2] = {(uint32_t)r, (uint32_t)max(r_hi, 0)};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const uint32_t need = needs[which];
+    if (need >= 1u && excl < need && need <= incl) {
+      uint32_t cum = excl;
+#pragma unroll
+      for (int b = 0; b < kBPT; ++b) {
+        if (cum < need && need <= cum + c[b]) {
+          if (which == 0) bin_lo = top - 1 - b; else bin_hi = top - 1 - b;
+        }
+        cum += c[b];
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    // one bin of slack for the rounding of the edges; bins 0 and 1 mean "everything"
+    const bool all = bin_lo <= 1;
+    const float tau = all ? kNegInf : lo + (float)(bin_lo - 1) / inv_w;
+    const float tau_hi = bin_hi < 0 ? hi : lo + (float)(bin_hi + 2) / inv_w;
+    a.row_tau[row] = tau;
+    a.row_bin[2 * row] = all ? 0.f : tau;
+    a.row_bin[2 * row + 1] = (!all && tau_hi > tau) ? (float)PQHSA_SELECT_BINS / (tau_hi - tau) : 0.f;
+  }
+}
+
+static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, LutArgs& a) {
   char* ws = static_cast<char*>(p.workspace);
-  LutArgs a;
   a.q = p.q;
+  a.io_map = p.io_map;
   a.codebooks = p.codebooks;
   a.coarse = p.coarse;
   a.state = static_cast<int32_t*>(p.state);
@@ -397,17 +395,15 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.lut = reinterpret_cast<float*>(ws + w.lut);
   a.pair_tab = w.pair_tab == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.pair_tab);
   a.list_scores = reinterpret_cast<float*>(ws + w.list_scores);
-  a.row_info = reinterpret_cast<int32_t*>(ws + w.row_info);
   a.row_bin = reinterpret_cast<float*>(ws + w.row_bin);
   a.row_tau = reinterpret_cast<float*>(ws + w.row_tau);
   a.ticket = reinterpret_cast<int32_t*>(ws + w.ticket);
   a.num_lists = p.num_lists;
   a.cap = p.slot_capacity;
+  a.G = p.group;
   a.scale = p.scale;
   a.top_fraction = p.top_fraction;
   a.topk_fixed = p.topk_fixed;
-  a.fixed_lo = p.hist_lo;
-  a.fixed_inv_w = p.hist_inv_width;
   a.margin = p.select_margin;
   a.sample = static_cast<const int4*>(p.sample);
   a.sample_start = static_cast<const int32_t*>(p.sample_start);
@@ -419,18 +415,26 @@ static int launch_lut_build_t(const pqhsa_params& p, const pqhsa_ws_layout& w, c
   a.kv = make_kvaddr(p);
   a.new_k = ap ? ap->new_k : nullptr;
   a.new_v = ap ? ap->new_v : nullptr;
+  a.bump = (ap && ap->new_k == nullptr && p.external_append != 0) ? 1 : 0;
   a.encode = (ap && (ap->enc_count != nullptr || ap->uniform_count > 0)) ? 1 : 0;
   a.enc = make_encode_args(p, ap ? ap->enc_count : nullptr, ap ? ap->uniform_count : 0);
-  a.enc.norm_max = reinterpret_cast<float*>(ws + w.norm_pend);  // folded into norm_max once all CTAs are done
-  const size_t smem = (size_t)(G < 4 ? G : 4) * kBins * sizeof(uint32_t);
-  auto kern = lut_build_kernel<E, G>;
+  a.enc.norm_max = w.norm_pend == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.norm_pend);
+}
+
+template <typename E, int G>
+static int launch_lut_build_t(const pqhsa_params& p, const LutArgs& a, cudaStream_t st) {
   const dim3 grid(p.num_streams, a.list_ctas + a.encode);
-  kern<<<grid, kLutThreads, smem, st>>>(a);
-  return check_launch("lut_build");
+  lut_build_kernel<E, G><<<grid, kLutThreads, 0, st>>>(a);
+  if (int rc = check_launch("lut_build")) return rc;
+  if (a.slog == nullptr) return PQHSA_OK;  // tables only: no threshold wanted
+  tau_kernel<E><<<p.num_streams * p.group, kTauThreads, 0, st>>>(a);
+  return check_launch("tau");
 }
 
 int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st) {
-  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_lut_build_t<E, G>(p, w, ap, st))));
+  LutArgs a;
+  fill_lut_args(p, w, ap, a);
+  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_lut_build_t<E, G>(p, a, st))));
   return PQHSA_OK;
 }
 

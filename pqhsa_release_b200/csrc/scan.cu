@@ -29,16 +29,15 @@
 //   * the rows of a pass are carried as packed f32x2 values (add / mul / fma on
 //     two rows per instruction, same IEEE rounding as the scalar form);
 //   * the unit maximum is one redux.sync.max.f32 per row;
-//   * a row looks for candidates (logit >= the row's threshold) only in units whose
-//     maximum reaches the threshold; a candidate goes to a lane-private shared-memory
-//     buffer and the warp flushes the buffers together, one global atomic per row
-//     and flush.
+//   * candidates (logit >= the row's threshold) are marked in a bit map: one vote per
+//     row and 32 slots, taken only in units whose maximum reaches the threshold (the
+//     others store zero words); the 4 words of a (row, unit) are one 16-byte store.
 //
 // Outputs per query row: per-unit (max, sum exp) - a unit's logits stay in
 // registers and the sum is taken against the unit's final maximum, so every key
 // contributes exactly unit_term(logit, reference) and the selection kernel can
 // remove a selected key again without cancellation error - the tail logits, and
-// the candidates.  The logits themselves are never written; the separate dump
+// the hit bits.  The logits themselves are never written; the separate dump
 // kernel writes all of them for tests and the stand-alone scoring entry point.
 #include "common.cuh"
 
@@ -260,6 +259,8 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
         // with many candidates would otherwise all fall to the one CTA that owns their range.
         int stride = 127;
         if (u_tot % stride == 0) stride = 131;
+        if (u_tot % stride == 0) stride = 137;
+        if (u_tot % stride == 0) stride = 139;  // 127 x 131 x 137 exceeds any unit count, so one of the four fits
 
 #pragma unroll 1
         for (int pass = 0; pass < PS::NP; ++pass) {
@@ -365,13 +366,18 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
                   for (int it = 1; it < kIter; ++it) mx = fmaxf(mx, xs[it][g]);
                   mg[g] = redux_max(mx);
                 }
-                // candidates: one vote per row and 32 slots; the 4 words of a row and unit are one 16-byte store
+                // candidates: one vote per row and 32 slots, only where the unit maximum reaches the threshold
+                // (padding lanes are excluded by index: the threshold may be -inf); the 4 words of a row and unit are one 16-byte store
 #pragma unroll
                 for (int g = 0; g < GP; ++g) {
                   unsigned m[kIter];
 #pragma unroll
-                  for (int it = 0; it < kIter; ++it)
-                    m[it] = __ballot_sync(0xffffffffu, it * 32 + lane < n && xs[it][g] >= tau[g]);
+                  for (int it = 0; it < kIter; ++it) m[it] = 0u;
+                  if (mg[g] >= tau[g]) {  // warp-uniform
+#pragma unroll
+                    for (int it = 0; it < kIter; ++it)
+                      m[it] = __ballot_sync(0xffffffffu, it * 32 + lane < n && xs[it][g] >= tau[g]);
+                  }
                   if (lane == 0)
                     *reinterpret_cast<uint4*>(a.hitmap + ((size_t)(row0 + g) * a.ucap + u) * kIter) =
                         make_uint4(m[0], m[1], m[2], m[3]);

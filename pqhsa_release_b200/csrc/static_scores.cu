@@ -26,7 +26,7 @@ constexpr size_t kOffListScores = kOffLut + align256((size_t)kStaticMaxRows * kM
 constexpr size_t kOffRowBin = kOffListScores + align256((size_t)kStaticMaxRows * kLMax * sizeof(float));
 constexpr size_t kOffRowTau = kOffRowBin + align256((size_t)kStaticMaxRows * 2 * sizeof(float));
 constexpr size_t kOffTicket = kOffRowTau + align256((size_t)kStaticMaxRows * sizeof(float));
-constexpr size_t kOffRowInfo = kOffTicket + align256((size_t)kStaticMaxRows * sizeof(int32_t));
+constexpr size_t kOffRowInfo = kOffTicket + align256((size_t)2 * kStaticMaxRows * sizeof(int32_t));  // int32 [S, 2], S <= rows
 constexpr size_t kStaticBytes = kOffRowInfo + align256((size_t)kStaticMaxRows * kRI * sizeof(int32_t));
 
 // The scratch itself.  In host code this name is only a handle for the runtime, not a device
@@ -69,8 +69,10 @@ extern "C" int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, vo
   void* base = nullptr;
   if (int rc = static_scratch(&base)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  // the arrival counters must start from zero whatever an earlier (possibly failed) call left behind
-  if (cudaMemsetAsync(static_cast<char*>(base) + kOffTicket, 0, (size_t)p->num_streams * sizeof(int32_t), st) !=
+  // The table kernel keeps two arrival counters per stream, int32 [S, 2], that it expects at zero.  This
+  // entry point appends and encodes nothing, so today's kernels never count on them; they are cleared
+  // all the same, so that the call does not depend on what an earlier one left in the shared array.
+  if (cudaMemsetAsync(static_cast<char*>(base) + kOffTicket, 0, (size_t)2 * p->num_streams * sizeof(int32_t), st) !=
       cudaSuccess)
     return check_launch("static scratch: clearing the arrival counters");
   pqhsa_params q = *p;
@@ -82,6 +84,7 @@ extern "C" int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, vo
   w.lut = kOffLut;
   w.pair_tab = (size_t)-1;  // only the full scan reads pair tables
   w.slog = (size_t)-1;      // ... and thresholds
+  w.norm_pend = (size_t)-1;
   w.list_scores = kOffListScores;
   w.row_bin = kOffRowBin;
   w.row_tau = kOffRowTau;

@@ -57,7 +57,7 @@ def words_to_codes(words: torch.Tensor) -> torch.Tensor:
 
 def list_sorted_layout(list_ids: torch.Tensor, num_lists: int):
     """Stable sort by list (the CSR order of pq_hsa/index/ivfpq.py:864-882) and
-    the scan units: ranges of at most 256 slots inside one list.
+    the scan units: ranges of at most 128 slots inside one list.
     Returns (perm, unit_off [U+1], unit_list [U])."""
     ids = list_ids.to(torch.int64)
     n = ids.numel()
@@ -372,6 +372,13 @@ class DeviceIndexPool:
         if encode:
             if int((self.h_tail + encode).max()) > self.tail_capacity:
                 raise RuntimeError("tail capacity exhausted: compact() the pool first")
+            # the fused call encodes tokens that were in the cache before it (all of them with local_window == 0,
+            # where the library appends first): the host mirror must not run ahead of the device
+            room = self.h_seq - (np.minimum(self.sink, self.h_seq) + self.h_sorted + self.h_tail)
+            if new_k is not None and self.local == 0:
+                room = room + 1
+            if int((room - encode).min()) < 0:
+                raise ValueError("decode_step_append asked to index tokens that are not in the cache yet")
             self.h_tail += encode
         if new_k is not None:
             self.h_seq += 1

@@ -94,3 +94,42 @@ class PeerExchange:
 
     def timed_out(self) -> bool:
         return bool(int(self.seq[1].item()) != 0)
+
+
+class LocalPeerGroup:
+    """The same exchange between several pools that live in ONE process on ONE GPU (shards of a
+    layer stepped one after the other on the same stream): every pool plays a rank, the gather
+    buffers and flag arrays are ordinary device tensors.  Used to exercise the exchange protocol
+    without a second GPU; the kernels are the ones the multi-GPU path runs."""
+
+    def __init__(self, pools, wait_polls: int = 0):
+        from . import _lib
+
+        self._lib, self.pools = _lib, list(pools)
+        self.world = len(self.pools)
+        p0 = self.pools[0]
+        R = p0.S * p0.G
+        if any(p.S * p.G != R or p.dtype != p0.dtype or p.device != p0.device for p in self.pools):
+            raise ValueError("all pools of a local peer group need the same row count, dtype and device")
+        dev = p0.device
+        self.bufs = [torch.zeros(2, self.world, R, _lib.HEAD_DIM, dtype=p0.dtype, device=dev) for _ in self.pools]
+        self.flags = [torch.zeros(max(self.world, 8), dtype=torch.int32, device=dev) for _ in self.pools]
+        self.seqs = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in self.pools]
+        self.ptr_out = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=dev)
+        self.ptr_flags = torch.tensor([f.data_ptr() for f in self.flags], dtype=torch.int64, device=dev)
+        for r, pool in enumerate(self.pools):
+            p = pool.p
+            p.peer_out, p.peer_flags, p.peer_seq = self.ptr_out.data_ptr(), self.ptr_flags.data_ptr(), self.seqs[r].data_ptr()
+            p.peer_world, p.peer_rank, p.peer_wait_polls = self.world, r, int(wait_polls)
+
+    def wait(self, rank: int) -> None:
+        import ctypes as C
+
+        pool = self.pools[rank]
+        self._lib.call("pqhsa_wait_peers", C.byref(pool.p), pool._stream())
+
+    def result(self, rank: int, steps_done: int) -> torch.Tensor:
+        return self.bufs[rank][(steps_done - 1) & 1]
+
+    def timed_out(self, rank: int) -> bool:
+        return bool(int(self.seqs[rank][1].item()) != 0)

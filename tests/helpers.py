@@ -44,7 +44,7 @@ class Case:
 
 
 def make_case(B=1, Hkv=2, G=4, S=1500, L=64, dtype=torch.bfloat16, frac=0.02, sink=4, local=128, seed=0,
-              interval=256, strategy="deferred", contexts=None, kind="mixture") -> Case:
+              interval=256, strategy="deferred", contexts=None, kind="mixture", components=16) -> Case:
     """Build inputs + one oracle stream per (request, KV head).  The oracle's index
     float tensors are rounded to ``dtype`` after the build: both sides then see the
     identical stored index."""
@@ -54,7 +54,7 @@ def make_case(B=1, Hkv=2, G=4, S=1500, L=64, dtype=torch.bfloat16, frac=0.02, si
     queries = torch.empty(B, Hkv * G, D, dtype=dtype)
     for b in range(B):
         if kind == "mixture":
-            k, v = workloads.mixture_kv(seed * 1000 + b, Hkv, S, dtype=dtype, components=16)
+            k, v = workloads.mixture_kv(seed * 1000 + b, Hkv, S, dtype=dtype, components=components)
             q = workloads.planted_queries(seed * 1000 + 500 + b, k, G)
         else:
             ks, vs, qs = [], [], []

@@ -171,3 +171,63 @@ def test_gqa_sidecar_reads_vllm_pages_in_place(layout):
         flat.append(nk.cuda(), nv.cuda())
     with pytest.raises(ValueError):
         paged.forward(torch.zeros(2, Hkv * G, 128, dtype=dtype, device="cuda"))
+
+
+def test_deferred_fixture_of_the_reference_through_the_engine():
+    """The reference's own run with deferred index updates (tests/golden/golden_mix_deferred.npz: 20 appends,
+    the pending update applied after the 11th) replayed on the GPU: the engine starts from the index tensors
+    the reference built, appends the same rows, applies the update at the same step (EMA of centroids and code
+    words, every key re-encoded: pq_hsa/index/ivfpq.py:647-707) and must give the reference's outputs at every
+    step, and the reference's codes, list ids and codebooks at the end."""
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    here = Path(__file__).resolve().parent
+    sys.path.insert(0, str(here / "golden"))
+    from make_golden import CASES, case_inputs
+
+    from pqhsa_release_b200.device_index import StreamIndexTensors
+    from pqhsa_release_b200.engine import PoolAttention
+
+    name = "mix_deferred"
+    kind, seed, ctx, lists, group, dtype, strategy, interval, appends = CASES[name]
+    g = np.load(here / "golden" / f"golden_{name}.npz")
+    k, v, q, nk, nv = case_inputs(name)
+    eng = PoolAttention(paper_index_config(num_lists=lists),
+                        paper_attention_config(retrieval_top_fraction=0.02, index_update_interval=interval,
+                                               index_update_strategy=strategy), group=group)
+    idx = StreamIndexTensors(torch.from_numpy(g["packed_codes"]), torch.from_numpy(g["list_ids"]).long(),
+                             torch.from_numpy(g["key_norms"]), torch.from_numpy(g["coarse"]),
+                             torch.from_numpy(g["codebooks"]), torch.from_numpy(g["value_means"]))
+    eng.restore({"keys": k.cuda()[None, None], "values": v.cuda()[None, None], "indexed_length": ctx, "pending": 0,
+                 "deferred_pending": False, "streams": (idx,)})
+    out0 = eng.forward(q.cuda()[None]).cpu()[0]
+    for r in range(group):
+        assert_output_close(out0[r], torch.from_numpy(g["output0"][r]), torch.float32, f"row {r} before any append")
+    flushed = False
+    for i in range(appends):
+        eng.append(nk[i].cuda()[None, None], nv[i].cuda()[None, None])
+        if i == appends // 2:
+            assert eng.apply_pending_index_update()
+            flushed = True
+        out = eng.forward((q + 0.01 * i).cuda()[None]).cpu()[0]
+        want = torch.from_numpy(g["outputs_after_appends"][i])
+        for r in range(group):
+            if not flushed:
+                assert_output_close(out[r], want[r], torch.float32, f"append {i} row {r}")
+            else:
+                # after the update a handful of keys may sit in another list or carry another code than in the
+                # reference's CPU run (ties of the re-encode): the bar is the 2e-3 of the output tolerance
+                err = float((out[r] - want[r]).norm() / want[r].norm())
+                assert err <= 2e-3, f"append {i} row {r}: {err:.2e}"
+    e = eng.pool.export_stream_state(0)
+    n = g["list_ids_end"].shape[0]
+    assert e.list_ids.numel() == n
+    lid_same = (e.list_ids.cpu().numpy() == g["list_ids_end"].astype(np.int64))
+    code_same = (e.packed_codes.cpu().numpy() == g["packed_codes_end"]).all(axis=1)
+    assert lid_same.mean() >= 0.99 and (code_same | ~lid_same).mean() >= 0.95, (lid_same.mean(), code_same.mean())
+    np.testing.assert_allclose(e.coarse_centroids.float().cpu().numpy(), g["coarse_end"], rtol=0, atol=2e-6)
+    np.testing.assert_allclose(e.codebooks.float().cpu().numpy(), g["codebooks_end"], rtol=0, atol=2e-6)
+    np.testing.assert_allclose(e.key_norms.float().cpu().numpy(), g["key_norms_end"], rtol=1e-6)

@@ -102,11 +102,31 @@ def test_forced_fallback_is_still_exact():
     assert int(info[:, 4].sum()) >= 1, "expected at least one row to take the fallback"
 
 
+@pytest.mark.parametrize("name, kw", [
+    # the benchmark configurations at their stated sizes, a slice of streams each (streams are independent)
+    ("c0", dict(B=1, Hkv=1, G=1, S=8192, L=512, dtype=torch.float32, seed=0, kind="config0")),
+    ("c1", dict(B=1, Hkv=2, G=4, S=32768, L=512, dtype=torch.bfloat16, seed=31, components=64)),
+    ("c2", dict(B=1, Hkv=2, G=4, S=131072, L=512, dtype=torch.bfloat16, seed=32, components=64)),
+    ("c4", dict(B=1, Hkv=1, G=8, S=262144, L=512, dtype=torch.bfloat16, seed=34, components=64)),
+])
+def test_baseline_config_sizes_match_the_oracle(name, kw):
+    """Oracle parity at the context length, list count, group size and dtype each benchmark configuration
+    states (8192 keys x 512 lists fp32; 32768, 131072 and 262144 keys bf16): approximate logits within 1e-3,
+    K exact, top-K sets equal up to boundary ties, output within 2e-3 - the bars of every other case."""
+    case = make_case(**kw)
+    pool, _, _ = pool_from_case(case, extra_slots=64, tail_capacity=64)
+    info = _check_case(case, pool)
+    assert int(info[:, 4].sum()) == 0, "the exact fallback should not be needed at the default margin"
+    k = int(info[0, 0])
+    assert k == {"c0": 162, "c1": 653, "c2": 2619, "c4": 5241}[name]
+    assert (info[:, 2] >= k).all() and (info[:, 2] <= 3 * k + 64).all(), "candidate count out of the expected range"
+
+
 @pytest.mark.parametrize("name, H", [("c2", 2), ("c4", 1)])
 def test_full_context_properties_against_the_dumped_scores(name, H):
-    """The full contexts of the benchmark configurations (c2: 131072 keys, G = 4; c4: 262144 keys, G = 8, where a row has
-    more candidates than the selection kernel keeps in registers; 512 lists, bf16), too large for
-    the CPU oracle: size-independent properties instead.  The selected set must be exactly the K
+    """The full contexts of the benchmark configurations (c2: 131072 keys, G = 4; c4: 262144 keys, G = 8; 512 lists,
+    bf16) with the index built on the GPU (the oracle comparison at these sizes is the test above):
+    size-independent properties.  The selected set must be exactly the K
     largest of the logits the library itself dumps (same floats, ties to the lower slot), every
     row's candidate count must lie between K and a small multiple of it without the fallback, and
     the output must equal a plain fp32 softmax over [exact sink/local/selected rows, per-list
