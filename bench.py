@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--workload", default="c2", choices=sorted(workloads.WORKLOADS))
     ap.add_argument("--context", type=int, default=None, help="override the context length (debugging)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (debugging)")
+    ap.add_argument("--layers", type=int, default=None, help="layers of workload c4 (default 80)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--flush", default="write+read", choices=["write+read", "write", "read", "none"],
@@ -466,6 +467,238 @@ def run_b200(args):
 
 
 # --------------------------------------------------------------------------
+# c3: the paged plugin path (vLLM page layout, ragged batch, one key appended and encoded per step)
+# --------------------------------------------------------------------------
+def run_paged_plugin(args):
+    """Workloads c3 and c4 through the plugin's own entry, ``pq_or_dense_forward``.
+
+    c3: 16 requests with contexts drawn uniformly from [8192, 65536], 16-token pages in vLLM's
+    [blocks, Hkv, block_size, 2D] layout behind a randomly permuted block table; every decode step stores one
+    K/V row per head in the pages (vLLM's own cache write, outside the timed region as in the reference's
+    attention segment) and the hook appends it, encodes the key that leaves the local window and attends -
+    one fused library call per layer-step.  One layer, one GPU.
+
+    c4: Llama-3-70B attention shape (8 KV heads, GQA 8), 80 layers with independent synthetic KV, context
+    262144, batch 8, the KV heads sharded over the ranks as vLLM's tensor parallelism does (one head per GPU on
+    8 GPUs; every rank holds its heads' pages and index and runs this same path - the attention outputs stay
+    sharded, as in vLLM, where the row-parallel output projection follows).  A step = all 80 layers; the
+    production index policy (deferred, flush every 256 tokens).  ``value`` counts the keys of all layers and ranks."""
+    from types import SimpleNamespace as NS
+
+    from pqhsa_release_b200.pq_hsa_vllm import runtime
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    wl = workloads.WORKLOADS[args.workload]
+    is_c4 = args.workload == "c4"
+    if not is_c4 and world > 1:
+        raise SystemExit("workload c3 is measured on one GPU")
+    if wl.kv_heads % world:
+        raise SystemExit(f"{wl.kv_heads} KV heads do not shard over {world} ranks")
+    B = args.batch or wl.batch
+    layers = (args.layers or 80) if is_c4 else 1
+    K, W = args.steps, max(args.warmup, 3)
+    Hkv, G, D, bs = wl.kv_heads // world, wl.group, wl.head_dim, wl.block_size
+    Hq = Hkv * G
+    g = torch.Generator().manual_seed(33)
+    if is_c4:
+        ctxs = [args.context or wl.context] * B
+    else:
+        ctxs = [int(x) for x in torch.randint(8192, (args.context or wl.context) + 1, (B,), generator=g)]
+    need_gb = layers * sum(ctxs) * Hkv * 2 * D * 2 / 2 ** 30
+    if need_gb > 150:
+        raise SystemExit(f"{need_gb:.0f} GiB of KV pages per GPU do not fit: use more ranks (--gpus) or fewer --layers")
+    grow = W + 2 * K + 32   # tokens a request gains over the whole run: warm-up, the timed steps, the end-to-end steps
+    blocks_of = [(c + grow + bs - 1) // bs for c in ctxs]
+    max_blocks = max(blocks_of)
+    nblk = sum(blocks_of) + 16
+    perm = torch.randperm(nblk, generator=g)
+    table = torch.zeros(B, max_blocks, dtype=torch.int32)
+    at = 0
+    for b, nb in enumerate(blocks_of):
+        table[b, :nb] = perm[at : at + nb].to(torch.int32)
+        at += nb
+    table = table.to(device)
+    t0 = time.time()
+    caches, q_layers = [], []
+    for layer_i in range(layers):
+        kv_cache = torch.zeros(nblk, Hkv, bs, 2 * D, dtype=wl.dtype, device=device)
+        qs = []
+        for b, c in enumerate(ctxs):
+            k, v = workloads.mixture_kv(300_000 + 1000 * layer_i + 10 * b + rank, Hkv, c, dtype=wl.dtype, device=device)
+            t = torch.arange(c, device=device)
+            blk, off = table[b, t // bs].long(), t % bs
+            kv_cache[blk, :, off, :D] = k.permute(1, 0, 2)
+            kv_cache[blk, :, off, D:] = v.permute(1, 0, 2)
+            qs.append(workloads.planted_queries(7_000 + b + 31 * layer_i, k, G))
+            del k, v
+        caches.append(kv_cache)
+        q_layers.append(torch.stack(qs).contiguous())  # [B, Hq, D]
+    env = {"PQ_HSA_BATCH": "1", "PQ_HSA_TOP_FRAC": str(wl.top_fraction), "PQ_HSA_NUM_LISTS": str(wl.num_lists),
+           "PQ_HSA_MAX_REQUESTS": str(B), "PQ_HSA_MAX_CONTEXT": str(max_blocks * bs), "PQ_HSA_ENABLE": "1",
+           "PQ_HSA_SINK": str(wl.sink_tokens), "PQ_HSA_LOCAL": str(wl.local_window), "PQ_HSA_PREFIX_CACHE": "0"}
+    env.update({"PQ_HSA_UPD_STRATEGY": "deferred", "PQ_HSA_UPD_INTERVAL": "256", "PQ_HSA_FLUSH_INTERVAL": "256"} if is_c4 else
+               {"PQ_HSA_UPD_STRATEGY": "incremental", "PQ_HSA_UPD_INTERVAL": "1"})
+    os.environ.update(env)
+    runtime.reset()
+    runner = NS(input_batch=NS(req_ids=[f"req{b}" for b in range(B)]), requests={})
+    impl = NS(scale=1.0 / math.sqrt(D), num_heads=Hq, num_kv_heads=Hkv, kv_cache_dtype="auto")
+    layer_objs = [object() for _ in range(layers)]
+    lens = list(ctxs)
+
+    def dense(*a, **k):
+        raise SystemExit("the step fell through to the dense path: " + str(runtime.rejects()))
+
+    nq = 4
+    gd = torch.Generator(device=device).manual_seed(5 + rank)
+    rows = [(torch.randn(B, Hkv, D, generator=gd, device=device).to(wl.dtype), torch.randn(B, Hkv, D, generator=gd, device=device).to(wl.dtype))
+            for _ in range(nq)]
+    out = torch.zeros(layers, B, Hq * D, dtype=wl.dtype, device=device)
+    hq = torch.stack(q_layers).cpu().pin_memory()            # [layers, B, Hq, D]: the step's queries on the host
+    q_dev = torch.zeros(layers, B, Hq, D, dtype=wl.dtype, device=device)
+    hout = torch.empty(layers, B, Hq * D, dtype=wl.dtype).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    flush_rd = torch.zeros(64 << 20, dtype=torch.int32, device=device)
+    bidx = torch.arange(B, device=device)
+
+    def vllm_cache_write(i):
+        """What vLLM does before the attention forwards: the step's K/V rows go into every layer's pages."""
+        nk, nv = rows[i % nq]
+        pos = torch.tensor(lens, device=device)
+        blk, off = table[bidx, pos // bs].long(), pos % bs
+        for kv_cache in caches:
+            kv_cache[blk, :, off, :D] = nk
+            kv_cache[blk, :, off, D:] = nv
+        for b in range(B):
+            lens[b] += 1
+        return nk, nv
+
+    def metadata():
+        t = torch.tensor(lens, dtype=torch.int32)
+        return NS(use_cascade=False, max_query_len=1, num_actual_tokens=B, seq_lens=t, seq_lens_cpu=t, max_seq_len=max(lens),
+                  block_table=table, slot_mapping=None, _pq_runner=runner)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def step(i, e2e=False, ev=None):
+        nk, nv = vllm_cache_write(i)
+        md = metadata()
+        flush.zero_(); flush_rd.sum()
+        if ev is not None:
+            ev[0].record()
+        if e2e:
+            q_dev.copy_(hq, non_blocking=True)
+        for li in range(layers):
+            q = q_dev[li] if e2e else q_layers[li]
+            runtime.pq_or_dense_forward(dense, impl, layer_objs[li], q, nk, nv, caches[li], md, output=out[li])
+        if e2e:
+            hout.copy_(out, non_blocking=True)
+        if ev is not None:
+            ev[1].record()
+
+    step(0)                     # builds every layer's and request's index
+    barrier()
+    setup_s = time.time() - t0
+    for i in range(1, W):
+        step(i)
+    barrier()
+    engines = [runtime._LAYERS[id(l)] for l in layer_objs]
+    n_keys = sum(int((e.pool.h_sorted + e.pool.h_tail)[: B * Hkv].sum()) for e in engines)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    sampler.start()
+    for i in range(K):
+        step(W + i, ev=ev[i])
+    barrier()
+    clocks = sampler.stop()
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for i in range(K):
+        step(W + K + i, e2e=True, ev=ev2[i])
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in ev2)
+    if not bool(torch.isfinite(hout.float()).all()):
+        raise SystemExit("end-to-end check failed: the host buffer holds non-finite values")
+    assert runtime.STATS["builds"] == B * layers and runtime.STATS["dense_steps"] == 0, runtime.STATS
+    # per-kernel durations of one layer-step, launched stage by stage behind the flush (first layer)
+    import ctypes as C
+
+    from pqhsa_release_b200 import _lib
+
+    stage_names = ["lut_build", "scan", "select", "attend", "merge"]
+    stage_ms = [0.0] * 5
+    reps = min(10, K)
+    pool = engines[0].pool
+    for r in range(reps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        flush.zero_(); flush_rd.sum()
+        evs[0].record()
+        for sidx in range(5):
+            pool.p.q, pool.p.out = q_layers[0].data_ptr(), out[0].data_ptr()
+            _lib.call("pqhsa_run_stage", C.byref(pool.p), sidx, torch.cuda.current_stream().cuda_stream)
+            evs[sidx + 1].record()
+        torch.cuda.synchronize()
+        for sidx in range(5):
+            stage_ms[sidx] += evs[sidx].elapsed_time(evs[sidx + 1]) / reps
+    t = torch.tensor([total_ms, e2e_ms, float(n_keys)], dtype=torch.float64, device=device)
+    if world > 1:
+        tm = t.clone()
+        torch.distributed.all_reduce(tm, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.SUM)
+        total_ms, e2e_ms, n_keys = float(tm[0]), float(tm[1]), int(t[2])
+    peak, peak_kind = measured_peaks()
+    mid = [c + W + K // 2 for c in ctxs]
+    step_bytes = layers * (wl.algorithmic_bytes(contexts=mid) + (B * wl.kv_heads * (2 * D * 2 + 8) if not is_c4 else 0))
+    e = 2
+    attend_bytes = sum(Hq * wl.topk(c) * 2 * D * e + Hkv * (c - wl.retrieval_len(c)) * 2 * D * e + Hkv * wl.num_lists * D * e
+                       for c in ctxs)
+    achieved = attend_bytes / (stage_ms[3] / 1e3) / 1e9
+    per_layer_us = 1e3 * total_ms / K / layers
+    line = {
+        "metric": METRIC, "value": n_keys * K / (total_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": total_ms / K, "us_per_layer_step": per_layer_us, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl.name, "batch": B, "kv_heads": wl.kv_heads, "group": G, "layers": layers,
+                   "contexts": ctxs if not is_c4 else ctxs[0], "indexed_keys_all_layers_and_ranks": n_keys, "lists": wl.num_lists,
+                   "kv_layout": "paged: vLLM [blocks, Hkv, 16, 2D] pages, permuted block table",
+                   "index_update": "deferred, flush every 256 tokens" if is_c4 else "incremental, 1 key per request-head and step",
+                   "entry": "pq_hsa_vllm runtime.pq_or_dense_forward (eager, 7 launches per layer-step)",
+                   "parallelism": f"kv-head shard x{world}, attention outputs stay sharded (vLLM tensor parallelism)",
+                   "l2": "flushed between timed steps (write+read of 256 MiB)", "cuda_graph": False},
+        "step_roofline": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / world / (total_ms / K / 1e3) / 1e9,
+                          "peak_gbs": peak, "frac": step_bytes / world / (total_ms / K / 1e3) / 1e9 / peak, "of": peak_kind},
+        "roofline": {"kernel": "attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "of": peak_kind, "algorithmic_bytes_per_launch": attend_bytes},
+        "stages_us": {n: round(1e3 * m, 2) for n, m in zip(stage_names, stage_ms)},
+        "e2e": {"value": n_keys * K / (e2e_ms / 1e3), "unit": UNIT, "us_per_layer_step": 1e3 * e2e_ms / K / layers,
+                "h2d_bytes_per_step": hq.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
+        "gpu_launches": 7 * K * layers, "clocks": clocks, "setup_s": setup_s, "runtime_stats": dict(runtime.STATS),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from dataclasses import replace
+
+        line["cpu_baseline"] = cpu_reference(replace(wl, batch=B, context=int(sum(ctxs) / B)), budget_s=20.0, steps=3, warmup=1)["cpu_baseline"]
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        os._exit(0)
+
+
+# --------------------------------------------------------------------------
 # reference arm: the CPU port of the reference's torch path (oracle/)
 # --------------------------------------------------------------------------
 def cpu_reference(wl, budget_s, steps, warmup):
@@ -547,5 +780,7 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload in ("c3", "c4"):
+        run_paged_plugin(a)
     else:
         run_b200(a)

@@ -177,16 +177,16 @@ typedef struct pqhsa_ws_layout {
   size_t ticket;       /* int32  [S, 2]   arrival counters of the table kernel's CTAs (0 between launches) */
   size_t slog;         /* float  [R, PQHSA_SAMPLE_KEYS]  approximate logits of the sample keys           */
   size_t norm_pend;    /* float  [S]      norm of a key encoded in the current launch                    */
+  size_t enc_best;     /* float  [S, 16, 2]  nearest list of the key being encoded, per list CTA of the table kernel */
   size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit                   */
   size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max), selected keys removed */
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */
   size_t row_info;     /* int32  [R, 8]   see enum pqhsa_row_info_slot                     */
   size_t hitmap;       /* uint32 [R, unit_capacity, 4]  bit b of word (u, i): slot first(u) + 32 i + b reached the threshold */
   size_t cand_key;     /* uint32 [R, parts, seg]  candidates of a row, listed by `parts` CTAs: order-preserving key of the logit */
-  size_t cand_slot;    /* int32  [R, parts, seg]  ... their slot                                      */
-  size_t cand_pos;     /* int32  [R, parts, seg]  ... token position                                  */
-  size_t cand_term;    /* float  [R, parts, seg]  ... the term the scan added to the unit's exp-sum   */
-  size_t cand_unit;    /* uint16 [R, parts, seg]  ... scan unit                                       */
+  size_t cand_rec;     /* int32  [R, parts, seg, 4]  ... slot, token position, the term the scan added to the unit's
+                                                     exp-sum (float bits), scan unit                 */
+  size_t cand_bin;     /* uint16 [R, parts, seg]  ... bin between the threshold and its upper companion */
   size_t part_hist;    /* uint32 [R, parts, PQHSA_SELECT_BINS + 4]  candidates per bin and part        */
   size_t part_cnt;     /* int32  [R, parts]       candidates found by each part (> seg: overflow)      */
   size_t sel_slot;     /* int32  [R, kcap]  the K selected slots (unordered)               */

@@ -542,6 +542,68 @@ class OracleStream:
             live = self._vcnt > 0
             self.value_means[live] = self._vsum[live] / self._vcnt[live].unsqueeze(1)
 
+    # ---- production deferred flush (benchmarks/e2e_pq_param_sweep.py:3021-3344, incremental branch) ----
+    def apply_pending_incremental_flush(self) -> bool:
+        """The head-batched flush of the production adapter with PQ_HSA_INCREMENTAL_FLUSH=1 (its default),
+        restated for one stream: the keys that left the local window since the last update move the coarse
+        centroids and the code words by one EMA step (benchmarks/e2e_pq_param_sweep.py:3173-3220, PQ part
+        :2454-2513), then ONLY those keys are assigned and encoded against the moved codebooks (:3222-3256) -
+        old list ids and codes stay - and the value means are merged count-weighted (:3259-3281).
+        PARITY UNPINNED for this method: the reference code needs CUDA tensors (:3049-3054), so no fixture of
+        the reference itself could be generated; it follows the cited lines in fp32."""
+        if not self.deferred_pending:
+            return False
+        self.deferred_pending = False
+        if self.index is None:
+            self._refresh_now()
+            return True
+        s, old_r = self.bounds()
+        self.indexed_length = self.length
+        self.pending = 0
+        s, r = self.bounds()
+        if r <= old_r:
+            return True
+        ix, lr, eps = self.index, self.icfg.online_codebook_lr, self.icfg.eps
+        new_keys, new_vals = self.keys[old_r:r], self.values[old_r:r]
+        uu, nrm = ix.split_direction(new_keys)
+        lists = ix.coarse.shape[0]
+        # coarse EMA on the update batch (:3173-3190), then re-assignment and residuals (:3191-3195)
+        lid = ix.assign(uu)
+        sums = torch.zeros_like(ix.coarse)
+        sums.index_add_(0, lid, uu)
+        cnt = torch.bincount(lid, minlength=lists).to(uu.dtype)
+        means = sums / cnt.unsqueeze(1).clamp_min(eps)
+        ix.coarse = torch.where((cnt > 0).unsqueeze(1), (1.0 - lr) * ix.coarse + lr * means, ix.coarse)
+        lid = ix.assign(uu)
+        ures = uu - ix.coarse[lid]
+        # code-word EMA on the update residuals (:3197-3220 = :2454-2513)
+        m, ncodes, sub = ix.codebooks.shape
+        chunks = ures.reshape(ures.shape[0], m, sub)
+        newbooks = ix.codebooks.clone()
+        for j in range(m):
+            a = torch.cdist(chunks[:, j, :].float(), ix.codebooks[j].float(), p=2).argmin(dim=1)
+            sj = torch.zeros_like(ix.codebooks[j])
+            sj.index_add_(0, a, chunks[:, j, :])
+            nj = torch.bincount(a, minlength=ncodes).to(ures.dtype)
+            mu = sj / nj.unsqueeze(1).clamp_min(eps)
+            newbooks[j] = torch.where((nj > 0).unsqueeze(1), (1.0 - lr) * ix.codebooks[j] + lr * mu, ix.codebooks[j])
+        ix.codebooks = newbooks
+        # only the update batch is encoded, against the moved codebooks (:3222-3256)
+        old_counts = torch.bincount(ix.list_ids, minlength=lists).to(new_vals.dtype)
+        ix.list_ids = torch.cat([ix.list_ids, lid])
+        ix.norms = torch.cat([ix.norms, nrm])
+        ix.packed = torch.cat([ix.packed, pack_nibbles(pq_encode(ures, ix.codebooks))])
+        # value means: count-weighted merge (:3259-3281)
+        vs = torch.zeros_like(self.value_means)
+        vs.index_add_(0, lid, new_vals)
+        new_counts = old_counts + torch.bincount(lid, minlength=lists).to(new_vals.dtype)
+        self.value_means = torch.where(
+            (new_counts > 0).unsqueeze(1),
+            (self.value_means * old_counts.unsqueeze(1) + vs) / new_counts.unsqueeze(1).clamp_min(eps),
+            torch.zeros_like(self.value_means))
+        self._vsum = self._vcnt = None
+        return True
+
     # ---- forward (pq_hsa/attention/sparse_attention.py:245-345) ---------
     def forward_detail(self, queries: torch.Tensor) -> HybridDetail:
         scale = (1.0 / sqrt(queries.shape[-1])) if self.acfg.scale is None else self.acfg.scale

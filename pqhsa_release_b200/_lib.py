@@ -17,7 +17,10 @@ RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK = range(5)
 F32, BF16, F16 = 0, 1, 2
 STAGE_LUT, STAGE_SCAN, STAGE_SELECT, STAGE_ATTEND, STAGE_MERGE = range(5)
 
-_LIB_PATH = Path(__file__).resolve().parent / "libpqhsa_b200.so"
+import os
+
+# PQHSA_LIBRARY names another build of the same ABI (a debug build, a build kept outside the package)
+_LIB_PATH = Path(os.environ.get("PQHSA_LIBRARY") or Path(__file__).resolve().parent / "libpqhsa_b200.so")
 
 
 class Params(C.Structure):
@@ -51,10 +54,10 @@ class WsLayout(C.Structure):
     _fields_ = [
         ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("pair_tab", C.c_size_t),
         ("row_bin", C.c_size_t),
-        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
+        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("enc_best", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
-        ("cand_key", C.c_size_t), ("cand_slot", C.c_size_t), ("cand_pos", C.c_size_t), ("cand_term", C.c_size_t),
-        ("cand_unit", C.c_size_t), ("part_hist", C.c_size_t), ("part_cnt", C.c_size_t),
+        ("cand_key", C.c_size_t), ("cand_rec", C.c_size_t), ("cand_bin", C.c_size_t),
+        ("part_hist", C.c_size_t), ("part_cnt", C.c_size_t),
         ("sel_slot", C.c_size_t), ("sel_off", C.c_size_t), ("partial", C.c_size_t), ("row_ticket", C.c_size_t), ("work_counter", C.c_size_t), ("combine_ticket", C.c_size_t),
         ("parts", C.c_int32), ("seg", C.c_int32), ("kcap", C.c_int32), ("tail_cap", C.c_int32), ("chunks", C.c_int32),
     ]

@@ -53,15 +53,18 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->kcap = topk_capacity(p);
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
-  // The selection of a row is shared by `parts` CTAs (a power of two): enough of them to fill the GPU when
-  // there are few rows, and enough that a part's candidate list (`seg` entries, a quarter more than an even
+  // With fewer than 96 query rows the selection of a row is shared by `parts` CTAs (a power of two): enough of
+  // them to fill the GPU, and enough that a part's candidate list (`seg` entries, a quarter more than an even
   // share of the candidates a row can reasonably have) fits in shared memory.
   {
     const size_t ccap = cap < (size_t)2 * o->kcap + 2048 ? cap : (size_t)2 * o->kcap + 2048;
     int parts = 1;
-    while (parts < 16 && (R * parts < 296 || ccap * 5 / 4 > (size_t)parts * 8192)) parts *= 2;
-    o->parts = parts;
-    o->seg = (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
+    if (R < 96) {
+      parts = 2;
+      while (parts < 16 && (R * parts < 296 || ccap * 5 / 4 > (size_t)parts * 8192)) parts *= 2;
+    }
+    o->parts = parts;  // 1: enough rows to fill the GPU with one CTA per row, which then needs no candidate lists
+    o->seg = parts == 1 ? 8 : (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
   }
   const size_t nrec = R * (size_t)o->parts * (size_t)o->seg;
   size_t off = 0;
@@ -78,16 +81,15 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->ticket = take(2 * S * sizeof(int32_t));
   o->slog = take(R * kSample * sizeof(float));
   o->norm_pend = take(S * sizeof(float));
+  o->enc_best = take(S * 16 * 2 * sizeof(float));
   o->unit_max = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->unit_sum = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
   o->row_info = take(R * kRI * sizeof(int32_t));
   o->hitmap = take(R * (size_t)p->unit_capacity * (kUnit / 32) * sizeof(uint32_t));
   o->cand_key = take(nrec * sizeof(uint32_t));
-  o->cand_slot = take(nrec * sizeof(int32_t));
-  o->cand_pos = take(nrec * sizeof(int32_t));
-  o->cand_term = take(nrec * sizeof(float));
-  o->cand_unit = take(nrec * sizeof(uint16_t));
+  o->cand_rec = take(nrec * 4 * sizeof(int32_t));
+  o->cand_bin = take(nrec * sizeof(uint16_t));
   o->part_hist = take(R * (size_t)o->parts * (PQHSA_SELECT_BINS + 4) * sizeof(uint32_t));
   o->part_cnt = take(R * (size_t)o->parts * sizeof(int32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));

@@ -198,7 +198,9 @@ __device__ __forceinline__ void background_item(const AttendArgs& a, int row, in
   }
 }
 
-template <typename E>
+// MAPPED: the streams' query blocks are looked up in io_map (a separate instantiation, so that the plain case keeps
+// its address arithmetic free of the lookup).
+template <typename E, bool MAPPED>
 __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs a) {
   __shared__ float wm[kAttWarps], wl[kAttWarps];
   __shared__ float wacc[kAttWarps][kD];
@@ -262,12 +264,16 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
     }
     // query slice of this lane, pre-multiplied by scale * log2(e)
     float qv[8];
-    const int qb = a.io_map != nullptr ? a.io_map[s] : s;  // negative: idle stream (it has no entries either)
-    if (qb >= 0) {
-      load8(static_cast<const E*>(a.q) + ((size_t)qb * a.G + (row - s * a.G)) * kD + l16 * 8, qv);
-    } else {
+    if constexpr (MAPPED) {
+      const int qb = a.io_map[s];  // negative: idle stream (it has no entries either)
+      if (qb >= 0) {
+        load8(static_cast<const E*>(a.q) + ((size_t)qb * a.G + (row - s * a.G)) * kD + l16 * 8, qv);
+      } else {
 #pragma unroll
-      for (int d = 0; d < 8; ++d) qv[d] = 0.f;
+        for (int d = 0; d < 8; ++d) qv[d] = 0.f;
+      }
+    } else {
+      load8(static_cast<const E*>(a.q) + (size_t)row * kD + l16 * 8, qv);
     }
 #pragma unroll
     for (int d = 0; d < 8; ++d) qv[d] *= a.scale * kLog2e;
@@ -304,10 +310,11 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
         for (int u = 0; u < kAttUnroll; ++u) {
           float kf[8];
           cvt_row(kr[u], kf);
-          float d0 = kf[0] * qv[0];
+          // two dims per instruction (packed f32x2 multiply-add)
+          float2 d2 = __fmul2_rn(make_float2(kf[0], kf[1]), make_float2(qv[0], qv[1]));
 #pragma unroll
-          for (int d = 1; d < 8; ++d) d0 = fmaf(kf[d], qv[d], d0);
-          dp[u] = d0;
+          for (int d = 2; d < 8; d += 2) d2 = __ffma2_rn(make_float2(kf[d], kf[d + 1]), make_float2(qv[d], qv[d + 1]), d2);
+          dp[u] = d2.x + d2.y;
         }
         const bool b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
         const float e0 = (b3 ? dp[2] : dp[0]) + __shfl_xor_sync(0xffffffffu, b3 ? dp[0] : dp[2], 8);
@@ -327,16 +334,26 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
       if (mx != kNegInf) {
         const float corr = ex2(m - mx);  // m == -inf gives 0
         l *= corr;
+        const float2 c2 = make_float2(corr, corr);
 #pragma unroll
-        for (int d = 0; d < 8; ++d) acc[d] *= corr;
+        for (int d = 0; d < 8; d += 2) {
+          const float2 t = __fmul2_rn(make_float2(acc[d], acc[d + 1]), c2);
+          acc[d] = t.x;
+          acc[d + 1] = t.y;
+        }
 #pragma unroll
         for (int u = 0; u < kAttUnroll; ++u) {
           const float pe = ex2(x[u] - mx);
+          const float2 p2 = make_float2(pe, pe);
           float vf[8];
           cvt_row(vr[u], vf);
           l += pe;
 #pragma unroll
-          for (int d = 0; d < 8; ++d) acc[d] = fmaf(pe, vf[d], acc[d]);
+          for (int d = 0; d < 8; d += 2) {
+            const float2 t = __ffma2_rn(make_float2(vf[d], vf[d + 1]), p2, make_float2(acc[d], acc[d + 1]));
+            acc[d] = t.x;
+            acc[d + 1] = t.y;
+          }
         }
         m = mx;
       }
@@ -508,12 +525,12 @@ __global__ void __launch_bounds__(32) wait_peers_kernel(int32_t* const* peer_fla
   if (!ok) peer_seq[1] = 1;
 }
 
-template <typename E>
+template <typename E, bool MAPPED>
 static int launch_attend_t(const AttendArgs& a, bool combine, cudaStream_t st) {
   static int per_sm = 0;  // resident CTAs per SM of this instantiation
   if (per_sm == 0) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attend_kernel<E>, kAttThreads, 0) != cudaSuccess || n < 1)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attend_kernel<E, MAPPED>, kAttThreads, 0) != cudaSuccess || n < 1)
       n = 4;
     per_sm = n;
   }
@@ -525,7 +542,7 @@ static int launch_attend_t(const AttendArgs& a, bool combine, cudaStream_t st) {
     combine_kernel<E><<<(unsigned)a.R, kD, 0, st>>>(a);
     return check_launch("combine");
   }
-  attend_kernel<E><<<(unsigned)grid, kAttThreads, 0, st>>>(a);
+  attend_kernel<E, MAPPED><<<(unsigned)grid, kAttThreads, 0, st>>>(a);
   return check_launch("attend");
 }
 
@@ -569,7 +586,10 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
   // Few rows: the background of a row is a long chain and would be the kernel's critical path, so it is cut
   // into parts.  Many rows: the parts only add items, and one item per row hides behind the chunk items.
   a.bg_parts = a.R >= 96 ? 1 : kBgParts;  // kBgParts - 1 unit parts + the tail part
-  PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E>(a, combine, st)));
+  if (a.io_map != nullptr) {
+    PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E, true>(a, combine, st)));
+  }
+  PQHSA_DISPATCH_E(p.dtype, return (launch_attend_t<E, false>(a, combine, st)));
   return PQHSA_OK;
 }
 

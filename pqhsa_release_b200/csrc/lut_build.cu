@@ -60,6 +60,7 @@ struct LutArgs {
   float* row_bin;
   float* row_tau;
   int32_t* ticket;
+  float2* enc_best;  // [S, 16] nearest list of the key being encoded among each list CTA's lists: (distance, list as int bits)
   int num_lists, cap, G;
   float scale;
   double top_fraction;
@@ -98,6 +99,8 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
   __shared__ float qs[G][kD];
   __shared__ float lut_s[G][kM * kC];
   __shared__ float lsc_s[G][kListsPerCta];
+  __shared__ EncodeShared<kLutThreads> esh;
+  __shared__ int last_list_s;
   const int s = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const E* q = static_cast<const E*>(a.q);
@@ -107,14 +110,23 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
   const int n_sorted = st[PQHSA_ST_N_SORTED];
   const bool sampling = a.slog != nullptr && n_sorted > kSample;  // shorter streams: every key is a candidate
   const bool is_encode = (int)blockIdx.y >= a.list_ctas;
+  const bool bump = a.bump != 0 && seq_old > 0;
+  // One key to encode (the usual decode step): the list CTAs share the nearest-list search - each over the lists
+  // whose scores it computes anyway - and the one that arrives last among them finishes the key.  More keys: the
+  // encode CTA takes them one after the other.
+  const int want = a.encode ? (a.enc.enc_count ? a.enc.enc_count[s] : a.enc.uniform_count) : 0;
+  const bool shared_encode = want == 1;
 
-  if (is_encode) {
+  if (is_encode && shared_encode) {
+    // nothing to do here: the list CTAs encode the key
+  } else if (is_encode) {
     // encode role.  Only tokens that were in the cache when the kernel started are encoded: the row
-    // another CTA of this launch is writing is not read.  A larger norm is parked in norm_pend and
-    // folded into norm_max by the last CTA, like the length.
+    // another CTA of this launch is writing is not read (a row the caller stored before the call
+    // counts).  A larger norm is parked in norm_pend and folded into norm_max by the last CTA, like
+    // the length.
     if (tid == 0) a.enc.norm_max[s] = a.norm_max[s];
     __syncthreads();
-    const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old);
+    const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old + (bump ? 1 : 0));
     if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail;
   } else {
     const int l0 = blockIdx.y * kListsPerCta;
@@ -233,11 +245,54 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
       for (int g = 0; g < G; ++g)
         a.slog[((size_t)s * G + g) * kSample + i] = finish_logit(pq_sum_row(lut_s[g], code), lsc_s[g][l], kn);
     }
+    if (shared_encode) {
+      // the key that leaves the local window: position, slot, and whether it can be taken at all (never a token
+      // that is not in the cache, never beyond the pool) - the same tests as encode_tokens
+      const int n_tail_old = st[PQHSA_ST_N_TAIL];
+      const int seq_lim = seq_old + (bump ? 1 : 0);
+      const int pos = min(a.enc.sink, seq_lim) + n_sorted + n_tail_old, slot = n_sorted + n_tail_old;
+      const bool valid = pos < seq_lim && slot < a.enc.cap && n_tail_old < a.enc.tail_cap;
+      if (valid) {  // uniform over the CTA (and over the stream's CTAs)
+        const int nl = st[PQHSA_ST_N_LISTS];
+        const long long off = a.enc.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], pos);
+        float vval = 0.f;
+        if (tid < kD) vval = to_f(static_cast<const E*>(a.enc.v_base)[off + tid]);
+        const float nrm = enc_direction<E, kLutThreads>(static_cast<const E*>(a.enc.k_base), off, esh);
+        float bd;
+        int bl;
+        enc_nearest_list<E, kLutThreads>(coarse, l0, l0 + kListsPerCta, nl, esh, bd, bl);
+        if (tid == 0) {
+          a.enc_best[(size_t)s * 16 + blockIdx.y] = make_float2(bd, __int_as_float(bl));
+          __threadfence();
+          const int t = atomicAdd(a.ticket + 2 * s, 1);
+          last_list_s = (t == a.list_ctas - 1);
+          if (last_list_s) a.ticket[2 * s] = 0;  // ready for the next launch
+        }
+        __syncthreads();
+        if (last_list_s) {
+          if (tid == 0) {
+            float d0 = __builtin_huge_valf();
+            int lw = 0;
+            for (int y = 0; y < a.list_ctas; ++y) {  // ascending list ranges: strict < keeps the lowest index on ties
+              const float2 b = __ldcg(a.enc_best + (size_t)s * 16 + y);
+              if (y * kListsPerCta < nl && b.x < d0) {
+                d0 = b.x;
+                lw = __float_as_int(b.y);
+              }
+            }
+            esh.list_sh = lw;
+            a.enc.norm_max[s] = a.norm_max[s];  // the pending norm bound starts from the stream's
+          }
+          __syncthreads();
+          enc_finish<E, kLutThreads>(a.enc, s, slot, pos, esh.list_sh, nrm, vval, w, esh);
+          if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail_old + 1;
+        }
+      }
+    }
   }
 
   // ---- counters: the CTA of the stream that arrives last of all.  Every CTA of the stream is then done
   // reading the length: the token written above now counts, a larger norm becomes the stream's bound ----
-  const bool bump = a.bump != 0 && seq_old > 0;
   if (!append && !a.encode && !bump) return;
   __syncthreads();
   if (tid == 0) {
@@ -398,6 +453,7 @@ static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const
   a.row_bin = reinterpret_cast<float*>(ws + w.row_bin);
   a.row_tau = reinterpret_cast<float*>(ws + w.row_tau);
   a.ticket = reinterpret_cast<int32_t*>(ws + w.ticket);
+  a.enc_best = w.enc_best == (size_t)-1 ? nullptr : reinterpret_cast<float2*>(ws + w.enc_best);
   a.num_lists = p.num_lists;
   a.cap = p.slot_capacity;
   a.G = p.group;

@@ -4,30 +4,39 @@
 // leave the chip except for the ~2K candidates per row).
 //
 // The scan left one bit per (row, slot): the key's approximate logit reached the
-// row's threshold tau.  The selection is two launches, each with `parts` CTAs per
-// query row so that the GPU is full whatever the row count is; a CTA never waits
-// for another one (the second launch starts when the first has ended).
+// row's threshold tau.  Two forms, chosen by the number of query rows R:
+//
+// R >= 96 - row_select_kernel, one CTA of 1024 threads per row (end of this file):
+// the GPU is full with a CTA per row, and the row's candidates never leave the SM.
+//
+// R < 96 (a shard of a multi-GPU step, a single request) - two launches with
+// `parts` CTAs per row, so that the GPU is full whatever the row count is; a CTA
+// never waits for another one (the second launch starts when the first has ended):
 //
 // cand_kernel.  The hit words of a row are dealt out to its CTAs word by word.  A
-// CTA turns its set bits into a candidate list in shared memory, scores the
-// candidates again from their codes (bit-identical to the scan; a few thousand
-// gathers that hit the L2 the scan just filled) and writes one record per
-// candidate - logit key, slot, token position, the term the scan added to the
-// unit's exp-sum for it, unit - plus a histogram of its candidates over
-// PQHSA_SELECT_BINS linear bins between tau and an upper companion tau_hi placed by
-// the threshold kernel (one more bin holds everything above).
+// CTA tabulates its words (bits, first slot, list, candidates listed before) in
+// shared memory; candidate i is then the (i - offset)-th set bit of the word a
+// binary search over the offsets finds, so every thread gets an even share of the
+// candidates whatever the words look like.  The candidates are scored again from
+// their codes (bit-identical to the scan; a few thousand gathers that hit the L2
+// the scan just filled) and one record per candidate is written - logit key, bin,
+// and (slot, token position, the term the scan added to the unit's exp-sum for it,
+// unit) - plus a histogram of the part's candidates over PQHSA_SELECT_BINS linear
+// bins between tau and an upper companion tau_hi placed by the threshold kernel
+// (one more bin holds everything above).
 //
 // emit_kernel.  Every CTA of a row adds up the row's partial histograms and walks
 // them from the top: the bin in which the count reaches K is the boundary bin.
-// Candidates above it are selected outright; of the boundary bin's few members the
-// best `need` are taken by (logit desc, slot asc) - by rank counting when there
-// are at most 256 of them, by a block radix select otherwise.  A CTA emits the
-// selected candidates of its own part: place in the selection, element offset of the
-// K/V row in the (paged) cache, and removal from the approximate side of the
-// softmax - exactly the term the scan added is subtracted from the unit's exp-sum
-// (a selected tail slot has its stored logit set to -inf).  This is the
-// "- old_exact_exp" of pq_hsa/attention/sparse_attention.py:985-1009, done per unit
-// so that no cancellation error is left behind.
+// One pass over the bins of all the row's candidates (eight to a 16-byte load)
+// collects the boundary bin's few members and emits this part's candidates above
+// it; of the boundary members the best `need` are taken by (logit desc, slot asc) -
+// by rank counting when there are at most 256 of them, by a block radix select
+// otherwise.  Emitting a candidate = its place in the selection, the element
+// offset of its K/V row in the (paged) cache, and its removal from the approximate
+// side of the softmax: exactly the term the scan added is subtracted from the
+// unit's exp-sum (a selected tail slot has its stored logit set to -inf).  This is
+// the "- old_exact_exp" of pq_hsa/attention/sparse_attention.py:985-1009, done per
+// unit so that no cancellation error is left behind.
 //
 // If fewer than K candidates turned up (the threshold estimate was too high,
 // probability ~1e-9 at the default margin), a part overflowed its list, or the
@@ -44,6 +53,9 @@ constexpr int kSelBins = PQHSA_SELECT_BINS;
 constexpr int kSelHist = kSelBins + 4;  // bins, the bin above them, padding to 16 bytes
 constexpr int kBoundPer = 8;
 constexpr int kBoundCap = kSelThreads * kBoundPer;  // boundary keys resolved in shared memory
+constexpr int kSelWords = 8;                        // hit words a thread holds at a time
+constexpr int kSelBatch = 8;                        // candidates a thread holds at a time
+constexpr int kSelVecs = 4;                         // 8-candidate bin vectors a thread holds at a time
 constexpr int kSlotBits = 22;                       // a list entry is slot | list << 22
 constexpr uint32_t kSlotMask = (1u << kSlotBits) - 1u;
 
@@ -62,10 +74,8 @@ struct SelectArgs {
   int32_t* row_info;
   const uint32_t* hitmap;
   uint32_t* cand_key;
-  int32_t* cand_slot;
-  int32_t* cand_pos;
-  float* cand_term;
-  uint16_t* cand_unit;
+  int4* cand_rec;      // (slot, token position, exp-sum term as float bits, unit)
+  uint16_t* cand_bin;
   uint32_t* part_hist;
   int32_t* part_cnt;
   int32_t* sel_slot;
@@ -75,6 +85,7 @@ struct SelectArgs {
   float* tail_logit;
   KvAddr kv;
   int G, cap, ucap, tail_cap, kcap, parts, seg;
+  int wcap;  // hit words one part can hold: its share of the unit capacity
   double top_fraction;
   int topk_fixed;
 };
@@ -91,13 +102,46 @@ __device__ __forceinline__ int cand_bin(float logit, float lo, float inv_w) {
 
 // The words of a row's hit map are dealt out so that word `it` of unit u goes to part (u + it) mod parts:
 // full units spread their four words, units of a few slots (only word 0 populated) spread by unit.
-__device__ __forceinline__ bool word_of_part(int u, int it, int part, int parts) { return ((u + it) & (parts - 1)) == part; }
+// A part enumerates its words by an index k: with parts <= 4 every unit gives it 4 / parts words, with
+// more parts every run of `parts` units gives it four.
+__device__ __forceinline__ int part_word_count(int parts, int n_all) {
+  return parts <= 4 ? n_all * (4 / parts) : ((n_all + parts - 1) / parts) * 4;
+}
+__device__ __forceinline__ bool part_word(int k, int parts, int part, int n_all, int& u, int& it) {
+  if (parts <= 4) {
+    const int lm = parts == 1 ? 2 : (parts == 2 ? 1 : 0);  // log2(4 / parts): no integer division in the loops
+    u = k >> lm;
+    it = ((part - u) & (parts - 1)) + parts * (k & ((1 << lm) - 1));
+  } else {
+    u = parts * (k >> 2) + ((part - (k & 3)) & (parts - 1));
+    it = k & 3;
+  }
+  return u < n_all;
+}
+
+// position of the n-th (0-based) set bit of `bits` (n < popc(bits))
+__device__ __forceinline__ int nth_set_bit(uint32_t bits, int n) {
+  int pos = 0;
+#pragma unroll
+  for (int w = 16; w >= 1; w >>= 1) {
+    const int c = __popc(bits & ((1u << w) - 1u));
+    if (n >= c) {
+      n -= c;
+      bits >>= w;
+      pos += w;
+    }
+  }
+  return pos;
+}
 
 template <typename E>
-__global__ void __launch_bounds__(kSelThreads) cand_kernel(const SelectArgs a) {
+__global__ void __launch_bounds__(kSelThreads, 4) cand_kernel(const SelectArgs a) {
+  // per hit word of this part: candidates listed before it, its bits, its first slot, its list (0xFFFF: tail)
   extern __shared__ __align__(16) unsigned char sel_smem[];
-  uint32_t* cslot = reinterpret_cast<uint32_t*>(sel_smem);       // [seg] slot | list << kSlotBits
-  uint16_t* cunit = reinterpret_cast<uint16_t*>(cslot + a.seg);  // [seg]
+  uint32_t* woff = reinterpret_cast<uint32_t*>(sel_smem);
+  uint32_t* wbits = woff + a.wcap;
+  int32_t* wfirst = reinterpret_cast<int32_t*>(wbits + a.wcap);
+  uint16_t* wlist = reinterpret_cast<uint16_t*>(wfirst + a.wcap);
   __shared__ float lut_s[kM * kC];
   __shared__ float lsc_s[kLMax];
   __shared__ uint32_t hist[kSelHist];
@@ -128,103 +172,120 @@ __global__ void __launch_bounds__(kSelThreads) cand_kernel(const SelectArgs a) {
   for (int i = tid; i < kLMax; i += kSelThreads) lsc_s[i] = a.list_scores[(size_t)row * kLMax + i];
   for (int i = tid; i < kSelHist; i += kSelThreads) hist[i] = 0u;
 
-  // ---- pass 1: how many candidates this thread's words hold ----
+  // ---- the part's hit words, kSelWords consecutive ones per thread: bits, first slot and list go to shared
+  // memory together with the number of candidates listed before the word ----
   const int n_all = n_units + (n_tail + kUnit - 1) / kUnit;  // sorted units, then 128-slot chunks of the tail
-  int mine = 0;
-  for (int u = tid; u < n_all; u += kSelThreads) {
+  const int nwp = min(part_word_count(P, n_all), a.wcap);
+  int C = 0;  // candidates so far (all rounds)
+  for (int k0 = 0; k0 < nwp; k0 += kSelWords * kSelThreads) {
+    uint32_t b[kSelWords], l[kSelWords];
+    int first[kSelWords];
 #pragma unroll
-    for (int it = 0; it < kUnit / 32; ++it)
-      if (word_of_part(u, it, part, P)) mine += __popc(__ldg(hm + (size_t)u * (kUnit / 32) + it));
-  }
-  int incl = mine;
+    for (int j = 0; j < kSelWords; ++j) {
+      const int k = k0 + tid * kSelWords + j;
+      int u, it;
+      b[j] = 0u;
+      l[j] = 0xFFFFu;
+      first[j] = 0;
+      if (k < nwp && part_word(k, P, part, n_all, u, it)) {
+        b[j] = __ldg(hm + (size_t)u * (kUnit / 32) + it);
+        if (u < n_units) {
+          first[j] = uoff[u] + it * 32;
+          l[j] = ulist[u];
+        } else {
+          first[j] = n_sorted + (u - n_units) * kUnit + it * 32;
+        }
+      }
+    }
+    int mine = 0;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int v = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += v;
-  }
-  if (lane == 31) wtot[warp] = incl;
-  __syncthreads();  // also: tables, list scores and the cleared histogram are in place
-  int before = 0, C = 0;
+    for (int j = 0; j < kSelWords; ++j) mine += __popc(b[j]);
+    int incl = mine;
 #pragma unroll
-  for (int w = 0; w < kSelThreads / 32; ++w) {
-    const int v = wtot[w];
-    before += w < warp ? v : 0;
-    C += v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    __syncthreads();  // wtot of the previous round has been read
+    if (lane == 31) wtot[warp] = incl;
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kSelThreads / 32; ++w) {
+      const int v = wtot[w];
+      before += w < warp ? v : 0;
+      total += v;
+    }
+    int o = C + before + incl - mine;
+#pragma unroll
+    for (int j = 0; j < kSelWords; ++j) {
+      const int k = k0 + tid * kSelWords + j;
+      if (k < nwp) {
+        woff[k] = (uint32_t)o;
+        wbits[k] = b[j];
+        wfirst[k] = first[j];
+        wlist[k] = (uint16_t)l[j];
+      }
+      o += __popc(b[j]);
+    }
+    C += total;
   }
+  __syncthreads();  // the word table, the tables, the list scores and the cleared histogram are in place
   if (C > a.seg) {  // more candidates than this part can list: the row is selected from all keys
     if (tid == 0) *pcnt = C;
     return;
   }
-  // ---- pass 2: the set bits become list entries (the words are read again: L1 / L2 hits) ----
-  {
-    int o = before + incl - mine;
-    for (int u = tid; u < n_all; u += kSelThreads) {
-      const bool sorted = u < n_units;
-      int first0 = 0;
-      uint32_t l = 0xFFFFu;
-      bool have = false;
-#pragma unroll
-      for (int it = 0; it < kUnit / 32; ++it) {
-        if (!word_of_part(u, it, part, P)) continue;
-        uint32_t bits = __ldg(hm + (size_t)u * (kUnit / 32) + it);
-        if (bits == 0u) continue;
-        if (!have) {
-          have = true;
-          if (sorted) {
-            first0 = uoff[u];
-            l = ulist[u];
-          } else {
-            first0 = n_sorted + (u - n_units) * kUnit;
-          }
-        }
-        while (bits) {
-          const int slot = first0 + it * 32 + __ffs((int)bits) - 1;
-          bits &= bits - 1u;
-          cslot[o] = (uint32_t)slot | ((sorted ? l : (uint32_t)lids[slot]) << kSlotBits);
-          cunit[o] = (uint16_t)u;
-          ++o;
-        }
-      }
-    }
-  }
-  __syncthreads();
 
-  // ---- the candidates are scored again, four per thread at a time: their gathers travel together ----
+  // ---- candidate i (a thread takes i = tid, tid + 256, ...: an even share whatever the words look like) is the
+  // (i - woff[w])-th set bit of the last word w whose offset does not exceed i; kSelBatch candidates per thread
+  // are scored again at a time, so that their gathers travel together ----
   const size_t rec0 = ((size_t)row * P + part) * a.seg;
-  for (int i0 = 0; i0 < C; i0 += 4 * kSelThreads) {
-    uint32_t ent[4], code[4];
-    float kn[4], um[4];
-    int pos[4], un[4];
+  for (int i0 = 0; i0 < C; i0 += kSelBatch * kSelThreads) {
+    uint32_t code[kSelBatch];
+    float kn[kSelBatch], um[kSelBatch];
+    int slot[kSelBatch], pos[kSelBatch], un[kSelBatch], li[kSelBatch];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int i = i0 + j * kSelThreads + tid;
-      ent[j] = i < C ? cslot[i] : 0xFFFFFFFFu;
+    for (int j = 0; j < kSelBatch; ++j) {
+      slot[j] = -1;
       code[j] = 0u;
       kn[j] = 0.f;
       um[j] = 0.f;
       pos[j] = 0;
       un[j] = 0;
+      li[j] = 0;
+      if (i0 + j * kSelThreads >= C) continue;  // block-uniform: slots past the list cost nothing
+      const int i = i0 + j * kSelThreads + tid;
       if (i < C) {
-        const int slot = (int)(ent[j] & kSlotMask);
-        un[j] = cunit[i];
-        code[j] = __ldg(codes + slot);
-        kn[j] = to_f(norms[slot]);
-        pos[j] = spos[slot];
-        if (slot < n_sorted) um[j] = umax[un[j]];
+        int lo_w = 0, hi_w = nwp;  // first word whose offset exceeds i
+        while (lo_w < hi_w) {
+          const int mid = (lo_w + hi_w) >> 1;
+          if (woff[mid] <= (uint32_t)i) lo_w = mid + 1; else hi_w = mid;
+        }
+        const int w = lo_w - 1;
+        int u, it;
+        part_word(w, P, part, n_all, u, it);
+        slot[j] = wfirst[w] + nth_set_bit(wbits[w], i - (int)woff[w]);
+        un[j] = u;
+        li[j] = wlist[w];
+        code[j] = __ldg(codes + slot[j]);
+        kn[j] = to_f(norms[slot[j]]);
+        pos[j] = spos[slot[j]];
+        if (li[j] == 0xFFFF) li[j] = lids[slot[j]];  // a tail slot carries its own list
+        else um[j] = umax[u];
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kSelBatch; ++j) {
+      if (i0 + j * kSelThreads >= C) continue;  // block-uniform
       const int i = i0 + j * kSelThreads + tid;
       if (i >= C) continue;
-      const int slot = (int)(ent[j] & kSlotMask);
-      const float x = finish_logit(pq_sum_row(lut_s, code[j]), lsc_s[ent[j] >> kSlotBits], kn[j]);
-      atomicAdd(&hist[cand_bin(x, lo, inv_w)], 1u);
+      const float x = finish_logit(pq_sum_row(lut_s, code[j]), lsc_s[li[j]], kn[j]);
+      const int bin = cand_bin(x, lo, inv_w);
+      atomicAdd(&hist[bin], 1u);
+      const float term = slot[j] < n_sorted ? unit_term(x, unit_ref(um[j])) : 0.f;
       a.cand_key[rec0 + i] = float_key(x);
-      a.cand_slot[rec0 + i] = slot;
-      a.cand_pos[rec0 + i] = pos[j];
-      a.cand_term[rec0 + i] = slot < n_sorted ? unit_term(x, unit_ref(um[j])) : 0.f;
-      a.cand_unit[rec0 + i] = (uint16_t)un[j];
+      a.cand_bin[rec0 + i] = (uint16_t)bin;
+      a.cand_rec[rec0 + i] = make_int4(slot[j], pos[j], __float_as_int(term), un[j]);
     }
   }
   __syncthreads();
@@ -241,11 +302,13 @@ struct EmitShared {
   int emit_count;        // this CTA's selected candidates placed so far
   int base_above;        // selected candidates above the boundary in the parts before this one
   int base_bound;        // taken boundary keys in the parts before this one (radix path)
+  int pcnt[16];          // candidates listed by part q
+  int vpref[17];         // 8-candidate vectors of the parts before part q
   uint32_t wsum[kSelThreads / 32];
 };
 
 template <typename E>
-__global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
+__global__ void __launch_bounds__(kSelThreads, 4) emit_kernel(const SelectArgs a) {
   extern __shared__ __align__(16) unsigned char sel_smem[];
   uint32_t* bkey = reinterpret_cast<uint32_t*>(sel_smem);  // [kBoundCap] boundary keys: logit key,
   uint32_t* bslot = bkey + kBoundCap;                      //   slot,
@@ -274,7 +337,6 @@ __global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
     return;
   }
   const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
-  const float lo = a.row_bin[2 * row], inv_w = a.row_bin[2 * row + 1];
   const uint32_t* ph = a.part_hist + (size_t)row * P * kSelHist;
   const int32_t* pc = a.part_cnt + (size_t)row * P;
   int32_t* sel = a.sel_slot + (size_t)row * a.kcap;
@@ -303,6 +365,17 @@ __global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
     }
     const int over = __any_sync(0xffffffffu, cnt > a.seg);
     const int tot = __reduce_add_sync(0xffffffffu, cnt);
+    {
+      const int nv = (lane < P && !over) ? (cnt + 7) >> 3 : 0;
+      int incl = nv;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (lane < 16) es.pcnt[lane] = lane < P ? cnt : 0;
+      if (lane <= 16) es.vpref[lane] = incl - nv;  // lanes >= P hold the total
+    }
     const int tops = __reduce_add_sync(0xffffffffu, over ? 0 : top);
     if (lane == 0) {
       es.total = tot;
@@ -364,22 +437,22 @@ __global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
   }
   if (!fallback && nb > kBoundCap) fallback = true;
 
-  // one selected candidate of this part: its place in the selection, the offset of its K/V row, and its
-  // removal from the approximate side of the softmax
+  // one selected candidate of this part: its place in the selection, the offset of its K/V row, and its removal from
+  // the approximate side of the softmax
   const size_t rec0 = ((size_t)row * P + part) * a.seg;
-  auto emit = [&](int i, int o) {
+  auto emit_rec = [&](const int4& r, int o) {  // r = (slot, token position, term, unit)
     if (o >= a.kcap) return;
-    const int slot = a.cand_slot[rec0 + i];
-    sel[o] = slot;
-    soff[o] = a.kv.offset(req, head, a.cand_pos[rec0 + i]);
-    if (slot < n_sorted)
-      atomicAdd(usum + a.cand_unit[rec0 + i], -a.cand_term[rec0 + i]);
+    sel[o] = r.x;
+    soff[o] = a.kv.offset(req, head, r.y);
+    if (r.x < n_sorted)
+      atomicAdd(usum + r.w, -__int_as_float(r.z));
     else
-      tlog[slot - n_sorted] = kNegInf;
+      tlog[r.x - n_sorted] = kNegInf;
   };
+  auto emit = [&](int i, int o) { emit_rec(__ldg(a.cand_rec + rec0 + i), o); };
 
   if (!fallback) {
-    // ---- selected candidates above the boundary in the parts before this one ----
+    // ---- selected candidates above the boundary in the parts before this one (the histograms again: L1 hits) ----
     if (part > 0) {
       uint32_t v = 0;
       for (int pp = 0; pp < part; ++pp) {
@@ -391,38 +464,85 @@ __global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
       v = __reduce_add_sync(0xffffffffu, v);
       if (lane == 0 && v != 0u) atomicAdd(&es.base_above, (int)v);
     }
-    // ---- the boundary bin's keys, from all parts ----
-    if (need > 0) {
-      for (int pp = 0; pp < P; ++pp) {
-        const int cnt = pc[pp];
-        const size_t r0 = ((size_t)row * P + pp) * a.seg;
-        for (int i = tid; i < cnt; i += kSelThreads) {
-          const uint32_t k = a.cand_key[r0 + i];
-          if (cand_bin(key_float(k), lo, inv_w) == bstar) {
-            const int o = atomicAdd(&es.bcount, 1);
-            if (o < kBoundCap) {
-              bkey[o] = k;
-              bslot[o] = (uint32_t)a.cand_slot[r0 + i];
-              bref[o] = ((uint32_t)pp << 24) | (uint32_t)i;
+    __syncthreads();
+    const int base_above = es.base_above;
+    // ---- one pass over the bins of all the row's candidates, eight to a 16-byte vector, the parts' lists walked as
+    // one sequence with kSelVecs vectors per thread in flight: members of the boundary bin are collected from every
+    // part; candidates of this part above the boundary are placed (one shared-memory atomic per warp) and emitted ----
+    {
+      const int VT = es.vpref[P];
+      for (int g0 = 0; g0 < VT; g0 += kSelVecs * kSelThreads) {
+        uint4 w[kSelVecs];
+        int vpp[kSelVecs], vidx[kSelVecs];
+#pragma unroll
+        for (int j = 0; j < kSelVecs; ++j) {
+          vpp[j] = -1;
+          vidx[j] = 0;
+          w[j] = make_uint4(0u, 0u, 0u, 0u);
+          if (g0 + j * kSelThreads >= VT) continue;  // block-uniform
+          const int g = g0 + j * kSelThreads + tid;
+          if (g < VT) {
+            int pp = 0;
+            for (int q = 1; q < P; ++q) pp += g >= es.vpref[q] ? 1 : 0;
+            vpp[j] = pp;
+            vidx[j] = g - es.vpref[pp];
+            w[j] = __ldg(reinterpret_cast<const uint4*>(a.cand_bin + ((size_t)row * P + pp) * a.seg) + vidx[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kSelVecs; ++j) {
+          if (g0 + j * kSelThreads >= VT) continue;  // block-uniform
+          unsigned mask = 0u;
+          if (vpp[j] >= 0) {
+            const int cnt = es.pcnt[vpp[j]];
+            const uint32_t ww[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int bin = (int)((ww[e >> 1] >> (16 * (e & 1))) & 0xFFFFu);
+              const int i = vidx[j] * 8 + e;
+              if (i < cnt) {
+                if (need > 0 && bin == bstar) {
+                  const int o = atomicAdd(&es.bcount, 1);
+                  if (o < kBoundCap) bref[o] = ((uint32_t)vpp[j] << 24) | (uint32_t)i;
+                }
+                if (bin > bstar && vpp[j] == part) mask |= 1u << e;
+              }
             }
+          }
+          if (__ballot_sync(0xffffffffu, mask != 0u) == 0u) continue;  // warp-uniform
+          const int mine = __popc(mask);
+          int incl = mine;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+          }
+          int base = 0;
+          if (lane == 31) base = atomicAdd(&es.emit_count, incl);
+          int o = base_above + __shfl_sync(0xffffffffu, base, 31) + incl - mine;
+          // the records of four finds at a time are requested together
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            int4 r[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if ((mask >> (4 * h + e)) & 1u) r[e] = __ldg(a.cand_rec + rec0 + vidx[j] * 8 + 4 * h + e);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if ((mask >> (4 * h + e)) & 1u) emit_rec(r[e], o++);
           }
         }
       }
     }
-    __syncthreads();
-    const int base_above = es.base_above;
-    // ---- candidates of this part above the boundary ----
-    {
-      const int cnt = pc[part];
-      for (int i0 = 0; i0 < cnt; i0 += kSelThreads) {
-        const int i = i0 + tid;
-        const bool take = i < cnt && cand_bin(key_float(a.cand_key[rec0 + i]), lo, inv_w) > bstar;
-        const unsigned m = __ballot_sync(0xffffffffu, take);
-        int base = 0;
-        if (m != 0u && lane == 0) base = atomicAdd(&es.emit_count, __popc(m));
-        base = __shfl_sync(0xffffffffu, base, 0) + __popc(m & ((1u << lane) - 1u));
-        if (take) emit(i, base_above + base);
+    if (need > 0) {
+      __syncthreads();
+      // the boundary members' keys and slots (ties are broken towards the lower slot)
+      for (int i = tid; i < nb; i += kSelThreads) {
+        const size_t at = ((size_t)row * P + (bref[i] >> 24)) * a.seg + (bref[i] & 0xFFFFFFu);
+        bkey[i] = __ldg(a.cand_key + at);
+        bslot[i] = (uint32_t)__ldg(a.cand_rec + at).x;
       }
+      __syncthreads();
     }
     // ---- the boundary: the best `need` of its nb keys by (logit desc, slot asc) ----
     if (need > 0) {
@@ -545,6 +665,324 @@ __global__ void __launch_bounds__(kSelThreads) emit_kernel(const SelectArgs a) {
   }
 }
 
+// ---- one CTA per query row --------------------------------------------------------------------------
+// With many query rows (R >= 96) a row's selection stays in one CTA of 1024 threads; the GPU is full with one CTA per
+// row, and nothing is written to or read back from global memory in between.
+//   1. Word table: a thread takes 8 consecutive hit words (two 16-byte loads) with their first slot and list, and the
+//      table in shared memory says for every word how many candidates are listed before it.
+//   2. Candidate i belongs to the last word whose offset does not exceed i: the words write their index at their offset
+//      into an array over the candidates and a prefix maximum carries it forward - every candidate finds its word with
+//      one load, and the threads get even shares (i = tid, tid + 1024, ...) whatever the bits look like.
+//   3. The candidates are scored again (bit-identical to the scan), at most 8 per thread in registers; a block radix
+//      select over the register-resident keys finds the K-th largest (ties to the lower slot); the CTA emits.
+// More than 8192 candidates, or fewer than K (the threshold estimate failed): the same select over all N slots with the
+// keys recomputed on every pass - slow, exact, flagged.
+constexpr int kRowThreads = 1024;
+constexpr int kRowPer = 8;                          // candidates per thread held in registers
+constexpr int kRowCandCap = kRowThreads * kRowPer;  // more candidates than that select from all keys
+constexpr int kRowWords = 8;                        // consecutive hit words per thread and round
+
+struct RowShared {
+  float lut[kM * kC];
+  float lsc[kLMax];
+  int wtot[kRowThreads / 32];
+  int emit_count;
+};
+
+template <typename E>
+__global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArgs a) {
+  extern __shared__ __align__(16) unsigned char sel_smem[];
+  uint32_t* wbits = reinterpret_cast<uint32_t*>(sel_smem);              // [wcap] bits of a hit word
+  int32_t* wfirst = reinterpret_cast<int32_t*>(wbits + a.wcap);         // [wcap] slot of its bit 0
+  uint16_t* woff = reinterpret_cast<uint16_t*>(wfirst + a.wcap);        // [wcap] candidates listed before it
+  uint16_t* wlist = woff + a.wcap;                                      // [wcap] its list (0xFFFF: tail, per slot)
+  uint16_t* owner = wlist + a.wcap;                                     // [kRowCandCap] candidate -> word + 1
+  __shared__ RowShared sh;
+  __shared__ RadixShared rsh;
+  __shared__ RadixShared2 rsh2;
+  const int row = blockIdx.x, s = row / a.G;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int32_t* ri = a.row_info + (size_t)row * kRI;
+  const int32_t* st = a.state + (size_t)s * kST;
+  const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
+  const int N = n_sorted + n_tail;
+  const int K = resolve_topk(N, a.top_fraction, a.topk_fixed);
+  if (K <= 0) {
+    if (threadIdx.x == 0) {
+      ri[PQHSA_RI_K] = 0;
+      ri[PQHSA_RI_N] = N;
+      ri[PQHSA_RI_NCAND] = 0;
+      ri[PQHSA_RI_NSEL] = 0;
+      ri[PQHSA_RI_FALLBACK] = 0;
+    }
+    return;
+  }
+  const int req = st[PQHSA_ST_REQ], head = st[PQHSA_ST_KV_HEAD];
+  const uint32_t* codes = a.codes + (size_t)s * a.cap;
+  const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+  const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+  const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
+  const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
+  const float* umax = a.unit_max + (size_t)row * a.ucap;
+
+  if (tid < kM * kC) sh.lut[tid] = a.lut[(size_t)row * kM * kC + tid];
+  if (tid < kLMax) sh.lsc[tid] = a.list_scores[(size_t)row * kLMax + tid];
+  if (tid == 0) sh.emit_count = 0;
+
+  // ---- 1. the word table ----
+  const uint32_t* hm = a.hitmap + (size_t)row * a.ucap * (kUnit / 32);
+  const int nw = min((n_units + (n_tail + kUnit - 1) / kUnit) * (kUnit / 32), a.wcap);
+  int C = 0;  // candidates so far (all rounds); only counted once the list is known to overflow
+  for (int k0 = 0; k0 < nw; k0 += kRowWords * kRowThreads) {
+    const int kb = k0 + tid * kRowWords;  // this thread's words kb .. kb + 7: units kb / 4 and kb / 4 + 1
+    uint32_t b[kRowWords];
+    int first[2];
+    uint32_t l[2];
+#pragma unroll
+    for (int j = 0; j < kRowWords; ++j) b[j] = 0u;
+    if (kb < nw) {  // the hit map of a row is a whole number of 16-byte word quadruples
+      const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(hm + kb));
+      b[0] = q0.x; b[1] = q0.y; b[2] = q0.z; b[3] = q0.w;
+      if (kb + 4 < nw) {
+        const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(hm + kb + 4));
+        b[4] = q1.x; b[5] = q1.y; b[6] = q1.z; b[7] = q1.w;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int u = (kb >> 2) + h;
+      first[h] = 0;
+      l[h] = 0xFFFFu;
+      if (kb + 4 * h < nw) {
+        if (u < n_units) {
+          first[h] = uoff[u];
+          l[h] = ulist[u];
+        } else {
+          first[h] = n_sorted + (u - n_units) * kUnit;
+        }
+      }
+    }
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < kRowWords; ++j) mine += __popc(b[j]);
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    __syncthreads();  // wtot of the previous round has been read (and, first round, the tables are being loaded)
+    if (lane == 31) sh.wtot[warp] = incl;
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; ++w) {
+      const int v = sh.wtot[w];
+      before += w < warp ? v : 0;
+      total += v;
+    }
+    int o = C + before + incl - mine;
+    if (C + total <= kRowCandCap) {  // block-uniform
+#pragma unroll
+      for (int j = 0; j < kRowWords; ++j) {
+        const int k = kb + j;
+        if (k < nw) {
+          wbits[k] = b[j];
+          wfirst[k] = first[j >> 2] + (j & 3) * 32;
+          woff[k] = (uint16_t)o;
+          wlist[k] = (uint16_t)l[j >> 2];
+        }
+        o += __popc(b[j]);
+      }
+    }
+    C += total;
+  }
+  const int ncand = C;
+  const bool fallback = C < K || C > kRowCandCap;
+  if (fallback) C = N;
+  // ---- 2. candidate -> word ----
+  if (!fallback) {
+    __syncthreads();
+    for (int i = tid; i < C; i += kRowThreads) owner[i] = 0;
+    __syncthreads();
+    for (int k = tid; k < nw; k += kRowThreads)
+      if (wbits[k] != 0u) owner[woff[k]] = (uint16_t)(k + 1);
+    __syncthreads();
+    // prefix maximum: a thread takes `per` consecutive candidates, then the warps and the block are scanned
+    const int per = (C + kRowThreads - 1) / kRowThreads;  // <= kRowPer
+    const int i0 = tid * per;
+    uint32_t run = 0;
+    for (int j = 0; j < per; ++j)
+      if (i0 + j < C) run = max(run, (uint32_t)owner[i0 + j]);
+    uint32_t incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl = max(incl, v);
+    }
+    if (lane == 31) sh.wtot[warp] = (int)incl;
+    __syncthreads();
+    uint32_t before = 0;
+    for (int w = 0; w < warp; ++w) before = max(before, (uint32_t)sh.wtot[w]);
+    uint32_t carry = max(before, __shfl_up_sync(0xffffffffu, incl, 1));
+    if (lane == 0) carry = before;
+    for (int j = 0; j < per; ++j)
+      if (i0 + j < C) {
+        carry = max(carry, (uint32_t)owner[i0 + j]);
+        owner[i0 + j] = (uint16_t)carry;
+      }
+  }
+  __syncthreads();
+
+  // slot, list and unit of candidate i (normal path) / slot i (fallback)
+  auto locate = [&](int i, int& slot, int& list, int& unit) {
+    if (fallback) {
+      slot = i;
+      list = lids[i];
+      unit = 0;
+      return;
+    }
+    const int w = (int)owner[i] - 1;
+    slot = wfirst[w] + nth_set_bit(wbits[w], i - (int)woff[w]);
+    list = wlist[w];
+    if (list == 0xFFFF) list = lids[slot];
+    unit = w >> 2;
+  };
+  auto logit_at = [&](int slot, int list) -> float {
+    return finish_logit(pq_sum_row(sh.lut, __ldg(codes + slot)), sh.lsc[list], to_f(norms[slot]));
+  };
+  auto slot_of = [&](int i) -> int {
+    int slot, list, unit;
+    locate(i, slot, list, unit);
+    return slot;
+  };
+  auto key = [&](int i) -> uint32_t {
+    int slot, list, unit;
+    locate(i, slot, list, unit);
+    return float_key(logit_at(slot, list));
+  };
+  int32_t* sel = a.sel_slot + (size_t)row * a.kcap;
+  long long* soff = a.sel_off + (size_t)row * a.kcap;
+  const bool take_all = K >= C;
+  uint32_t T = 0u, T2 = 0u;
+  int t = 0;
+  const size_t sb = (size_t)s * a.cap;
+  if (!fallback) {
+    // ---- 3. the candidates sit in registers, kRowPer per thread; their gathers travel four at a time ----
+    uint32_t kreg[kRowPer];
+    int sreg[kRowPer], ureg[kRowPer];
+#pragma unroll
+    for (int j0 = 0; j0 < kRowPer; j0 += 4) {
+      uint32_t code[4];
+      int list[4];
+      float kn[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj, i = j * kRowThreads + tid;
+        kreg[j] = 0u;
+        sreg[j] = -1;
+        ureg[j] = 0;
+        code[jj] = 0u;
+        list[jj] = 0;
+        kn[jj] = 0.f;
+        if (j * kRowThreads >= C) continue;  // block-uniform: slots past the list cost nothing
+        if (i < C) {
+          locate(i, sreg[j], list[jj], ureg[j]);
+          code[jj] = __ldg(codes + sreg[j]);
+          kn[jj] = to_f(norms[sreg[j]]);
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        if (j * kRowThreads >= C) continue;  // block-uniform
+        if (sreg[j] >= 0) kreg[j] = float_key(finish_logit(pq_sum_row(sh.lut, code[jj]), sh.lsc[list[jj]], kn[jj]));
+      }
+    }
+    if (!take_all) {
+      const int ties = block_radix_threshold_regs<kRowThreads, kRowPer>(kreg, K, rsh2, T, t);
+      if (ties != t) {  // more keys tie at the K-th value than fit: lowest slots first
+        auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)slot_of(i) : 0u; };
+        int t2;
+        block_radix_threshold<kRowThreads>(tie_key, C, t, rsh, T2, t2);
+      }
+    }
+    // Emit: a taken key gets its place in the selection (one shared-memory atomic per warp), the
+    // element offset of its K/V row, and leaves the approximate side of the softmax - its unit's
+    // exp-sum loses exactly the term the scan added (a tail slot's stored logit becomes -inf).
+#pragma unroll
+    for (int j0 = 0; j0 < kRowPer; j0 += 4) {
+      int o[4], pos[4];
+      float um[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        o[jj] = -1;
+        pos[jj] = 0;
+        um[jj] = 0.f;
+        if (j * kRowThreads >= C) continue;  // block-uniform
+        const uint32_t k = kreg[j];
+        const bool take = k != 0u && (take_all || k > T || (k == T && ~(uint32_t)sreg[j] >= T2));
+        const unsigned m = __ballot_sync(0xffffffffu, take);
+        int base = 0;
+        if (m != 0u && lane == 0) base = atomicAdd(&sh.emit_count, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0) + __popc(m & ((1u << lane) - 1u));
+        o[jj] = take && base < a.kcap ? base : -1;
+        if (o[jj] >= 0) {
+          pos[jj] = a.slot_pos[sb + sreg[j]];
+          if (sreg[j] < n_sorted) um[jj] = umax[ureg[j]];
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        if (o[jj] < 0) continue;
+        sel[o[jj]] = sreg[j];
+        soff[o[jj]] = a.kv.offset(req, head, pos[jj]);
+        if (sreg[j] < n_sorted)
+          atomicAdd(a.unit_sum + (size_t)row * a.ucap + ureg[j], -unit_term(key_float(kreg[j]), unit_ref(um[jj])));
+        else
+          a.tail_logit[(size_t)row * a.tail_cap + (sreg[j] - n_sorted)] = kNegInf;
+      }
+    }
+  } else {
+    // all N keys: the keys are recomputed on every pass
+    if (!take_all) {
+      const int ties = block_radix_threshold<kRowThreads>(key, C, K, rsh, T, t);
+      if (ties != t) {
+        auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)i : 0u; };
+        int t2;
+        block_radix_threshold<kRowThreads>(tie_key, C, t, rsh, T2, t2);
+      }
+    }
+    for (int slot = tid; slot < C; slot += kRowThreads) {
+      const float x = logit_at(slot, lids[slot]);
+      const uint32_t k = float_key(x);
+      if (take_all || k > T || (k == T && ~(uint32_t)slot >= T2)) {
+        const int o = atomicAdd(&sh.emit_count, 1);
+        if (o < a.kcap) {
+          sel[o] = slot;
+          soff[o] = a.kv.offset(req, head, a.slot_pos[sb + slot]);
+          if (slot < n_sorted) {
+            const int u = a.slot_unit[sb + slot];
+            atomicAdd(a.unit_sum + (size_t)row * a.ucap + u, -unit_term(x, unit_ref(umax[u])));
+          } else {
+            a.tail_logit[(size_t)row * a.tail_cap + (slot - n_sorted)] = kNegInf;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    ri[PQHSA_RI_K] = K;
+    ri[PQHSA_RI_N] = N;
+    ri[PQHSA_RI_NCAND] = ncand;
+    ri[PQHSA_RI_NSEL] = sh.emit_count;
+    ri[PQHSA_RI_FALLBACK] = fallback ? 1 : 0;
+  }
+}
+
 int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t st) {
   char* ws = static_cast<char*>(p.workspace);
   const int R = p.num_streams * p.group;
@@ -563,10 +1001,8 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.unit_off = static_cast<const int32_t*>(p.unit_off);
   a.unit_list = static_cast<const uint16_t*>(p.unit_list);
   a.cand_key = reinterpret_cast<uint32_t*>(ws + w.cand_key);
-  a.cand_slot = reinterpret_cast<int32_t*>(ws + w.cand_slot);
-  a.cand_pos = reinterpret_cast<int32_t*>(ws + w.cand_pos);
-  a.cand_term = reinterpret_cast<float*>(ws + w.cand_term);
-  a.cand_unit = reinterpret_cast<uint16_t*>(ws + w.cand_unit);
+  a.cand_rec = reinterpret_cast<int4*>(ws + w.cand_rec);
+  a.cand_bin = reinterpret_cast<uint16_t*>(ws + w.cand_bin);
   a.part_hist = reinterpret_cast<uint32_t*>(ws + w.part_hist);
   a.part_cnt = reinterpret_cast<int32_t*>(ws + w.part_cnt);
   a.sel_slot = reinterpret_cast<int32_t*>(ws + w.sel_slot);
@@ -584,8 +1020,21 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.seg = w.seg;
   a.top_fraction = p.top_fraction;
   a.topk_fixed = p.topk_fixed;
-  const size_t smem_a = (size_t)w.seg * (sizeof(uint32_t) + sizeof(uint16_t));
+  a.wcap = w.parts <= 4 ? p.unit_capacity * (4 / w.parts) : ((p.unit_capacity + w.parts - 1) / w.parts) * 4;
+  const size_t smem_a = (size_t)a.wcap * (3 * sizeof(uint32_t) + sizeof(uint16_t));
   const size_t smem_b = (size_t)kBoundCap * 3 * sizeof(uint32_t);
+  if (w.parts == 1) {
+    a.wcap = (p.unit_capacity + 1) * (kUnit / 32);  // hit words of a row, rounded up to a thread's eight
+    a.wcap = (a.wcap + kRowWords - 1) / kRowWords * kRowWords;
+    const size_t smem = (size_t)a.wcap * (2 * sizeof(uint32_t) + 2 * sizeof(uint16_t)) + (size_t)kRowCandCap * sizeof(uint16_t);
+    PQHSA_DISPATCH_E(p.dtype, {
+      auto kern = row_select_kernel<E>;
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return check_launch("select: shared memory opt-in");
+      kern<<<R, kRowThreads, smem, st>>>(a);
+    });
+    return check_launch("select");
+  }
   const unsigned grid = (unsigned)(R * w.parts);
   PQHSA_DISPATCH_E(p.dtype, {
     auto ka = cand_kernel<E>;

@@ -207,6 +207,11 @@ class DeviceIndexPool:
             if idx.value_sums is not None and idx.value_counts is not None:
                 self.vsum[s, :lists] = idx.value_sums.to(dev).float()
                 self.vcnt[s, :lists] = idx.value_counts.to(dev).to(torch.int32)
+            else:
+                # running sums for later appends, rebuilt from the means and the list sizes
+                cnt = torch.bincount(ids, minlength=lists)[:lists]
+                self.vcnt[s, :lists] = cnt.to(torch.int32)
+                self.vsum[s, :lists] = idx.value_means.to(dev).float() * cnt.unsqueeze(-1).float()
             st[_lib.ST_N_SORTED], st[_lib.ST_N_UNITS], st[_lib.ST_N_LISTS] = n, u, lists
         self.state[s] = st.to(dev)
         self.h_sorted[s], self.h_tail[s], self.h_seq[s] = n, 0, seq_len
@@ -309,7 +314,7 @@ class DeviceIndexPool:
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def _prep(self, q: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
+    def _prep(self, q: torch.Tensor | None = None, out: torch.Tensor | None = None, mapped: bool = False) -> None:
         # grids are sized for the largest stream plus the growth a captured graph may see
         self.p.max_slots = min(int((self.h_sorted + self.h_tail).max()) + int(self.graph_headroom), self.cap)
         full = int((np.minimum(self.sink, self.h_seq) + np.maximum(
@@ -318,12 +323,13 @@ class DeviceIndexPool:
             raise RuntimeError(
                 f"{full} sink+local rows exceed max_full={self.max_full}: apply the pending index update "
                 "or build the pool with a larger max_full")
+        # with an io_map the streams pick their blocks of q / out themselves: the tensors may hold fewer blocks
         if q is not None:
-            if q.dtype != self.dtype or not q.is_contiguous() or q.numel() != self.S * self.G * _lib.HEAD_DIM:
+            if q.dtype != self.dtype or not q.is_contiguous() or (not mapped and q.numel() != self.S * self.G * _lib.HEAD_DIM):
                 raise ValueError(f"q must be a contiguous {self.dtype} tensor of {self.S}x{self.G}x128 elements")
             self.p.q = q.data_ptr()
         if out is not None:
-            if out.dtype != self.dtype or not out.is_contiguous() or out.numel() != self.S * self.G * _lib.HEAD_DIM:
+            if out.dtype != self.dtype or not out.is_contiguous() or (not mapped and out.numel() != self.S * self.G * _lib.HEAD_DIM):
                 raise ValueError("out must match q in dtype and size")
             self.p.out = out.data_ptr()
 
@@ -360,34 +366,60 @@ class DeviceIndexPool:
         return scores
 
     def decode_step_append(self, q: torch.Tensor, new_k: torch.Tensor | None, new_v: torch.Tensor | None,
-                           encode: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
-        """append_kv(new_k, new_v) + append_encode(encode) + decode_step(q) as one call of five
-        launches (the first kernel does the append, the encode and the tables side by side)."""
+                           encode: int = 0, out: torch.Tensor | None = None, external: bool = False) -> torch.Tensor:
+        """append_kv(new_k, new_v) + append_encode(encode) + decode_step(q) as one call of seven
+        launches (the first kernel does the append, the encode and the tables side by side).
+        ``external`` (with new_k None): the caller already stored this step's rows in the cache;
+        every live stream's length advances by one."""
         if (new_k is None) != (new_v is None):
             raise ValueError("new_k and new_v go together")
+        if external and new_k is not None:
+            raise ValueError("external=True goes with new_k=None")
+        encode = int(encode)
+        self.check_step(new_k is not None, external, encode)
+        if out is None:
+            out = torch.empty_like(q)
+        self.enqueue_step_append(q, new_k, new_v, None, encode, out, external)
+        self.note_step(new_k is not None, external, encode)
+        return out
+
+    def check_step(self, appended: bool, external: bool, encode: int) -> None:
+        """Host-side admission of a fused step that encodes ``encode`` keys per stream."""
+        if not encode:
+            return
+        if int((self.h_tail + encode).max()) > self.tail_capacity:
+            raise RuntimeError("tail capacity exhausted: compact() the pool first")
+        # the fused call encodes tokens that were in the cache before it (all of them with local_window == 0,
+        # where the library appends first): the host mirror must not run ahead of the device
+        room = self.h_seq - (np.minimum(self.sink, self.h_seq) + self.h_sorted + self.h_tail)
+        if (appended and self.local == 0) or external:
+            room = room + 1  # the new row is in the cache before the encode looks for it
+        if int((room - encode).min()) < 0:
+            raise ValueError("decode_step_append asked to index tokens that are not in the cache yet")
+
+    def enqueue_step_append(self, q: torch.Tensor, new_k, new_v, enc_count: torch.Tensor | None, uniform: int,
+                            out: torch.Tensor, external: bool, mapped: bool = False) -> None:
+        """The library call of :meth:`decode_step_append` and nothing else (no host bookkeeping): what a
+        CUDA-graph capture records.  ``enc_count``: device int32 [S] or None for ``uniform`` on every stream."""
         for t in (new_k, new_v):
             if t is not None and (t.dtype != self.dtype or not t.is_contiguous() or t.numel() != self.S * _lib.HEAD_DIM):
                 raise ValueError(f"new_k/new_v must be contiguous {self.dtype} tensors of {self.S}x128 elements")
-        encode = int(encode)
-        if encode:
-            if int((self.h_tail + encode).max()) > self.tail_capacity:
-                raise RuntimeError("tail capacity exhausted: compact() the pool first")
-            # the fused call encodes tokens that were in the cache before it (all of them with local_window == 0,
-            # where the library appends first): the host mirror must not run ahead of the device
-            room = self.h_seq - (np.minimum(self.sink, self.h_seq) + self.h_sorted + self.h_tail)
-            if new_k is not None and self.local == 0:
-                room = room + 1
-            if int((room - encode).min()) < 0:
-                raise ValueError("decode_step_append asked to index tokens that are not in the cache yet")
-            self.h_tail += encode
-        if new_k is not None:
-            self.h_seq += 1
-        if out is None:
-            out = torch.empty_like(q)
-        self._prep(q, out)
+        if enc_count is not None and (enc_count.dtype != torch.int32 or enc_count.numel() != self.S or not enc_count.is_cuda):
+            raise ValueError("enc_count must be a device int32 tensor with one entry per stream")
+        self.p.external_append = 1 if external else 0
+        self._prep(q, out, mapped)
         _lib.call("pqhsa_decode_step_append", C.byref(self.p), new_k.data_ptr() if new_k is not None else None,
-                  new_v.data_ptr() if new_v is not None else None, None, encode, self._stream())
-        return out
+                  new_v.data_ptr() if new_v is not None else None,
+                  enc_count.data_ptr() if enc_count is not None else None, int(uniform), self._stream())
+
+    def note_step(self, appended: bool, external: bool, encode: int) -> None:
+        """Advance the host mirrors by one fused step (the device counters advance by themselves)."""
+        if encode:
+            self.h_tail += int(encode)
+        if appended:
+            self.h_seq += 1
+        elif external:
+            self.h_seq[self.h_seq > 0] += 1
 
     def append_kv(self, new_k: torch.Tensor, new_v: torch.Tensor) -> None:
         """Write one K/V row per stream at its current length and advance it."""

@@ -38,6 +38,7 @@ class PoolAttention:
         self.deferred_pending = False
         self.paged = False
         self.index_adds = self.index_rebuilds = self.online_updates = 0
+        self.generation = 0                  # bumped whenever a device address the library sees changes
 
     # ---- regions (pq_hsa/attention/kv_cache.py:1160-1170) -------------------
     def bounds(self, length=None, indexed=None):
@@ -74,6 +75,7 @@ class PoolAttention:
         self.paged = False
         self._make_pool(keys.dtype, keys.device, cap)
         self.pool.bind_kv_contiguous(self.keys, self.values)
+        self.generation += 1
         self._rebuild_index()
 
     def _make_pool(self, dtype, device, token_capacity: int) -> None:
@@ -125,19 +127,73 @@ class PoolAttention:
                                 values.reshape(-1, _lib.HEAD_DIM).contiguous())
         else:
             self.pool.note_external_append(1)
-        self.length += 1
-        self.pending += 1
-        if self.pending >= self.acfg.index_update_interval:
-            if self.acfg.index_update_strategy == "deferred":
-                self.deferred_pending = True
-            else:
-                self._refresh_now()
+        self._after_append()
 
     def apply_pending_index_update(self) -> bool:
         if not self.deferred_pending:
             return False
         self._refresh_now()
         self.deferred_pending = False
+        return True
+
+    @torch.no_grad()
+    def apply_pending_incremental_flush(self) -> bool:
+        """The production form of the deferred update (benchmarks/e2e_pq_param_sweep.py:3021-3344 with
+        PQ_HSA_INCREMENTAL_FLUSH=1, its default): the keys that left the local window since the last update move
+        the coarse centroids and the code words by one EMA step, then ONLY those keys are assigned and encoded
+        against the moved codebooks - by the library's append-encode kernel, into the unsorted tail; old list ids
+        and codes stay - and the value means follow as running sums (the count-weighted merge of :3259-3281).
+        The EMA itself is a handful of tensor operations over the update batch (S x U x L distances)."""
+        if not self.deferred_pending:
+            return False
+        self.deferred_pending = False
+        s, old_r = self.bounds()
+        if old_r <= s:            # no index yet: build one
+            self._refresh_now()
+            return True
+        self.indexed_length = self.length
+        self.pending = 0
+        s, r = self.bounds()
+        new = r - old_r
+        if new <= 0:
+            return True
+        p = self.pool
+        if r - s > p.cap:
+            raise RuntimeError("index slot capacity exhausted: rebuild the cache with a larger margin")
+        if int(p.h_tail.max()) + new > p.tail_capacity:
+            p.compact()
+        if new > p.tail_capacity:
+            raise RuntimeError("the update batch exceeds the tail capacity: flush more often")
+        lr, eps = self.icfg.online_codebook_lr, self.icfg.eps
+        k, _ = self._kv_rows(old_r, r)                       # [B, H, U, D]
+        S, D = self.B * self.H, _lib.HEAD_DIM
+        kf = k.reshape(S, new, D).float()
+        nrm = torch.linalg.vector_norm(kf, dim=-1).to(k.dtype).float().clamp_min(eps)
+        uu = kf / nrm.unsqueeze(-1)
+        lists = int(p.state[0, _lib.ST_N_LISTS])
+        coarse = p.coarse[:, :lists].float()
+
+        def ema(cent, x):
+            ids = torch.cdist(x, cent, p=2).argmin(dim=-1)
+            sums = torch.zeros_like(cent)
+            sums.scatter_add_(1, ids.unsqueeze(-1).expand(-1, -1, x.shape[-1]), x)
+            cnt = torch.zeros(cent.shape[:2], dtype=torch.float32, device=x.device)
+            cnt.scatter_add_(1, ids, torch.ones_like(ids, dtype=torch.float32))
+            means = sums / cnt.unsqueeze(-1).clamp_min(eps)
+            return torch.where((cnt > 0).unsqueeze(-1), (1.0 - lr) * cent + lr * means, cent)
+
+        coarse = ema(coarse, uu).to(p.dtype)
+        p.coarse[:, :lists] = coarse
+        cf = coarse.float()
+        ids = torch.cdist(uu, cf, p=2).argmin(dim=-1)
+        ures = uu - torch.gather(cf, 1, ids.unsqueeze(-1).expand(-1, -1, D))
+        M, sub = _lib.SUBSPACES, D // _lib.SUBSPACES
+        books = p.codebooks.float()                          # [S, M, 16, sub]
+        chunks = ures.reshape(S, new, M, sub).permute(0, 2, 1, 3).reshape(S * M, new, sub)
+        books = ema(books.reshape(S * M, _lib.CODES, sub), chunks).reshape(S, M, _lib.CODES, sub)
+        p.codebooks.copy_(books.to(p.dtype))
+        p.append_encode(int(new))                            # assign + encode the batch, value sums and means
+        self.online_updates += 1
         return True
 
     def _grow(self) -> None:
@@ -148,6 +204,7 @@ class PoolAttention:
         nk[:, :, :cap], nv[:, :, :cap] = self.keys, self.values
         self.keys, self.values = nk, nv
         self.pool.bind_kv_contiguous(self.keys, self.values)
+        self.generation += 1
 
     def _refresh_now(self) -> None:
         strategy = self.acfg.index_update_strategy
@@ -203,6 +260,7 @@ class PoolAttention:
         self.paged = False
         self._make_pool(keys.dtype, keys.device, cap)
         self.pool.bind_kv_contiguous(self.keys, self.values)
+        self.generation += 1
         streams = att["streams"]
         if len(streams) != B * H:
             raise ValueError("stream state count does not match leading_shape")
@@ -229,6 +287,7 @@ class PoolAttention:
         self._paged = (kv_cache, block_table)
         self._make_pool(kv_cache.dtype, kv_cache.device, token_capacity)
         self.pool.bind_kv_paged(kv_cache, block_table)
+        self.generation += 1
         s, r = self.bounds()
         for b in range(self.B):
             idx = None
@@ -239,6 +298,120 @@ class PoolAttention:
                 self.pool.load_stream(b * self.H + h, None if idx is None else idx[h], seq_len=self.length, req=b,
                                       kv_head=h)
         self.index_rebuilds += 1
+
+    # ---- one decode step: append + index update + attention as ONE library call ---------------
+    def step_plan(self) -> tuple[int, bool]:
+        """Bookkeeping of :meth:`append` for a token that the next :meth:`step` call will carry: advances the
+        host counters and returns ``(encode, fused)`` - how many keys per stream the fused library call has
+        to encode, and whether the update can ride in that call at all (rebuild / online refreshes and a full
+        tail cannot: the caller then appends and refreshes with the separate calls first)."""
+        a = self.acfg
+        pending = self.pending + 1
+        if pending < a.index_update_interval or a.index_update_strategy == "deferred":
+            return 0, True
+        if a.index_update_strategy != "incremental":
+            return 0, False
+        s, old_r = self.bounds()
+        if old_r <= s:
+            return 0, False                      # no index yet: the refresh builds one
+        _, r = self.bounds(self.length + 1, self.length + 1)
+        new = r - old_r
+        if new <= 0:
+            return 0, True
+        if int(self.pool.h_tail.max()) + new > self.pool.tail_capacity:
+            return 0, False                      # the tail has to be folded into the sorted region first
+        return int(new), True
+
+    def step(self, queries: torch.Tensor, keys: torch.Tensor | None = None, values: torch.Tensor | None = None,
+             out: torch.Tensor | None = None, *, external_write: bool = False) -> torch.Tensor:
+        """``append(keys, values)`` followed by ``forward(queries)`` as one fused library call (token row
+        write, incremental encode of the keys that leave the local window, tables, scan, selection,
+        attention: seven launches), with the bookkeeping of :meth:`append`.  ``external_write``: the
+        caller's own cache write already stored the row (vLLM's pages), only the length advances."""
+        if self.pool is None:
+            raise RuntimeError("build_cache must be called first")
+        if keys is None and not external_write:
+            return self.forward(queries, out)
+        exp = (self.B, self.H * self.G, _lib.HEAD_DIM)
+        if tuple(queries.shape) != exp:
+            raise ValueError(f"queries must have shape {exp}, got {tuple(queries.shape)}")
+        encode, fused = self.step_plan()
+        if not fused or (keys is not None and not self.paged and self.length + 1 > self.keys.shape[2]):
+            if keys is None:
+                self.pool.note_external_append(1)
+                self._after_append()
+            else:
+                self.append(keys, values)
+            return self.forward(queries, out)
+        p = self.pool
+        if keys is not None:
+            exp_kv = (self.B, self.H, _lib.HEAD_DIM)
+            if tuple(keys.shape) != exp_kv or tuple(values.shape) != exp_kv:
+                raise ValueError(f"keys/values must have shape {exp_kv}, got {tuple(keys.shape)}")
+            nk = keys.reshape(-1, _lib.HEAD_DIM).contiguous()
+            nv = values.reshape(-1, _lib.HEAD_DIM).contiguous()
+            res = p.decode_step_append(queries.contiguous(), nk, nv, encode=encode, out=out)
+        else:
+            res = p.decode_step_append(queries.contiguous(), None, None, encode=encode, out=out, external=True)
+        self.note_fused_step(encode)
+        return res
+
+    def note_fused_step(self, encode: int) -> None:
+        """The host counters of append() / _refresh_now() after a fused step that encoded ``encode`` keys."""
+        self.length += 1
+        self.pending += 1
+        if self.pending >= self.acfg.index_update_interval:
+            if self.acfg.index_update_strategy == "deferred":
+                self.deferred_pending = True
+            else:
+                self.indexed_length = self.length
+                self.pending = 0
+                if encode:
+                    self.index_adds += 1
+
+    # ---- prefix checkpoint (benchmarks/e2e_pq_param_sweep.py:3358-3432, :3735-3899) ---------------------
+    _SNAP_SLOT = ("codes", "norms", "list_ids", "slot_pos", "slot_unit")
+    _SNAP_FULL = ("unit_off", "unit_list", "coarse", "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max",
+                  "sample", "sample_start")
+
+    def snapshot(self) -> dict:
+        """Device-side copy of everything the index holds (slot arrays up to the longest stream, tables,
+        counters) plus the host counters: what :meth:`restore_snapshot` needs to put the engine back without
+        rebuilding anything."""
+        if self.pool is None:
+            raise RuntimeError("build_cache must be called first")
+        p = self.pool
+        n = int((p.h_sorted + p.h_tail).max()) if p.S else 0
+        snap = {name: getattr(p, name)[:, :n].clone() for name in self._SNAP_SLOT}
+        snap.update({name: getattr(p, name).clone() for name in self._SNAP_FULL})
+        snap.update(n=n, h_sorted=p.h_sorted.copy(), h_tail=p.h_tail.copy(), h_seq=p.h_seq.copy(), length=self.length,
+                    indexed_length=self.indexed_length, pending=self.pending, deferred_pending=self.deferred_pending,
+                    shape=(self.B, self.H, p.cap, p.L))
+        return snap
+
+    def restore_snapshot(self, snap: dict) -> None:
+        """Inverse of :meth:`snapshot` on the same pool (same request count, heads and capacity).  The K/V
+        rows are not touched: tokens past the checkpoint simply stop counting."""
+        p = self.pool
+        if p is None or snap["shape"] != (self.B, self.H, p.cap, p.L):
+            raise ValueError("the checkpoint was taken from a different pool")
+        n = snap["n"]
+        for name in self._SNAP_SLOT:
+            getattr(p, name)[:, :n].copy_(snap[name])
+        for name in self._SNAP_FULL:
+            getattr(p, name).copy_(snap[name])
+        p.h_sorted[:], p.h_tail[:], p.h_seq[:] = snap["h_sorted"], snap["h_tail"], snap["h_seq"]
+        self.length, self.indexed_length = snap["length"], snap["indexed_length"]
+        self.pending, self.deferred_pending = snap["pending"], snap["deferred_pending"]
+
+    def _after_append(self) -> None:
+        self.length += 1
+        self.pending += 1
+        if self.pending >= self.acfg.index_update_interval:
+            if self.acfg.index_update_strategy == "deferred":
+                self.deferred_pending = True
+            else:
+                self._refresh_now()
 
     # ---- forward -------------------------------------------------------------------
     def forward(self, queries: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

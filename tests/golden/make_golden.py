@@ -11,7 +11,7 @@ guarded by a checksum, so a drifting generator fails the tests loudly instead of
 silently comparing different data.
 
 The fixtures pin the CPU oracle (tests/test_oracle_golden.py) and, through the
-stored index tensors, the CUDA path (tests/test_golden_gpu.py).  Nothing here is
+stored index tensors, the CUDA path (tests/test_pool_gpu.py, tests/test_adapters_gpu.py).  Nothing here is
 needed at test time except the .npz files.
 """
 
@@ -112,5 +112,38 @@ def main(ref_root: str) -> None:
         print(name, "indexed", idx.num_vectors, "bytes", (HERE / f"golden_{name}.npz").stat().st_size)
 
 
+def adapter_state(ref_root: str) -> None:
+    """``golden_adapter_state.pt``: a checkpoint written by the reference's own decode adapter
+    (``IVFPQDecodeAttentionAdapter.state_dict``, two heads, three appended tokens) with the queries it was then
+    asked and the contexts it answered - the wire format the B200 adapter must load and emit."""
+    sys.path.insert(0, ref_root)
+    from pq_hsa.attention.decode_adapter import IVFPQDecodeAttentionAdapter
+    from pq_hsa.attention.sparse_attention import SparseAttentionConfig
+    from pq_hsa.index.ivfpq import IVFPQConfig
+
+    dt = torch.bfloat16
+    kk, vv = workloads.mixture_kv(77, 2, 520, dtype=dt, components=16)
+    q = workloads.planted_queries(78, kk, 1).float()[None]            # [1, 2, 128]
+    ic = IVFPQConfig(num_lists=32, nprobe=64, num_subspaces=8, num_bits=4, residual=True, coarse_max_iter=1, pq_max_iter=2,
+                     pack_codes=True, topk_block_size=1024, kernel_backend="torch", rotation="none",
+                     direction_normalize=True, seed=0)
+    ac = SparseAttentionConfig(sink_tokens=4, local_window=128, retrieval_top_fraction=0.05, exact_rerank=True, mode="hybrid",
+                               hybrid_value_mode="centroid", hybrid_topk_source="all_pq", hybrid_denominator_source="all_pq",
+                               index_update_interval=1, index_update_strategy="incremental", collect_attention_details=False)
+    ad = IVFPQDecodeAttentionAdapter(ic, ac).build_cache(kk.float()[None], vv.float()[None])
+    g = torch.Generator().manual_seed(79)
+    for _ in range(3):
+        ad.append(torch.randn(1, 2, 128, generator=g).to(dt).float(), torch.randn(1, 2, 128, generator=g).to(dt).float())
+    out = ad.forward(q).context
+    state = ad.state_dict()
+    for st in state["attention"]["streams"]:
+        # the K/V rows hold bf16-representable values: stored as bf16 (lossless) to keep the fixture small;
+        # the test widens them to the float32 the reference wrote
+        st["keys"], st["values"] = st["keys"].to(dt), st["values"].to(dt)
+    torch.save({"state": state, "queries": q, "context": out}, HERE / "golden_adapter_state.pt")
+    print("adapter state bytes", (HERE / "golden_adapter_state.pt").stat().st_size)
+
+
 if __name__ == "__main__":
+    adapter_state(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])
     main(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])  # a checkout of the reference

@@ -231,3 +231,170 @@ def test_deferred_fixture_of_the_reference_through_the_engine():
     np.testing.assert_allclose(e.coarse_centroids.float().cpu().numpy(), g["coarse_end"], rtol=0, atol=2e-6)
     np.testing.assert_allclose(e.codebooks.float().cpu().numpy(), g["codebooks_end"], rtol=0, atol=2e-6)
     np.testing.assert_allclose(e.key_norms.float().cpu().numpy(), g["key_norms_end"], rtol=1e-6)
+
+
+@pytest.mark.parametrize("strategy, interval", [("incremental", 1), ("deferred", 4)])
+def test_sidecar_fast_path_replays_a_validated_cuda_graph(strategy, interval):
+    """lean_append + forward = one fused library call; with the graph on it is captured on the first step,
+    validates itself (NaN poison, replay, compare with the eager call: benchmarks/e2e_pq_param_sweep.py:6170-6201)
+    and is replayed from then on.  Graph and eager sidecars must agree step for step and follow the oracle,
+    also across a deferred flush and for two requests that advance together."""
+    from pqhsa_release_b200 import GQASidecar
+
+    dtype, B, Hkv, G, S = torch.bfloat16, 2, 2, 4, 5300
+    k, v, q = _inputs(B, Hkv, S, G=G, dtype=dtype, seed=6)
+    ic = paper_index_config(num_lists=64)
+    ac = paper_attention_config(retrieval_top_fraction=0.03, index_update_interval=interval, index_update_strategy=strategy)
+    fast = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv, cuda_graph=True).build_cache(k.cuda(), v.cuda())
+    slow = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv, cuda_graph=False).build_cache(k.cuda(), v.cuda())
+    assert not fast.cuda_graph_active and fast.batched_heads_active
+    gen = torch.Generator().manual_seed(4)
+    for step in range(10):
+        nk = (k[:, :, 13 * step + 7].float() + 0.3 * torch.randn(B, Hkv, 128, generator=gen)).to(dtype).cuda()
+        nv = torch.randn(B, Hkv, 128, generator=gen).to(dtype).cuda()
+        qq = (q.float() + 0.02 * step).to(dtype).cuda()
+        assert fast.lean_append(nk, nv, qq) and slow.lean_append(nk, nv, qq)
+        a = fast.forward(qq).clone()
+        b = slow.forward(qq)
+        torch.cuda.synchronize()
+        assert fast.cuda_graph_active and not slow.cuda_graph_active
+        assert fast.length == slow.length == S + step + 1 and fast.engine.length == slow.engine.length
+        assert float((a.float() - b.float()).abs().max()) <= 1e-2 * float(b.float().abs().max()), f"step {step}"
+        assert torch.equal(fast.engine.pool.state, slow.engine.pool.state)
+        if strategy == "deferred" and step == 5:
+            assert fast.apply_pending_index_update() == B * Hkv and slow.apply_pending_index_update() == B * Hkv
+        if step in (0, 6, 9):
+            out = a.float().cpu()
+            for s in range(B * Hkv):
+                st = _oracle_of(fast.engine, s, 0.03, interval, strategy)
+                b_, h_ = divmod(s, Hkv)
+                det = st.forward_detail(qq[b_, h_ * G : (h_ + 1) * G].float().cpu())
+                for g in range(G):
+                    assert_output_close(out[b_, h_ * G + g], det.output[g], dtype, f"step {step} stream {s} row {g}")
+    assert fast._step_graph.attempts == 1, "the first capture must validate"
+
+
+def test_prefix_checkpoint_restores_the_index_without_a_rebuild():
+    """checkpoint_prefix / restore_prefix (benchmarks/e2e_pq_param_sweep.py:3358-3432, :3735-3899): after decoding past
+    the prompt the sidecar goes back to the checkpointed prefix - same index, same counters, same output as right
+    after the build - and decodes again as if freshly built."""
+    from pqhsa_release_b200 import GQASidecar
+
+    dtype, Hkv, G, S = torch.bfloat16, 2, 4, 4800
+    k, v, q = _inputs(1, Hkv, S, G=G, dtype=dtype, seed=8)
+    ic = paper_index_config(num_lists=64)
+    ac = paper_attention_config(retrieval_top_fraction=0.03, index_update_interval=1, index_update_strategy="incremental")
+    side = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv).build_cache(k.cuda(), v.cuda())
+    assert side.prefix_checkpoint_length is None and not side.restore_prefix()
+    first = side.forward(q.cuda()).clone()
+    side.checkpoint_prefix()
+    assert side.prefix_checkpoint_length == S
+    state0 = side.engine.pool.state.clone()
+    gen = torch.Generator().manual_seed(3)
+    rows = [(torch.randn(1, Hkv, 128, generator=gen).to(dtype).cuda(), torch.randn(1, Hkv, 128, generator=gen).to(dtype).cuda())
+            for _ in range(6)]
+    outs = []
+    for nk, nv in rows:
+        side.lean_append(nk, nv)
+        outs.append(side.forward(q.cuda()).clone())
+    rebuilds = side.engine.index_rebuilds
+    assert side.length == S + 6 and side.restore_prefix()
+    assert side.length == S and side.engine.length == S and side.engine.index_rebuilds == rebuilds
+    assert torch.equal(side.engine.pool.state, state0)
+    again = side.forward(q.cuda())
+    assert float((again.float() - first.float()).abs().max()) <= 1e-2 * float(first.float().abs().max())
+    for (nk, nv), want in zip(rows, outs):   # the same continuation gives the same outputs
+        side.lean_append(nk, nv)
+        got = side.forward(q.cuda())
+        assert float((got.float() - want.float()).abs().max()) <= 1e-2 * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_incremental_deferred_flush_follows_the_production_update(dtype):
+    """The sidecar's deferred flush (PQ_HSA_INCREMENTAL_FLUSH=1: EMA of centroids and code words on the keys that
+    left the local window, only those keys encoded, count-weighted value means -
+    benchmarks/e2e_pq_param_sweep.py:3021-3344) against the CPU restatement of those lines: moved codebooks to
+    rounding, list ids and codes of the new keys bit for bit (a differing assignment must be a rare tie), old
+    entries untouched, value means and the attention output to tolerance."""
+    from helpers import round_to
+    from pqhsa_release_b200 import GQASidecar
+
+    Hkv, G, S, L = 2, 2, 3000, 48
+    k, v, q = _inputs(1, Hkv, S, G=G, dtype=dtype, seed=12)
+    ic = paper_index_config(num_lists=L)
+    ac = paper_attention_config(retrieval_top_fraction=0.03, index_update_interval=8, index_update_strategy="deferred")
+    side = GQASidecar(ic, ac, num_query_heads=Hkv * G, num_kv_heads=Hkv, cuda_graph=False).build_cache(k.cuda(), v.cuda())
+    oracles = [_oracle_of(side.engine, s, 0.03, 8, "deferred") for s in range(Hkv)]
+    before = [side.engine.pool.export_stream(s) for s in range(Hkv)]
+    gen = torch.Generator().manual_seed(5)
+    for step in range(11):
+        nk = (k[:, :, 17 * step + 3].float() + 0.4 * torch.randn(1, Hkv, 128, generator=gen)).to(dtype)
+        nv = torch.randn(1, Hkv, 128, generator=gen).to(dtype)
+        side.lean_append(nk.cuda(), nv.cuda())
+        side.forward(q.cuda())
+        for s, st in enumerate(oracles):
+            st.append(nk[0, s].float(), nv[0, s].float())
+    assert side.apply_pending_index_update() == Hkv and side.apply_pending_index_update() == 0
+    out = side.forward(q.cuda()).float().cpu()
+    mism = total = 0
+    for s, st in enumerate(oracles):
+        assert st.apply_pending_incremental_flush()
+        e = side.engine.pool.export_stream_state(s)
+        n_old, n_new = before[s]["list_ids"].numel(), 11
+        assert e.list_ids.numel() == st.index.num_vectors == n_old + n_new
+        tol = 2e-6 if dtype == torch.float32 else 1e-2
+        assert float((e.coarse_centroids.float().cpu() - st.index.coarse).abs().max()) <= tol
+        assert float((e.codebooks.float().cpu() - st.index.codebooks).abs().max()) <= tol
+        # old entries stay as they were
+        assert torch.equal(e.list_ids[:n_old].cpu(), before[s]["list_ids"].cpu())
+        assert torch.equal(e.packed_codes[:n_old].cpu(), before[s]["packed_codes"].cpu())
+        same = (e.list_ids[n_old:].cpu() == st.index.list_ids[n_old:]) & (
+            e.packed_codes[n_old:].cpu() == st.index.packed[n_old:]).all(dim=1)
+        total += n_new
+        mism += int((~same).sum())
+        if dtype == torch.float32 and bool(same.all()):
+            assert float((e.value_means.float().cpu() - st.value_means).abs().max()) <= 1e-5
+            st.index.coarse, st.index.codebooks = e.coarse_centroids.float().cpu(), e.codebooks.float().cpu()
+            st.index.norms = round_to(st.index.norms, dtype)
+            det = st.forward_detail(q[0, s * G : (s + 1) * G].float())
+            for g in range(G):
+                assert_output_close(out[0, s * G + g], det.output[g], dtype, f"stream {s} row {g} after the flush")
+    assert mism <= (1 if dtype == torch.float32 else 3), f"{mism} of {total} new keys differ from the restatement"
+
+
+def test_reference_adapter_checkpoint_loads_and_round_trips():
+    """A checkpoint written by the reference's own IVFPQDecodeAttentionAdapter.state_dict
+    (tests/golden/golden_adapter_state.pt, made by tests/golden/make_golden.py) loads here without a rebuild and
+    answers the stored queries as the reference did; what this adapter writes has the same layout, field for field,
+    holds the same index, and loads again."""
+    from pathlib import Path
+
+    from pqhsa_release_b200 import IVFPQDecodeAttentionAdapter
+
+    d = torch.load(Path(__file__).resolve().parent / "golden" / "golden_adapter_state.pt")
+    state, q, want = d["state"], d["queries"], d["context"]
+    for st in state["attention"]["streams"]:
+        st["keys"], st["values"] = st["keys"].float(), st["values"].float()
+    ad = IVFPQDecodeAttentionAdapter.from_state_dict(state)
+    assert ad.leading_shape == (1, 2) and ad.attention.length == 523 and ad.attention.index_rebuilds == 0
+    out = ad.forward(q.cuda()).context.cpu()
+    for h in range(2):
+        assert_output_close(out[0, h], want[0, h], torch.float32, f"head {h}")
+    mine, ref = ad.state_dict()["attention"], state["attention"]
+    assert list(mine) == list(ref) and mine["leading_shape"] == ref["leading_shape"] and mine["key_dim"] == 128
+    for a, b in zip(mine["streams"], ref["streams"]):
+        assert list(a) == list(b) and list(a["metadata"]) == list(b["metadata"]) and list(a["index"]) == list(b["index"])
+        assert a["metadata"]["indexed_length"] == b["metadata"]["indexed_length"] == 523
+        for name in ("coarse_centroids", "packed_codes", "pq_codebooks", "key_norms"):
+            assert a["index"][name].dtype == b["index"][name].dtype, name
+            assert torch.equal(a["index"][name].cpu(), b["index"][name]), name
+        assert a["index"]["list_ids"].dtype == torch.uint16
+        assert torch.equal(a["index"]["list_ids"].cpu().to(torch.int64), b["index"]["list_ids"].to(torch.int64))
+        assert torch.equal(a["keys"].cpu(), b["keys"]) and torch.equal(a["values"].cpu(), b["values"])
+        assert torch.allclose(a["retrieval_value_centroids"].cpu(), b["retrieval_value_centroids"], atol=1e-6)
+        assert torch.allclose(a["retrieval_value_sums"].cpu(), b["retrieval_value_sums"], atol=1e-4)
+    again = IVFPQDecodeAttentionAdapter.from_state_dict(ad.state_dict())
+    out2 = again.forward(q.cuda()).context.cpu()
+    assert float((out2 - out).abs().max()) <= 1e-5 * float(out.abs().max())
+    with pytest.raises(ValueError):
+        IVFPQDecodeAttentionAdapter(paper_index_config(num_lists=16), paper_attention_config()).load_state_dict(state)

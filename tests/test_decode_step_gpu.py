@@ -63,6 +63,17 @@ def test_batch_of_requests_and_group2():
     _check_case(case, pool)
 
 
+def test_many_query_rows_select_with_one_cta_per_row():
+    # 96 query rows and more: the selection of a row stays in one CTA (fewer rows split it over several)
+    case = make_case(B=6, Hkv=4, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
+    pool, _, _ = pool_from_case(case)
+    assert pool.layout.parts == 1
+    info = _check_case(case, pool)
+    assert int(info[:, 4].sum()) == 0
+    small = make_case(B=1, Hkv=2, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
+    assert pool_from_case(small)[0].layout.parts > 1
+
+
 def test_config0_like_fp32_single_head():
     case = make_case(B=1, Hkv=1, G=1, S=4096, L=128, dtype=torch.float32, seed=0, kind="config0")
     pool, _, _ = pool_from_case(case)

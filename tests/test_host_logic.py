@@ -164,11 +164,30 @@ def test_admission_rules_of_the_decode_runtime(monkeypatch):
     assert not runtime.should_pq_decode(NS(**{**md.__dict__, "max_query_len": 7}))
     assert not runtime.should_pq_decode(NS(**{**md.__dict__, "max_seq_len": 100}))
     assert not runtime.should_pq_decode(NS(**{**md.__dict__, "use_cascade": True}))
-    two = NS(**{**md.__dict__, "seq_lens": torch.tensor([5000, 6000]), "num_actual_tokens": 2})
+    two = NS(**{**md.__dict__, "seq_lens": torch.tensor([5000, 6000]), "num_actual_tokens": 2,
+                "seq_lens_cpu": torch.tensor([5000, 6000])})
     assert not runtime.should_pq_decode(two)
     monkeypatch.setenv("PQ_HSA_BATCH", "1")
+    assert not runtime.should_pq_decode(two) and runtime.rejects()["no_req_ids"] == 1   # slots alone do not tell requests apart
+    runner = NS(input_batch=NS(req_ids=["a", "b"]), requests={})
+    two._pq_runner = runner
     assert runtime.should_pq_decode(two)
-    assert runtime.rejects()["seq_too_short"] >= 1
+    assert runtime.batch_req_keys(two, 2) == ["a", "b"] and runtime.batch_seq_lens(two) == [5000, 6000]
+    short = NS(**{**two.__dict__, "seq_lens_cpu": torch.tensor([5000, 100]), "_pq_batch_seq_lens": None})
+    assert not runtime.should_pq_decode(short)
+    assert runtime.rejects()["seq_too_short"] >= 2
+    # the metadata builder wrap hands the runner to the metadata (pq_hsa_decode_runtime.py:874-902)
+    class Builder:
+        def build(self, *a, **k):
+            return NS(max_query_len=1)
+
+    Builder.runner = runner
+    assert runtime.attach_runner(Builder) == {"attached": True, "already": False}
+    assert Builder().build()._pq_runner is runner and runtime.attach_runner(Builder)["already"]
+    # prefix keys: (context length, digest of the prompt ids)
+    runner.requests = {"a": NS(prompt_token_ids=[1, 2, 3]), "b": NS(prompt_token_ids=None)}
+    keys = runtime.prefix_keys(two, [5000, 6000])
+    assert keys[0][0] == 4999 and len(keys[0][1]) == 16 and keys[1] is None
 
 
 def test_kv_head_sharding_and_gather_over_two_gloo_ranks(tmp_path):
@@ -195,3 +214,22 @@ def test_kv_head_sharding_and_gather_over_two_gloo_ranks(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29731", str(script)],
                          env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_reference_checkpoint_layout_is_understood_on_the_host():
+    """The reference adapter's state_dict (a fixture written by the reference itself) parses into what the engine
+    restores from: stacked K/V, the shared counters, one index per stream.  No GPU needed for the parsing."""
+    from pathlib import Path
+
+    from pqhsa_release_b200.decode_adapter import reference_attention_state
+
+    d = torch.load(Path(__file__).resolve().parent / "golden" / "golden_adapter_state.pt")
+    att = d["state"]["attention"]
+    r = reference_attention_state(att, device="cpu")
+    assert tuple(r["keys"].shape) == (1, 2, 523, 128) and r["indexed_length"] == 523 and r["pending"] == 0
+    ix = r["streams"][0]
+    assert ix.list_ids.dtype == torch.int64 and ix.packed_codes.dtype == torch.uint8 and ix.list_ids.numel() == 391
+    assert int(ix.value_counts.sum()) == 391
+    bad = dict(att, leading_shape=(2, 2))
+    with pytest.raises(ValueError):
+        reference_attention_state(bad, device="cpu")
