@@ -668,19 +668,24 @@ __global__ void __launch_bounds__(kSelThreads, 4) emit_kernel(const SelectArgs a
 // ---- one CTA per query row --------------------------------------------------------------------------
 // With many query rows (R >= 96) a row's selection stays in one CTA of 1024 threads; the GPU is full with one CTA per
 // row, and nothing is written to or read back from global memory in between.
-//   1. Word table: a thread takes 8 consecutive hit words (two 16-byte loads) with their first slot and list, and the
-//      table in shared memory says for every word how many candidates are listed before it.
-//   2. Candidate i belongs to the last word whose offset does not exceed i: the words write their index at their offset
-//      into an array over the candidates and a prefix maximum carries it forward - every candidate finds its word with
-//      one load, and the threads get even shares (i = tid, tid + 1024, ...) whatever the bits look like.
-//   3. The candidates are scored again (bit-identical to the scan), at most 8 per thread in registers; a block radix
-//      select over the register-resident keys finds the K-th largest (ties to the lower slot); the CTA emits.
+//   1. A thread takes 8 consecutive hit words (two 16-byte loads) and a block prefix sum says how many candidates are
+//      listed before each word.
+//   2. Candidate i belongs to the last non-empty word whose offset does not exceed i: such a word writes (its index,
+//      its offset) at its offset into an array over the candidates and a prefix maximum carries the pair forward.
+//      Every candidate finds its word, and its rank inside the word, with one shared-memory load, and the threads get
+//      even shares (i = tid, tid + 1024, ...) whatever the bits look like.  The array is all the shared memory the
+//      kernel needs (32 KB, whatever the context length); the word's bits, first slot and list come back out of L2.
+//   3. The candidates are scored again (bit-identical to the scan), at most 8 per thread in registers, with the token
+//      position each one would be gathered from; a block radix select over the register-resident keys finds the K-th
+//      largest (ties to the lower slot); the CTA emits.
 // More than 8192 candidates, or fewer than K (the threshold estimate failed): the same select over all N slots with the
 // keys recomputed on every pass - slow, exact, flagged.
 constexpr int kRowThreads = 1024;
 constexpr int kRowPer = 8;                          // candidates per thread held in registers
 constexpr int kRowCandCap = kRowThreads * kRowPer;  // more candidates than that select from all keys
 constexpr int kRowWords = 8;                        // consecutive hit words per thread and round
+constexpr int kRowIdxBits = 13;                     // bits of a candidate index (kRowCandCap = 1 << 13)
+static_assert(kRowCandCap == 1 << kRowIdxBits, "candidate index bits");
 
 struct RowShared {
   float lut[kM * kC];
@@ -691,12 +696,8 @@ struct RowShared {
 
 template <typename E>
 __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArgs a) {
-  extern __shared__ __align__(16) unsigned char sel_smem[];
-  uint32_t* wbits = reinterpret_cast<uint32_t*>(sel_smem);              // [wcap] bits of a hit word
-  int32_t* wfirst = reinterpret_cast<int32_t*>(wbits + a.wcap);         // [wcap] slot of its bit 0
-  uint16_t* woff = reinterpret_cast<uint16_t*>(wfirst + a.wcap);        // [wcap] candidates listed before it
-  uint16_t* wlist = woff + a.wcap;                                      // [wcap] its list (0xFFFF: tail, per slot)
-  uint16_t* owner = wlist + a.wcap;                                     // [kRowCandCap] candidate -> word + 1
+  // candidate -> (word + 1) << 13 | offset of the word's first candidate
+  __shared__ __align__(16) uint32_t owner[kRowCandCap];
   __shared__ RowShared sh;
   __shared__ RadixShared rsh;
   __shared__ RadixShared2 rsh2;
@@ -721,6 +722,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   const uint32_t* codes = a.codes + (size_t)s * a.cap;
   const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
   const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+  const int32_t* spos = a.slot_pos + (size_t)s * a.cap;
   const int32_t* uoff = a.unit_off + (size_t)s * (a.ucap + 1);
   const uint16_t* ulist = a.unit_list + (size_t)s * a.ucap;
   const float* umax = a.unit_max + (size_t)row * a.ucap;
@@ -728,16 +730,16 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   if (tid < kM * kC) sh.lut[tid] = a.lut[(size_t)row * kM * kC + tid];
   if (tid < kLMax) sh.lsc[tid] = a.list_scores[(size_t)row * kLMax + tid];
   if (tid == 0) sh.emit_count = 0;
+#pragma unroll
+  for (int j = 0; j < kRowPer / 4; ++j) reinterpret_cast<uint4*>(owner)[j * kRowThreads + tid] = make_uint4(0u, 0u, 0u, 0u);
 
-  // ---- 1. the word table ----
+  // ---- 1. candidates before every hit word ----
   const uint32_t* hm = a.hitmap + (size_t)row * a.ucap * (kUnit / 32);
-  const int nw = min((n_units + (n_tail + kUnit - 1) / kUnit) * (kUnit / 32), a.wcap);
-  int C = 0;  // candidates so far (all rounds); only counted once the list is known to overflow
+  const int nw = (n_units + (n_tail + kUnit - 1) / kUnit) * (kUnit / 32);
+  int C = 0;  // candidates so far (all rounds)
   for (int k0 = 0; k0 < nw; k0 += kRowWords * kRowThreads) {
-    const int kb = k0 + tid * kRowWords;  // this thread's words kb .. kb + 7: units kb / 4 and kb / 4 + 1
+    const int kb = k0 + tid * kRowWords;  // this thread's words kb .. kb + 7
     uint32_t b[kRowWords];
-    int first[2];
-    uint32_t l[2];
 #pragma unroll
     for (int j = 0; j < kRowWords; ++j) b[j] = 0u;
     if (kb < nw) {  // the hit map of a row is a whole number of 16-byte word quadruples
@@ -746,20 +748,6 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
       if (kb + 4 < nw) {
         const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(hm + kb + 4));
         b[4] = q1.x; b[5] = q1.y; b[6] = q1.z; b[7] = q1.w;
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int u = (kb >> 2) + h;
-      first[h] = 0;
-      l[h] = 0xFFFFu;
-      if (kb + 4 * h < nw) {
-        if (u < n_units) {
-          first[h] = uoff[u];
-          l[h] = ulist[u];
-        } else {
-          first[h] = n_sorted + (u - n_units) * kUnit;
-        }
       }
     }
     int mine = 0;
@@ -771,66 +759,57 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
       const int v = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += v;
     }
-    __syncthreads();  // wtot of the previous round has been read (and, first round, the tables are being loaded)
+    __syncthreads();  // the previous round's totals have been read; first round: the array is clear
     if (lane == 31) sh.wtot[warp] = incl;
     __syncthreads();
-    int before = 0, total = 0;
+    int wt = sh.wtot[lane];  // 32 warps: every warp scans the 32 totals
 #pragma unroll
-    for (int w = 0; w < kRowThreads / 32; ++w) {
-      const int v = sh.wtot[w];
-      before += w < warp ? v : 0;
-      total += v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, wt, o);
+      if (lane >= o) wt += v;
     }
+    const int total = __shfl_sync(0xffffffffu, wt, 31);
+    const int before = __shfl_sync(0xffffffffu, wt, warp) - __shfl_sync(0xffffffffu, incl, 31);
     int o = C + before + incl - mine;
-    if (C + total <= kRowCandCap) {  // block-uniform
 #pragma unroll
-      for (int j = 0; j < kRowWords; ++j) {
-        const int k = kb + j;
-        if (k < nw) {
-          wbits[k] = b[j];
-          wfirst[k] = first[j >> 2] + (j & 3) * 32;
-          woff[k] = (uint16_t)o;
-          wlist[k] = (uint16_t)l[j >> 2];
-        }
-        o += __popc(b[j]);
-      }
+    for (int j = 0; j < kRowWords; ++j) {
+      if (b[j] != 0u && o < kRowCandCap) owner[o] = ((uint32_t)(kb + j + 1) << kRowIdxBits) | (uint32_t)o;
+      o += __popc(b[j]);
     }
     C += total;
   }
   const int ncand = C;
-  const bool fallback = C < K || C > kRowCandCap;
+  const bool fallback = C < K || C > kRowCandCap || nw >= (1 << (32 - kRowIdxBits)) - 1;
   if (fallback) C = N;
-  // ---- 2. candidate -> word ----
+  // ---- 2. candidate -> word: prefix maximum, a warp over a contiguous stretch of the array ----
   if (!fallback) {
     __syncthreads();
-    for (int i = tid; i < C; i += kRowThreads) owner[i] = 0;
-    __syncthreads();
-    for (int k = tid; k < nw; k += kRowThreads)
-      if (wbits[k] != 0u) owner[woff[k]] = (uint16_t)(k + 1);
-    __syncthreads();
-    // prefix maximum: a thread takes `per` consecutive candidates, then the warps and the block are scanned
-    const int per = (C + kRowThreads - 1) / kRowThreads;  // <= kRowPer
-    const int i0 = tid * per;
-    uint32_t run = 0;
-    for (int j = 0; j < per; ++j)
-      if (i0 + j < C) run = max(run, (uint32_t)owner[i0 + j]);
-    uint32_t incl = run;
+    const int per = (C + kRowThreads - 1) / kRowThreads;  // <= kRowPer rounds of 32 per warp
+    const int base = warp * per * 32;
+    uint32_t v[kRowPer];
+    uint32_t carry = 0u;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl = max(incl, v);
-    }
-    if (lane == 31) sh.wtot[warp] = (int)incl;
-    __syncthreads();
-    uint32_t before = 0;
-    for (int w = 0; w < warp; ++w) before = max(before, (uint32_t)sh.wtot[w]);
-    uint32_t carry = max(before, __shfl_up_sync(0xffffffffu, incl, 1));
-    if (lane == 0) carry = before;
-    for (int j = 0; j < per; ++j)
-      if (i0 + j < C) {
-        carry = max(carry, (uint32_t)owner[i0 + j]);
-        owner[i0 + j] = (uint16_t)carry;
+    for (int j = 0; j < kRowPer; ++j) {
+      v[j] = 0u;
+      if (j >= per) continue;  // block-uniform
+      uint32_t x = owner[base + j * 32 + lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x = max(x, y);
       }
+      x = max(x, carry);
+      carry = __shfl_sync(0xffffffffu, x, 31);
+      v[j] = x;
+    }
+    if (lane == 0) sh.wtot[warp] = (int)carry;
+    __syncthreads();
+    const uint32_t prev = __reduce_max_sync(0xffffffffu, lane < warp ? (uint32_t)sh.wtot[lane] : 0u);
+#pragma unroll
+    for (int j = 0; j < kRowPer; ++j) {
+      if (j >= per) continue;  // block-uniform
+      owner[base + j * 32 + lane] = max(v[j], prev);
+    }
   }
   __syncthreads();
 
@@ -842,11 +821,20 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
       unit = 0;
       return;
     }
-    const int w = (int)owner[i] - 1;
-    slot = wfirst[w] + nth_set_bit(wbits[w], i - (int)woff[w]);
-    list = wlist[w];
-    if (list == 0xFFFF) list = lids[slot];
+    const uint32_t ow = owner[i];
+    const int w = (int)(ow >> kRowIdxBits) - 1, rank = i - (int)(ow & (kRowCandCap - 1));
     unit = w >> 2;
+    const uint32_t bits = __ldg(hm + w);
+    int first;
+    list = -1;
+    if (unit < n_units) {
+      first = __ldg(uoff + unit);
+      list = __ldg(ulist + unit);
+    } else {
+      first = n_sorted + (unit - n_units) * kUnit;
+    }
+    slot = first + (w & 3) * 32 + nth_set_bit(bits, rank);
+    if (list < 0) list = lids[slot];  // a tail slot carries its own list
   };
   auto logit_at = [&](int slot, int list) -> float {
     return finish_logit(pq_sum_row(sh.lut, __ldg(codes + slot)), sh.lsc[list], to_f(norms[slot]));
@@ -870,7 +858,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   if (!fallback) {
     // ---- 3. the candidates sit in registers, kRowPer per thread; their gathers travel four at a time ----
     uint32_t kreg[kRowPer];
-    int sreg[kRowPer], ureg[kRowPer];
+    int sreg[kRowPer], preg[kRowPer];
 #pragma unroll
     for (int j0 = 0; j0 < kRowPer; j0 += 4) {
       uint32_t code[4];
@@ -881,15 +869,17 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         const int j = j0 + jj, i = j * kRowThreads + tid;
         kreg[j] = 0u;
         sreg[j] = -1;
-        ureg[j] = 0;
+        preg[j] = 0;
         code[jj] = 0u;
         list[jj] = 0;
         kn[jj] = 0.f;
         if (j * kRowThreads >= C) continue;  // block-uniform: slots past the list cost nothing
         if (i < C) {
-          locate(i, sreg[j], list[jj], ureg[j]);
+          int unit;
+          locate(i, sreg[j], list[jj], unit);
           code[jj] = __ldg(codes + sreg[j]);
           kn[jj] = to_f(norms[sreg[j]]);
+          preg[j] = __ldg(spos + sreg[j]);
         }
       }
 #pragma unroll
@@ -912,13 +902,13 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
     // exp-sum loses exactly the term the scan added (a tail slot's stored logit becomes -inf).
 #pragma unroll
     for (int j0 = 0; j0 < kRowPer; j0 += 4) {
-      int o[4], pos[4];
+      int o[4], un[4];
       float um[4];
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const int j = j0 + jj;
         o[jj] = -1;
-        pos[jj] = 0;
+        un[jj] = 0;
         um[jj] = 0.f;
         if (j * kRowThreads >= C) continue;  // block-uniform
         const uint32_t k = kreg[j];
@@ -928,9 +918,9 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         if (m != 0u && lane == 0) base = atomicAdd(&sh.emit_count, __popc(m));
         base = __shfl_sync(0xffffffffu, base, 0) + __popc(m & ((1u << lane) - 1u));
         o[jj] = take && base < a.kcap ? base : -1;
-        if (o[jj] >= 0) {
-          pos[jj] = a.slot_pos[sb + sreg[j]];
-          if (sreg[j] < n_sorted) um[jj] = umax[ureg[j]];
+        if (o[jj] >= 0 && sreg[j] < n_sorted) {
+          un[jj] = ((int)(owner[j * kRowThreads + tid] >> kRowIdxBits) - 1) >> 2;
+          um[jj] = umax[un[jj]];
         }
       }
 #pragma unroll
@@ -938,9 +928,9 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         const int j = j0 + jj;
         if (o[jj] < 0) continue;
         sel[o[jj]] = sreg[j];
-        soff[o[jj]] = a.kv.offset(req, head, pos[jj]);
+        soff[o[jj]] = a.kv.offset(req, head, preg[j]);
         if (sreg[j] < n_sorted)
-          atomicAdd(a.unit_sum + (size_t)row * a.ucap + ureg[j], -unit_term(key_float(kreg[j]), unit_ref(um[jj])));
+          atomicAdd(a.unit_sum + (size_t)row * a.ucap + un[jj], -unit_term(key_float(kreg[j]), unit_ref(um[jj])));
         else
           a.tail_logit[(size_t)row * a.tail_cap + (sreg[j] - n_sorted)] = kNegInf;
       }
@@ -1024,15 +1014,7 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   const size_t smem_a = (size_t)a.wcap * (3 * sizeof(uint32_t) + sizeof(uint16_t));
   const size_t smem_b = (size_t)kBoundCap * 3 * sizeof(uint32_t);
   if (w.parts == 1) {
-    a.wcap = (p.unit_capacity + 1) * (kUnit / 32);  // hit words of a row, rounded up to a thread's eight
-    a.wcap = (a.wcap + kRowWords - 1) / kRowWords * kRowWords;
-    const size_t smem = (size_t)a.wcap * (2 * sizeof(uint32_t) + 2 * sizeof(uint16_t)) + (size_t)kRowCandCap * sizeof(uint16_t);
-    PQHSA_DISPATCH_E(p.dtype, {
-      auto kern = row_select_kernel<E>;
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return check_launch("select: shared memory opt-in");
-      kern<<<R, kRowThreads, smem, st>>>(a);
-    });
+    PQHSA_DISPATCH_E(p.dtype, { row_select_kernel<E><<<R, kRowThreads, 0, st>>>(a); });
     return check_launch("select");
   }
   const unsigned grid = (unsigned)(R * w.parts);
