@@ -208,6 +208,8 @@ enum pqhsa_row_info_slot {
   PQHSA_RI_NCAND = 2,    /* keys whose logit reached the candidate threshold            */
   PQHSA_RI_NSEL = 3,     /* keys selected (== K after the finish kernel)                */
   PQHSA_RI_FALLBACK = 4, /* 1 if the finish kernel had to select from all keys          */
+  PQHSA_RI_TIES = 5,     /* size of the group of equal logits the K-th fell into, when only part of it
+                            was taken (lowest slots first); 0 otherwise.  One CTA per row form only */
   PQHSA_RI_INTS = 8
 };
 

@@ -13,7 +13,7 @@ ABI_VERSION = 4
 SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 2048
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
-RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK = range(5)
+RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK, RI_TIES = range(6)
 F32, BF16, F16 = 0, 1, 2
 STAGE_LUT, STAGE_SCAN, STAGE_SELECT, STAGE_ATTEND, STAGE_MERGE = range(5)
 

@@ -173,6 +173,16 @@ __device__ __forceinline__ float pq_sum_row(const float* lut, uint32_t code) {
   return acc;
 }
 
+// asynchronous 16-byte copies from global to shared memory (L2 only), in groups a thread can wait for
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Contribution of one key to the exp-sum of its scan unit, relative to the unit's maximum
 // logit: 2^(logit * log2(e) + ref), ref = unit_ref(unit maximum), one fused multiply-add
 // (the scan runs it on two rows at a time with the packed form, which rounds identically).

@@ -264,6 +264,13 @@ __device__ __forceinline__ int encode_tokens(const EncodeArgs& a, const int s, c
 #pragma unroll
     for (int d = 0; d < 8; ++d) { cwv[d] = x[d]; cwv[8 + d] = y[d]; }
   }
+  if (count > 0) {
+    // the centroid rows are wanted two dependent loads from now (key row, then its direction): ask L2 for them already
+    const char* cb = reinterpret_cast<const char*>(coarse);
+    const size_t bytes = (size_t)nl * kD * sizeof(E);
+    for (size_t o = (size_t)tid * 128; o < bytes; o += (size_t)THREADS * 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(cb + o));
+  }
   for (int it = 0; it < count; ++it) {
     const int pos = sink_end + n_sorted + n_tail;
     const int slot = n_sorted + n_tail;

@@ -1,11 +1,11 @@
-// First two kernels of a decode step.
+// First kernel of a decode step.
 //
-// lut_build_kernel: per-query, per-head table construction, optionally fused with the step's token
-// append (raw K/V row write) and the incremental encode of the key that left the local window.  The
-// CTAs of a stream take roles by blockIdx.y - list scores for 64 lists each (they also share out the
-// byte-pair tables; the first one writes the K/V row), encode - and run side by side; the stream's
-// length and its norm bound change once all of them are done (arrival counter, no waiting), the tail
-// count is written by the encode CTA, which is the only one that reads it after the start.
+// lut_build_kernel: per-query-row table construction and threshold estimate, optionally fused with the step's
+// token append (raw K/V row write) and the incremental encode of the key that left the local window.  The CTAs
+// of a stream take roles by blockIdx.y - the encode CTA first (the longest chain of the kernel), then one CTA per
+// query row - and run side by side without waiting for one another: a row CTA needs nothing from the others.  The
+// stream's length and its norm bound change once all of them are done (arrival counter), the tail count is written
+// by the encode CTA at its very end.
 //
 // For every stream s and query row g:
 //   lut[s][g][m][c]      = scale * <q_g restricted to subspace m, codebooks[s][m][c]>
@@ -16,29 +16,35 @@
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:2975-3051), as is done here, in fp32.
 // The 8 nibble tables are also folded into the 4 byte-pair tables the scan looks codes up in.
 //
+// A row CTA streams the stream's centroid rows (128 KB at 512 lists in 16-bit elements) and then the sample
+// records (64 KB) through a ring of three 32 KB stages in shared memory with 16-byte asynchronous copies, three
+// chunks in flight: the list scores are computed from the stage (two threads per centroid row, pieces placed so
+// that the reads are free of bank conflicts) and kept in shared memory, the sample keys are scored from them
+// as their chunks land, and their logits never leave the registers.  The G row CTAs of a stream read the same
+// rows: one of them brings them in from HBM, the others find them in L2.
+//
 // Threshold estimate.  The exact top-K needs the K-th largest of N logits, which is not
 // known before the scan.  A stratified sample of 4096 slots of the list-sorted region
-// (contiguous records made when the layout was made) is scored by the list CTAs - each the
-// sample keys of its own lists, whose scores it has just computed - and their logits go to
-// the rows' sample arrays.
-//
-// tau_kernel (second launch, one CTA per query row) histograms the row's sample logits over their
-// own range, walks the histogram from the top and takes as threshold tau the logit below which all
-// but r sample keys lie, r = f n + margin * sqrt(f n) + 1 with f = K / N, and as its upper
-// companion tau_hi the logit that only f n - margin * sqrt(f n) - 1 sample keys exceed.  The scan
+// (contiguous records made when the layout was made) is scored by the row's CTA, which histograms
+// the logits over their own range, walks the histogram from the top and takes as threshold tau the
+// logit below which all but r sample keys lie, r = f n + margin * sqrt(f n) + 1 with f = K / N, and as its
+// upper companion tau_hi the logit that only f n - margin * sqrt(f n) - 1 sample keys exceed.  The scan
 // marks the keys with logit >= tau (about 1.7 K of them); the selection bins them between tau and
 // tau_hi, where the K-th largest lies.  Both are only filters: if fewer than K candidates turn up
 // (probability ~1e-9 at the default margin of 6 sigma) the selection falls back to all keys, and a
 // K-th largest outside [tau, tau_hi] only makes the boundary bin larger, so the result is exact
 // either way.
+//
+// tau_kernel (a second launch, only for an index without sample records) gathers and scores the sample slots
+// itself, one CTA per query row.
 #include "encode.cuh"
 
 namespace pqhsa {
 
 constexpr int kLutThreads = 256;
 constexpr int kLutWarps = kLutThreads / 32;
-constexpr int kListsPerCta = 64;  // 8 warps x 8 lists: 8 list CTAs + 1 encode CTA per stream at 512 lists
-constexpr int kTauThreads = 256;
+constexpr int kRingStages = 3;
+constexpr int kStageBytes = 32768;
 
 struct LutArgs {
   const void* q;
@@ -73,53 +79,150 @@ struct LutArgs {
   const void* new_v;
   KvAddr kv;
   int bump;       // 1: no row is written but the length of a live stream advances (the caller stored the row)
-  int list_ctas;  // CTAs per stream with the list-score role
   int encode;     // 1: one more CTA per stream encodes enc.enc_count[s] / enc.uniform_count keys
   EncodeArgs enc;
 };
 
-// Sums 32 values per lane across the warp; lane j returns the total of v[j].  Each step exchanges one
-// half of the remaining values with the lane `o` away and keeps the other half.
-__device__ __forceinline__ float warp_reduce_scatter32(float (&v)[32], int lane) {
+// Scratch of the threshold placement of one row by one CTA of kLutThreads threads.
+struct TauScratch {
+  uint32_t hist[kBins];
+  uint32_t wsum[kLutWarps], wmin[kLutWarps], wmax[kLutWarps];
+  int bin_lo, bin_hi;
+};
+constexpr int kTauPer = kSample / kLutThreads;  // sample logits per thread
+
+// Thresholds of a row from the kSample sample logits its CTA holds in registers (as ordered keys): a 2048-bin histogram
+// over the sample's own range is walked from the top; tau is the lower edge of the bin where the count reaches r (one
+// bin of slack), tau_hi the upper edge of the bin where it reaches r_hi.  n = the stream's key count this step.  All
+// threads of the CTA call.
+__device__ __forceinline__ void place_thresholds(const LutArgs& a, int row, int n_sorted, int n,
+                                                 const uint32_t (&key)[kTauPer], TauScratch& sh) {
+  constexpr int kBPT = kBins / kLutThreads;  // bins per thread
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
+  const int ns = min(kSample, n_sorted);
+  const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
+  const float margin = a.margin != 0.f ? a.margin : 6.f;
+  const int r = (int)ceilf(expect + margin * sqrtf(expect) + 1.f);
+  const int r_hi = (int)floorf(expect - fabsf(margin) * sqrtf(expect)) - 1;
+  if (K == 0 || r >= ns || r < 1) {
+    // nothing to select, or so large a fraction that every key is a candidate
+    if (tid == 0) {
+      a.row_tau[row] = (K == 0) ? __builtin_huge_valf() : kNegInf;
+      a.row_bin[2 * row] = 0.f;
+      a.row_bin[2 * row + 1] = 0.f;
+    }
+    return;
+  }
+  uint32_t mn = key[0], mx = key[0];
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) {
-    const bool up = (lane & o) != 0;
+  for (int i = 1; i < kTauPer; ++i) {
+    mn = min(mn, key[i]);
+    mx = max(mx, key[i]);
+  }
+  mn = __reduce_min_sync(0xffffffffu, mn);
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  if (lane == 0) {
+    sh.wmin[warp] = mn;
+    sh.wmax[warp] = mx;
+  }
+  for (int i = tid; i < kBins; i += kLutThreads) sh.hist[i] = 0u;
+  if (tid == 0) {
+    sh.bin_lo = -1;
+    sh.bin_hi = -1;
+  }
+  __syncthreads();
+  mn = __reduce_min_sync(0xffffffffu, sh.wmin[lane & (kLutWarps - 1)]);
+  mx = __reduce_max_sync(0xffffffffu, sh.wmax[lane & (kLutWarps - 1)]);
+  // linear bins over the row's own range [min, max]
+  const float lo = key_float(mn), hi = key_float(mx);
+  const float inv_w = hi > lo ? (float)kBins / (hi - lo) : 1.f;
 #pragma unroll
-    for (int i = 0; i < o; ++i) {  // o values stay after this step
-      const float keep = up ? v[i + o] : v[i];
-      const float send = up ? v[i] : v[i + o];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+  for (int i = 0; i < kTauPer; ++i) atomicAdd(&sh.hist[logit_bin(key_float(key[i]), lo, inv_w)], 1u);
+  __syncthreads();
+  const int top = kBins - kBPT * tid;  // thread j owns the kBPT bins just below
+  uint32_t c[kBPT], sum = 0;
+#pragma unroll
+  for (int b = 0; b < kBPT; ++b) {
+    c[b] = sh.hist[top - 1 - b];
+    sum += c[b];
+  }
+  uint32_t incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) sh.wsum[warp] = incl;
+  __syncthreads();
+  incl += __reduce_add_sync(0xffffffffu, lane < warp ? sh.wsum[lane & (kLutWarps - 1)] : 0u);
+  const uint32_t excl = incl - sum;
+  // the bin in which the count from the top reaches r (threshold) and r_hi (upper companion)
+  const uint32_t needs[2] = {(uint32_t)r, (uint32_t)max(r_hi, 0)};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const uint32_t need = needs[which];
+    if (need >= 1u && excl < need && need <= incl) {
+      uint32_t cum = excl;
+#pragma unroll
+      for (int b = 0; b < kBPT; ++b) {
+        if (cum < need && need <= cum + c[b]) {
+          if (which == 0) sh.bin_lo = top - 1 - b; else sh.bin_hi = top - 1 - b;
+        }
+        cum += c[b];
+      }
     }
   }
-  return v[0];
+  __syncthreads();
+  if (tid == 0) {
+    // one bin of slack for the rounding of the edges; bins 0 and 1 mean "everything"
+    const bool all = sh.bin_lo <= 1;
+    const float tau = all ? kNegInf : lo + (float)(sh.bin_lo - 1) / inv_w;
+    const float tau_hi = sh.bin_hi < 0 ? hi : lo + (float)(sh.bin_hi + 2) / inv_w;
+    a.row_tau[row] = tau;
+    a.row_bin[2 * row] = all ? 0.f : tau;
+    a.row_bin[2 * row + 1] = (!all && tau_hi > tau) ? (float)PQHSA_SELECT_BINS / (tau_hi - tau) : 0.f;
+  }
 }
 
-template <typename E, int G>
+// 16 bytes of a centroid row as floats
+template <typename E> struct Piece {
+  static constexpr int kDims = 16 / (int)sizeof(E);
+  static __device__ __forceinline__ void unpack(const uint4& r, float (&v)[kDims]) {
+    if constexpr (sizeof(E) == 2) {
+      unpack8(r, static_cast<const E*>(nullptr), v);
+    } else {
+      v[0] = __uint_as_float(r.x);
+      v[1] = __uint_as_float(r.y);
+      v[2] = __uint_as_float(r.z);
+      v[3] = __uint_as_float(r.w);
+    }
+  }
+};
+
+struct LutShared {
+  float q[kD];  // the query row times the softmax scale
+  float lut[kM * kC];
+  float lsc[kLMax];
+  TauScratch tau;
+};
+
+template <typename E>
 __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs a) {
-  __shared__ float qs[G][kD];
-  __shared__ float lut_s[G][kM * kC];
-  __shared__ float lsc_s[G][kListsPerCta];
-  __shared__ EncodeShared<kLutThreads> esh;
-  __shared__ int last_list_s;
-  const int s = blockIdx.x;
+  extern __shared__ __align__(16) unsigned char ring[];  // kRingStages x kStageBytes
+  __shared__ LutShared sh;
+  const int s = blockIdx.x, G = a.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const E* q = static_cast<const E*>(a.q);
   const bool append = a.new_k != nullptr;
   int32_t* st = a.state + (size_t)s * kST;
   const int seq_old = st[PQHSA_ST_SEQ_LEN];
   const int n_sorted = st[PQHSA_ST_N_SORTED];
-  const bool sampling = a.slog != nullptr && n_sorted > kSample;  // shorter streams: every key is a candidate
-  const bool is_encode = (int)blockIdx.y >= a.list_ctas;
+  const int n_tail_old = st[PQHSA_ST_N_TAIL];  // the encode CTA rewrites it at its very end
+  const bool is_encode = a.encode != 0 && blockIdx.y == 0;  // first in launch order: the longest chain of the kernel
   const bool bump = a.bump != 0 && seq_old > 0;
-  // One key to encode (the usual decode step): the list CTAs share the nearest-list search - each over the lists
-  // whose scores it computes anyway - and the one that arrives last among them finishes the key.  More keys: the
-  // encode CTA takes them one after the other.
   const int want = a.encode ? (a.enc.enc_count ? a.enc.enc_count[s] : a.enc.uniform_count) : 0;
-  const bool shared_encode = want == 1;
 
-  if (is_encode && shared_encode) {
-    // nothing to do here: the list CTAs encode the key
-  } else if (is_encode) {
+  if (is_encode) {
     // encode role.  Only tokens that were in the cache when the kernel started are encoded: the row
     // another CTA of this launch is writing is not read (a row the caller stored before the call
     // counts).  A larger norm is parked in norm_pend and folded into norm_max by the last CTA, like
@@ -129,19 +232,44 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
     const int n_tail = encode_tokens<E, kLutThreads>(a.enc, s, seq_old + (bump ? 1 : 0));
     if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail;
   } else {
-    const int l0 = blockIdx.y * kListsPerCta;
-    // requested before anything else is looked at: this warp's centroid rows (a lane owns 4 dims) ...
-    const E* coarse = static_cast<const E*>(a.coarse) + (size_t)s * a.num_lists * kD;
-    constexpr int kPerWarp = kListsPerCta / kLutWarps;
-    float c[kPerWarp][4];
+    const int g = (int)blockIdx.y - a.encode, row = s * G + g;
+    const bool want_tau = a.slog != nullptr && a.sample != nullptr;
+    const bool sampling = want_tau && n_sorted > kSample;  // shorter streams: every key is a candidate
+    // ---- the stream of 32 KB chunks through the ring: the centroid rows, then the sample records ----
+    constexpr int kRowBytes = kD * (int)sizeof(E);
+    constexpr int kPPR = kRowBytes / 16;           // 16-byte pieces per centroid row
+    constexpr int kLPS = kStageBytes / kRowBytes;  // centroid rows per chunk
+    constexpr int kPPT = kPPR / 2;                 // pieces per thread: two threads share a row, one the even pieces, one the odd
+    constexpr int kDPP = Piece<E>::kDims;
+    constexpr int kRecPerChunk = kStageBytes / 16;
+    constexpr int kSampleChunks = kSample / kRecPerChunk;
+    static_assert(2 * kLPS <= kLutThreads && kSample % kRecPerChunk == 0 && kRecPerChunk % kLutThreads == 0, "chunk shape");
+    const unsigned char* coarse = static_cast<const unsigned char*>(a.coarse) + (size_t)s * a.num_lists * kRowBytes;
+    const int4* sample = a.sample + (size_t)s * kSample;
+    const int nc = (a.num_lists + kLPS - 1) / kLPS;
+    const int total = nc + (sampling ? kSampleChunks : 0);
+    auto issue = [&](int c) {
+      if (c < total) {
+        unsigned char* stage = ring + (size_t)(c % kRingStages) * kStageBytes;
+        if (c < nc) {
+          // piece P of the chunk's row l sits at piece slot P ^ ((l & 3) << 1) of the row: the eight threads of a
+          // quarter warp (four rows, even and odd pieces) then read eight different 16-byte bank groups
+          const int rows = min(kLPS, a.num_lists - c * kLPS);
+          const unsigned char* src = coarse + (size_t)c * kStageBytes;
+          for (int i = tid; i < rows * kPPR; i += kLutThreads) {
+            const int l = i / kPPR, P = i % kPPR;
+            cp_async16(stage + l * kRowBytes + ((P ^ ((l & 3) << 1)) << 4), src + (size_t)i * 16);
+          }
+        } else {
+          const int4* src = sample + (size_t)(c - nc) * kRecPerChunk;
+          for (int i = tid; i < kRecPerChunk; i += kLutThreads) cp_async16(stage + i * 16, src + i);
+        }
+      }
+      cp_async_commit();  // one group per chunk slot, empty or not: the waits count groups
+    };
 #pragma unroll
-    for (int i = 0; i < kPerWarp; ++i) {
-      const int l = l0 + warp * kPerWarp + i;
-#pragma unroll
-      for (int d = 0; d < 4; ++d) c[i][d] = 0.f;
-      if (l < a.num_lists) load4(coarse + (size_t)l * kD + lane * 4, c[i]);
-    }
-    // ... the thread's code word ...
+    for (int c = 0; c < kRingStages; ++c) issue(c);
+    // ---- the row's tables while the first chunks travel ----
     float w[kSub];
     if (tid < kM * kC) {
       const E* cw = static_cast<const E*>(a.codebooks) + ((size_t)s * kM * kC + tid) * kSub;
@@ -151,30 +279,9 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
 #pragma unroll
       for (int d = 0; d < 8; ++d) { w[d] = x[d]; w[8 + d] = y[d]; }
     }
-    // ... and this CTA's slice of the stream's sample records (sorted by list)
-    int i0 = 0, i1 = 0;
-    if (sampling && a.sample != nullptr) {
-      const int32_t* ss = a.sample_start + (size_t)s * (kLMax + 1);
-      i0 = ss[min(l0, a.num_lists)];
-      i1 = ss[min(l0 + kListsPerCta, a.num_lists)];
-    }
     const int qb = a.io_map != nullptr ? a.io_map[s] : s;  // negative: the stream is idle this step
-    for (int i = tid; i < G * kD; i += kLutThreads)
-      qs[i / kD][i % kD] = qb >= 0 ? to_f(q[(size_t)qb * G * kD + i]) * a.scale : 0.f;
-    __syncthreads();
-    // the tables (every list CTA: it scores its share of the sample with them)
-    if (tid < kM * kC) {
-      const int m = tid / kC;
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float acc = 0.f;
-#pragma unroll
-        for (int d = 0; d < kSub; ++d) acc = fmaf(qs[g][m * kSub + d], w[d], acc);
-        if (blockIdx.y == 0) a.lut[((size_t)s * G + g) * kM * kC + tid] = acc;
-        lut_s[g][tid] = acc;
-      }
-    }
-    if (blockIdx.y == 0 && append && tid >= kM * kC && tid < kM * kC + 2 * kD / 8) {
+    if (tid < kD) sh.q[tid] = qb >= 0 ? to_f(static_cast<const E*>(a.q)[((size_t)qb * G + g) * kD + tid]) * a.scale : 0.f;
+    if (g == 0 && append && tid >= kM * kC && tid < kM * kC + 2 * kD / 8) {
       // the step's K/V row, 16 bytes per thread (elements are 2 or 4 bytes: 8 or 4 per vector)
       constexpr int kVec = 16 / (int)sizeof(E);
       const long long off = a.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], seq_old);
@@ -186,109 +293,91 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
       }
     }
-    // list scores: one warp per list, kPerWarp x G partial dot products per lane; 32 of them at a time
-    // are summed across the warp with 31 shuffles (halving exchange: lane j ends up with the total of
-    // value j) instead of 5 per value
-    float qr[G][4];
+    __syncthreads();
+    if (tid < kM * kC) {
+      const int m = tid / kC;
+      float acc = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int d = 0; d < 4; ++d) qr[g][d] = qs[g][lane * 4 + d];
-    constexpr int kVals = kPerWarp * G;
-#pragma unroll
-    for (int b0 = 0; b0 < kVals; b0 += 32) {
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int idx = b0 + j;
-        v[j] = 0.f;
-        if (idx < kVals) {
-          const int i = idx / G, g = idx % G;
-          float acc = c[i][0] * qr[g][0];
-          acc = fmaf(c[i][1], qr[g][1], acc);
-          acc = fmaf(c[i][2], qr[g][2], acc);
-          v[j] = fmaf(c[i][3], qr[g][3], acc);
-        }
-      }
-      const float tot = warp_reduce_scatter32(v, lane);
-      const int idx = b0 + lane;
-      if (idx < kVals) {
-        const int i = idx / G, g = idx % G;
-        const int l = l0 + warp * kPerWarp + i;
-        if (l < a.num_lists) {
-          a.list_scores[((size_t)s * G + g) * kLMax + l] = tot;
-          lsc_s[g][l - l0] = tot;
-        }
-      }
+      for (int d = 0; d < kSub; ++d) acc = fmaf(sh.q[m * kSub + d], w[d], acc);
+      a.lut[(size_t)row * kM * kC + tid] = acc;
+      sh.lut[tid] = acc;
     }
-    __syncthreads();  // tables and list scores of this CTA are in shared memory
+    // this thread's half of the query row: the dims of the even (h = 0) or odd (h = 1) pieces of a centroid row
+    const int h = tid & 1, ll = tid >> 1;
+    float qh[kD / 2];
+#pragma unroll
+    for (int k = 0; k < kPPT; ++k)
+#pragma unroll
+      for (int e = 0; e < kDPP; ++e) qh[k * kDPP + e] = sh.q[(2 * k + h) * kDPP + e];
+    __syncthreads();
     if (a.pair_tab != nullptr) {
       // the scan looks codes up a byte (two subspaces) at a time: entry (p, byte) = lut[2p][byte & 15] +
-      // lut[2p+1][byte >> 4]; the list CTAs of a stream write equal shares of the G x 1024 entries
-      constexpr int GP = G < 4 ? G : 4;
-      float* dst = a.pair_tab + (size_t)s * G * 1024;
-      const int per = (G * 1024 + a.list_ctas - 1) / a.list_ctas;
-      const int e1 = min(G * 1024, ((int)blockIdx.y + 1) * per);
-      for (int i = blockIdx.y * per + tid; i < e1; i += kLutThreads) {
-        const int pass = i / (1024 * GP), rem = i % (1024 * GP);
-        const int e = rem / GP, g = rem % GP;
-        dst[i] = pair_entry(lut_s[pass * GP + g], e >> 8, (uint32_t)(e & 255));
-      }
+      // lut[2p+1][byte >> 4], the rows of a group of min(G, 4) interleaved
+      const int GP = G < 4 ? G : 4;
+      float* dst = a.pair_tab + (size_t)s * G * 1024 + (size_t)(g / GP) * 1024 * GP + (g % GP);
+      for (int e = tid; e < 1024; e += kLutThreads) dst[(size_t)e * GP] = pair_entry(sh.lut, e >> 8, (uint32_t)(e & 255));
     }
-    // the sample keys of this CTA's lists are scored (same arithmetic as the scan)
-    for (int i = i0 + tid; i < i1; i += kLutThreads) {
-      const int4 v = __ldg(a.sample + (size_t)s * kSample + i);
-      const uint32_t code = (uint32_t)v.x;
-      const float kn = __int_as_float(v.y);
-      const int l = v.z - l0;
+    // ---- list scores: two threads per centroid row of the chunk ----
+    for (int c = 0; c < nc; ++c) {
+      cp_async_wait<kRingStages - 1>();
+      __syncthreads();  // every thread's pieces of chunk c have landed
+      const unsigned char* stage = ring + (size_t)(c % kRingStages) * kStageBytes;
+      const int l = c * kLPS + ll;
+      const bool valid = ll < kLPS && l < a.num_lists;
+      float dot = 0.f;
+      if (valid) {
+        const unsigned char* rowp = stage + ll * kRowBytes;
+        const int sw = (ll & 3) << 1;
 #pragma unroll
-      for (int g = 0; g < G; ++g)
-        a.slog[((size_t)s * G + g) * kSample + i] = finish_logit(pq_sum_row(lut_s[g], code), lsc_s[g][l], kn);
+        for (int k = 0; k < kPPT; ++k) {
+          float cv[kDPP];
+          Piece<E>::unpack(*reinterpret_cast<const uint4*>(rowp + (((2 * k + h) ^ sw) << 4)), cv);
+#pragma unroll
+          for (int e = 0; e < kDPP; ++e) dot = fmaf(cv[e], qh[k * kDPP + e], dot);
+        }
+      }
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      if (valid && h == 0) {
+        sh.lsc[l] = dot;
+        a.list_scores[(size_t)row * kLMax + l] = dot;
+      }
+      __syncthreads();  // the stage is free again
+      issue(c + kRingStages);
     }
-    if (shared_encode) {
-      // the key that leaves the local window: position, slot, and whether it can be taken at all (never a token
-      // that is not in the cache, never beyond the pool) - the same tests as encode_tokens
-      const int n_tail_old = st[PQHSA_ST_N_TAIL];
-      const int seq_lim = seq_old + (bump ? 1 : 0);
-      const int pos = min(a.enc.sink, seq_lim) + n_sorted + n_tail_old, slot = n_sorted + n_tail_old;
-      const bool valid = pos < seq_lim && slot < a.enc.cap && n_tail_old < a.enc.tail_cap;
-      if (valid) {  // uniform over the CTA (and over the stream's CTAs)
-        const int nl = st[PQHSA_ST_N_LISTS];
-        const long long off = a.enc.kv.offset(st[PQHSA_ST_REQ], st[PQHSA_ST_KV_HEAD], pos);
-        float vval = 0.f;
-        if (tid < kD) vval = to_f(static_cast<const E*>(a.enc.v_base)[off + tid]);
-        const float nrm = enc_direction<E, kLutThreads>(static_cast<const E*>(a.enc.k_base), off, esh);
-        float bd;
-        int bl;
-        enc_nearest_list<E, kLutThreads>(coarse, l0, l0 + kListsPerCta, nl, esh, bd, bl);
-        if (tid == 0) {
-          a.enc_best[(size_t)s * 16 + blockIdx.y] = make_float2(bd, __int_as_float(bl));
-          __threadfence();
-          const int t = atomicAdd(a.ticket + 2 * s, 1);
-          last_list_s = (t == a.list_ctas - 1);
-          if (last_list_s) a.ticket[2 * s] = 0;  // ready for the next launch
+    // ---- the sample keys are scored (same arithmetic as the scan) and the thresholds placed ----
+    if (sampling) {
+      constexpr int kPer = kRecPerChunk / kLutThreads;
+      uint32_t key[kSampleChunks * kPer];
+#pragma unroll
+      for (int j = 0; j < kSampleChunks; ++j) {
+        cp_async_wait<kRingStages - 1>();
+        __syncthreads();  // the chunk has landed; the first time round also: all list scores are in shared memory
+        const int4* rec = reinterpret_cast<const int4*>(ring + (size_t)((nc + j) % kRingStages) * kStageBytes);
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+          const int4 v = rec[tid + i * kLutThreads];
+          key[j * kPer + i] = float_key(finish_logit(pq_sum_row(sh.lut, (uint32_t)v.x), sh.lsc[v.z], __int_as_float(v.y)));
         }
         __syncthreads();
-        if (last_list_s) {
-          if (tid == 0) {
-            float d0 = __builtin_huge_valf();
-            int lw = 0;
-            for (int y = 0; y < a.list_ctas; ++y) {  // ascending list ranges: strict < keeps the lowest index on ties
-              const float2 b = __ldcg(a.enc_best + (size_t)s * 16 + y);
-              if (y * kListsPerCta < nl && b.x < d0) {
-                d0 = b.x;
-                lw = __float_as_int(b.y);
-              }
-            }
-            esh.list_sh = lw;
-            a.enc.norm_max[s] = a.norm_max[s];  // the pending norm bound starts from the stream's
-          }
-          __syncthreads();
-          enc_finish<E, kLutThreads>(a.enc, s, slot, pos, esh.list_sh, nrm, vval, w, esh);
-          if (tid == 0) st[PQHSA_ST_N_TAIL] = n_tail_old + 1;
-        }
+        issue(nc + j + kRingStages);
       }
+      // the encode role may still be running: its effect on the key count follows from the counters as they
+      // were when the kernel started (tau is only a filter: the selection takes K from the final counters)
+      int added = 0;
+      if (a.encode) {
+        const int seq_new = seq_old + ((append || bump) ? 1 : 0);
+        const int room_seq = seq_new - (min(a.enc.sink, seq_new) + n_sorted + n_tail_old);
+        added = max(0, min(min(want, room_seq), min(a.enc.cap - (n_sorted + n_tail_old), a.enc.tail_cap - n_tail_old)));
+      }
+      place_thresholds(a, row, n_sorted, n_sorted + n_tail_old + added, key, sh.tau);
+    } else if (want_tau && tid == 0) {
+      // so few keys that every key is a candidate (or nothing to select)
+      const int K = resolve_topk(n_sorted + n_tail_old, a.top_fraction, a.topk_fixed);
+      a.row_tau[row] = (K == 0) ? __builtin_huge_valf() : kNegInf;
+      a.row_bin[2 * row] = 0.f;
+      a.row_bin[2 * row + 1] = 0.f;
     }
+    cp_async_wait<0>();
   }
 
   // ---- counters: the CTA of the stream that arrives last of all.  Every CTA of the stream is then done
@@ -309,131 +398,39 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
   }
 }
 
-// One CTA per query row: the candidate threshold tau and the upper end tau_hi of the selection's bins from
-// the row's sample logits (see the file comment).  Runs after lut_build_kernel has ended, so the stream
-// counters are final.
+// One CTA per query row, for an index without sample records: the sample slots are gathered from the index, scored,
+// and the thresholds placed as above.  Runs after lut_build_kernel has ended, so the stream counters are final.
 template <typename E>
-__global__ void __launch_bounds__(kTauThreads) tau_kernel(const LutArgs a) {
-  __shared__ uint32_t hist[kBins];
-  __shared__ uint32_t wsum[kTauThreads / 32], wmin[kTauThreads / 32], wmax[kTauThreads / 32];
+__global__ void __launch_bounds__(kLutThreads) tau_kernel(const LutArgs a) {
+  __shared__ TauScratch tsh;
   __shared__ float lut_s[kM * kC];
-  __shared__ int bin_lo, bin_hi;
   const int row = blockIdx.x, s = row / a.G;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   const int32_t* st = a.state + (size_t)s * kST;
   const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL];
   const int n = n_sorted + n_tail;
-  const int K = resolve_topk(n, a.top_fraction, a.topk_fixed);
-  const int ns = min(kSample, n_sorted);
-  const float expect = n > 0 ? (float)K / (float)n * (float)ns : 0.f;
-  const float margin = a.margin != 0.f ? a.margin : 6.f;
-  const int r = (int)ceilf(expect + margin * sqrtf(expect) + 1.f);
-  const int r_hi = (int)floorf(expect - fabsf(margin) * sqrtf(expect)) - 1;
-  const bool trivial = K == 0 || n_sorted <= kSample || r >= ns || r < 1;
-  if (trivial) {
-    // nothing to select, or so few keys (or so large a fraction) that every key is a candidate
+  if (n_sorted <= kSample) {
+    // so few keys that every key is a candidate (or nothing to select)
     if (tid == 0) {
-      a.row_tau[row] = (K == 0) ? __builtin_huge_valf() : kNegInf;
+      a.row_tau[row] = resolve_topk(n, a.top_fraction, a.topk_fixed) == 0 ? __builtin_huge_valf() : kNegInf;
       a.row_bin[2 * row] = 0.f;
       a.row_bin[2 * row + 1] = 0.f;
     }
     return;
   }
-  constexpr int kVPT = kSample / kTauThreads;  // sample logits per thread
-  constexpr int kBPT = kBins / kTauThreads;    // bins per thread
-  uint32_t key[kVPT];
-  if (a.sample != nullptr) {
-    const float* slog = a.slog + (size_t)row * kSample;
-#pragma unroll
-    for (int i = 0; i < kVPT; ++i) key[i] = float_key(__ldcg(slog + tid + i * kTauThreads));
-  } else {
-    // no sample records: the sample slots are gathered from the index and scored here
-    if (tid < kM * kC) lut_s[tid] = a.lut[(size_t)row * kM * kC + tid];
-    __syncthreads();
-    const uint32_t* codes = a.codes + (size_t)s * a.cap;
-    const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
-    const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
-#pragma unroll
-    for (int i = 0; i < kVPT; ++i) {
-      const int slot = (int)((long long)(tid + i * kTauThreads) * n_sorted / ns);
-      key[i] = float_key(finish_logit(pq_sum_row(lut_s, __ldg(codes + slot)),
-                                      a.list_scores[(size_t)row * kLMax + lids[slot]], to_f(norms[slot])));
-    }
-  }
-  uint32_t mn = key[0], mx = key[0];
-#pragma unroll
-  for (int i = 1; i < kVPT; ++i) {
-    mn = min(mn, key[i]);
-    mx = max(mx, key[i]);
-  }
-  mn = __reduce_min_sync(0xffffffffu, mn);
-  mx = __reduce_max_sync(0xffffffffu, mx);
-  if (lane == 0) {
-    wmin[warp] = mn;
-    wmax[warp] = mx;
-  }
-  for (int i = tid; i < kBins; i += kTauThreads) hist[i] = 0u;
-  if (tid == 0) {
-    bin_lo = -1;
-    bin_hi = -1;
-  }
+  if (tid < kM * kC) lut_s[tid] = a.lut[(size_t)row * kM * kC + tid];
   __syncthreads();
+  const uint32_t* codes = a.codes + (size_t)s * a.cap;
+  const E* norms = static_cast<const E*>(a.norms) + (size_t)s * a.cap;
+  const uint16_t* lids = a.list_ids + (size_t)s * a.cap;
+  uint32_t key[kTauPer];
 #pragma unroll
-  for (int w = 0; w < kTauThreads / 32; ++w) {
-    mn = min(mn, wmin[w]);
-    mx = max(mx, wmax[w]);
+  for (int i = 0; i < kTauPer; ++i) {
+    const int slot = (int)((long long)(tid + i * kLutThreads) * n_sorted / kSample);
+    key[i] = float_key(finish_logit(pq_sum_row(lut_s, __ldg(codes + slot)),
+                                    a.list_scores[(size_t)row * kLMax + lids[slot]], to_f(norms[slot])));
   }
-  // linear bins over the row's own range [min, max]
-  const float lo = key_float(mn), hi = key_float(mx);
-  const float inv_w = hi > lo ? (float)kBins / (hi - lo) : 1.f;
-#pragma unroll
-  for (int i = 0; i < kVPT; ++i) atomicAdd(&hist[logit_bin(key_float(key[i]), lo, inv_w)], 1u);
-  __syncthreads();
-  const int top = kBins - kBPT * tid;  // thread j owns the kBPT bins just below
-  uint32_t c[kBPT], sum = 0;
-#pragma unroll
-  for (int b = 0; b < kBPT; ++b) {
-    c[b] = hist[top - 1 - b];
-    sum += c[b];
-  }
-  uint32_t incl = sum;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += v;
-  }
-  if (lane == 31) wsum[warp] = incl;
-  __syncthreads();
-  uint32_t before = 0;
-  for (int i = 0; i < warp; ++i) before += wsum[i];
-  incl += before;
-  const uint32_t excl = incl - sum;
-  // the bin in which the count from the top reaches r (threshold) and r_hi (upper companion)
-  const uint32_t needs[2] = {(uint32_t)r, (uint32_t)max(r_hi, 0)};
-#pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    const uint32_t need = needs[which];
-    if (need >= 1u && excl < need && need <= incl) {
-      uint32_t cum = excl;
-#pragma unroll
-      for (int b = 0; b < kBPT; ++b) {
-        if (cum < need && need <= cum + c[b]) {
-          if (which == 0) bin_lo = top - 1 - b; else bin_hi = top - 1 - b;
-        }
-        cum += c[b];
-      }
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    // one bin of slack for the rounding of the edges; bins 0 and 1 mean "everything"
-    const bool all = bin_lo <= 1;
-    const float tau = all ? kNegInf : lo + (float)(bin_lo - 1) / inv_w;
-    const float tau_hi = bin_hi < 0 ? hi : lo + (float)(bin_hi + 2) / inv_w;
-    a.row_tau[row] = tau;
-    a.row_bin[2 * row] = all ? 0.f : tau;
-    a.row_bin[2 * row + 1] = (!all && tau_hi > tau) ? (float)PQHSA_SELECT_BINS / (tau_hi - tau) : 0.f;
-  }
+  place_thresholds(a, row, n_sorted, n, key, tsh);
 }
 
 static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, LutArgs& a) {
@@ -465,7 +462,6 @@ static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const
   a.sample_start = static_cast<const int32_t*>(p.sample_start);
   a.slog = w.slog == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.slog);
   a.norm_max_rw = static_cast<float*>(p.norm_max);
-  a.list_ctas = (p.num_lists + kListsPerCta - 1) / kListsPerCta;
   a.k_base = const_cast<void*>(p.k_base);
   a.v_base = const_cast<void*>(p.v_base);
   a.kv = make_kvaddr(p);
@@ -477,20 +473,24 @@ static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const
   a.enc.norm_max = w.norm_pend == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.norm_pend);
 }
 
-template <typename E, int G>
+template <typename E>
 static int launch_lut_build_t(const pqhsa_params& p, const LutArgs& a, cudaStream_t st) {
-  const dim3 grid(p.num_streams, a.list_ctas + a.encode);
-  lut_build_kernel<E, G><<<grid, kLutThreads, 0, st>>>(a);
+  const dim3 grid(p.num_streams, p.group + a.encode);
+  constexpr size_t smem = (size_t)kRingStages * kStageBytes;
+  auto kern = lut_build_kernel<E>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return check_launch("lut_build: shared memory opt-in");
+  kern<<<grid, kLutThreads, smem, st>>>(a);
   if (int rc = check_launch("lut_build")) return rc;
-  if (a.slog == nullptr) return PQHSA_OK;  // tables only: no threshold wanted
-  tau_kernel<E><<<p.num_streams * p.group, kTauThreads, 0, st>>>(a);
+  if (a.slog == nullptr || a.sample != nullptr) return PQHSA_OK;  // no threshold wanted, or placed by the first kernel
+  tau_kernel<E><<<p.num_streams * p.group, kLutThreads, 0, st>>>(a);
   return check_launch("tau");
 }
 
 int launch_lut_build(const pqhsa_params& p, const pqhsa_ws_layout& w, const StepAppend* ap, cudaStream_t st) {
   LutArgs a;
   fill_lut_args(p, w, ap, a);
-  PQHSA_DISPATCH_E(p.dtype, PQHSA_DISPATCH_G(p.group, return (launch_lut_build_t<E, G>(p, a, st))));
+  PQHSA_DISPATCH_E(p.dtype, return (launch_lut_build_t<E>(p, a, st)));
   return PQHSA_OK;
 }
 

@@ -146,16 +146,6 @@ __device__ __forceinline__ void score_key(const float* __restrict__ mytab, uint3
   }
 }
 
-// 16-byte asynchronous copy global -> shared (L2 only) and its group bookkeeping
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 template <typename E> struct ScanRing {
   static constexpr int kCodeBytes = (kUnit / 4 + 1) * 16;                                  // 128 codes + alignment slack
   static constexpr int kNormBytes = (kUnit * (int)sizeof(E) / 16 + 1) * 16;                // 128 norms + slack

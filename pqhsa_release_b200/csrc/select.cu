@@ -839,11 +839,6 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   auto logit_at = [&](int slot, int list) -> float {
     return finish_logit(pq_sum_row(sh.lut, __ldg(codes + slot)), sh.lsc[list], to_f(norms[slot]));
   };
-  auto slot_of = [&](int i) -> int {
-    int slot, list, unit;
-    locate(i, slot, list, unit);
-    return slot;
-  };
   auto key = [&](int i) -> uint32_t {
     int slot, list, unit;
     locate(i, slot, list, unit);
@@ -853,7 +848,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   long long* soff = a.sel_off + (size_t)row * a.kcap;
   const bool take_all = K >= C;
   uint32_t T = 0u, T2 = 0u;
-  int t = 0;
+  int t = 0, tie_group = 0;
   const size_t sb = (size_t)s * a.cap;
   if (!fallback) {
     // ---- 3. the candidates sit in registers, kRowPer per thread; their gathers travel four at a time ----
@@ -891,10 +886,13 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
     }
     if (!take_all) {
       const int ties = block_radix_threshold_regs<kRowThreads, kRowPer>(kreg, K, rsh2, T, t);
-      if (ties != t) {  // more keys tie at the K-th value than fit: lowest slots first
-        auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)slot_of(i) : 0u; };
+      if (ties != t) {  // more keys tie at the K-th value than fit (equal code, list and norm): lowest slots first
+        uint32_t tk[kRowPer];
+#pragma unroll
+        for (int j = 0; j < kRowPer; ++j) tk[j] = (kreg[j] == T && kreg[j] != 0u) ? ~(uint32_t)sreg[j] : 0u;
         int t2;
-        block_radix_threshold<kRowThreads>(tie_key, C, t, rsh, T2, t2);
+        block_radix_threshold_regs<kRowThreads, kRowPer>(tk, t, rsh2, T2, t2);
+        tie_group = ties;
       }
     }
     // Emit: a taken key gets its place in the selection (one shared-memory atomic per warp), the
@@ -943,6 +941,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         auto tie_key = [&](int i) -> uint32_t { return key(i) == T ? ~(uint32_t)i : 0u; };
         int t2;
         block_radix_threshold<kRowThreads>(tie_key, C, t, rsh, T2, t2);
+        tie_group = ties;
       }
     }
     for (int slot = tid; slot < C; slot += kRowThreads) {
@@ -970,6 +969,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
     ri[PQHSA_RI_NCAND] = ncand;
     ri[PQHSA_RI_NSEL] = sh.emit_count;
     ri[PQHSA_RI_FALLBACK] = fallback ? 1 : 0;
+    ri[PQHSA_RI_TIES] = tie_group;
   }
 }
 
