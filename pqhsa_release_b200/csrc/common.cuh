@@ -102,6 +102,17 @@ __device__ __forceinline__ void unpack8(const uint4& r, const __half*, float (&v
   }
 }
 
+__device__ __forceinline__ void unpack4(const uint2& r, const __nv_bfloat16*, float (&v)[4]) {
+  v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+  v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+__device__ __forceinline__ void unpack4(const uint2& r, const __half*, float (&v)[4]) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void unpack4(const uint2&, const float*, float (&)[4]) {}  // never called: floats come as float4
+
 // 8 consecutive elements, 16-byte aligned
 __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
   const float4 a = __ldg(reinterpret_cast<const float4*>(p));

@@ -67,13 +67,12 @@ template <int THREADS> struct EncodeShared {
   int list_sh;
 };
 
-// Step 1: |k| (clamped at 1e-12) of the key row at element offset `off`, its unit direction into sh.unit.
-// All threads of the CTA call; all get the norm.  The squared norm is four 32-dim butterfly sums added left to right.
-template <typename E, int THREADS>
-__device__ __forceinline__ float enc_direction(const E* __restrict__ kb, long long off, EncodeShared<THREADS>& sh) {
+// Step 1: |k| (clamped at 1e-12) of the key row whose element tid this thread holds in kval (tid < 128; 0 otherwise),
+// its unit direction into sh.unit.  All threads of the CTA call; all get the norm.  The squared norm is four 32-dim
+// butterfly sums added left to right.
+template <int THREADS>
+__device__ __forceinline__ float enc_direction(float kval, EncodeShared<THREADS>& sh) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float kval = 0.f;
-  if (tid < kD) kval = to_f(kb[off + tid]);
   const float sq = warp_sum(kval * kval);
   __syncthreads();
   if (lane == 0) sh.red[warp] = sq;
@@ -85,6 +84,39 @@ __device__ __forceinline__ float enc_direction(const E* __restrict__ kb, long lo
   if (tid < kD) sh.unit[tid] = kval / nrm;
   __syncthreads();
   return nrm;
+}
+template <typename E, int THREADS>
+__device__ __forceinline__ float enc_direction(const E* __restrict__ kb, long long off, EncodeShared<THREADS>& sh) {
+  return enc_direction<THREADS>(threadIdx.x < kD ? to_f(kb[off + threadIdx.x]) : 0.f, sh);
+}
+
+// The best (distance, then lower list index) of the threads' candidates over the CTA; all threads call, the result is
+// valid in thread 0.
+template <int THREADS>
+__device__ __forceinline__ void enc_best_of_cta(float& bd, int& bl, EncodeShared<THREADS>& sh) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+    const int ol = __shfl_xor_sync(0xffffffffu, bl, o);
+    if (od < bd || (od == bd && ol < bl)) {
+      bd = od;
+      bl = ol;
+    }
+  }
+  if (lane == 0) {
+    sh.best_d[warp] = bd;
+    sh.best_l[warp] = bl;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 1; i < THREADS / 32; ++i)
+      if (sh.best_d[i] < bd || (sh.best_d[i] == bd && sh.best_l[i] < bl)) {
+        bd = sh.best_d[i];
+        bl = sh.best_l[i];
+      }
+  }
+  __syncthreads();  // best_d / best_l may be rewritten by the next call
 }
 
 // Step 2: nearest of the lists [l_begin, l_end) (clipped to [0, nl)) to sh.unit: argmin_l |u - c_l|^2 with ties to the
@@ -155,33 +187,9 @@ __device__ __forceinline__ void enc_nearest_list(const E* __restrict__ coarse, i
       }
     }
   }
-  // best over the 8 groups of a warp (distance, then lower list index), then over the warps
-#pragma unroll
-  for (int o = 4; o < 32; o <<= 1) {
-    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-    const int ol = __shfl_xor_sync(0xffffffffu, bl, o);
-    if (od < bd || (od == bd && ol < bl)) {
-      bd = od;
-      bl = ol;
-    }
-  }
-  if (lane == 0) {
-    sh.best_d[warp] = bd;
-    sh.best_l[warp] = bl;
-  }
-  __syncthreads();
-  float d0 = sh.best_d[0];
-  int l0 = sh.best_l[0];
-  if (tid == 0) {
-    for (int i = 1; i < THREADS / 32; ++i)
-      if (sh.best_d[i] < d0 || (sh.best_d[i] == d0 && sh.best_l[i] < l0)) {
-        d0 = sh.best_d[i];
-        l0 = sh.best_l[i];
-      }
-  }
-  out_d = d0;
-  out_l = l0;
-  __syncthreads();  // best_d / best_l may be rewritten by the next call
+  enc_best_of_cta<THREADS>(bd, bl, sh);
+  out_d = bd;
+  out_l = bl;
 }
 
 // Step 3: residual against the winning list, nearest code word per subspace (thread (m, c) for tid < 128 holds code
