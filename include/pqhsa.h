@@ -137,18 +137,21 @@ typedef struct pqhsa_params {
   int64_t stride_block, stride_head, stride_row;
 
   /* Output exchange between the GPUs of a node (all zero / NULL on one GPU).  With peer_world > 1 the
-   * combine kernel also stores every output row into the gather buffer of every rank, row r of this
-   * rank at element ((parity * peer_world + peer_rank) * R + r) * 128 of that rank's buffer (parity =
-   * step count & 1: two buffers, so a rank that is one step ahead never overwrites what a peer still
-   * reads), and then raises this rank's flag on every rank.  pqhsa_wait_peers makes the stream wait
-   * for the flags of all ranks.  All ranks must run the same sequence of steps. */
-  const void *peer_out;    /* device array of peer_world pointers: every rank's gather buffer,
-                              E [2, peer_world, R, 128], mapped into this process (peer memory) */
-  const void *peer_flags;  /* device array of peer_world pointers: every rank's int32 [peer_world] flags */
+   * combine kernel also sends every output row to every rank as flagged words: 8-byte stores of (4 bytes of the
+   * row, the step count), each of which arrives whole, so the receiver needs no fence and no separate flag.
+   * Row r of this rank goes to words ((parity * peer_world + peer_rank) * R + r) * W .. + W of a rank's receive
+   * buffer, W = 128 * sizeof(E) / 4 (parity = step count & 1: two buffers, so a rank that is one step ahead never
+   * overwrites what a peer still reads).  pqhsa_wait_peers enqueues the receiving kernel: it waits for every
+   * word of the step (bounded) and unpacks the rows into peer_gather.  All ranks must run the same sequence
+   * of steps. */
+  const void *peer_out;    /* device array of peer_world pointers: every rank's receive buffer,
+                              uint32 [2, peer_world, R, W, 2], mapped into this process (peer memory) */
+  void *peer_gather;       /* this rank's gathered rows: E [2, peer_world, R, 128] (parity, source rank, its rows) */
   void *peer_seq;          /* device int32 [2] of this rank: steps exchanged so far, error flag */
   int32_t peer_world;
   int32_t peer_rank;
-  int32_t peer_wait_polls; /* polls (about 200 ns apart) pqhsa_wait_peers makes before it gives up; 0 = about a second */
+  int32_t peer_wait_polls; /* polls (about 100 ns apart) a thread of pqhsa_wait_peers makes for its word before it gives
+                              up; 0 = about half a second */
   int32_t external_append; /* 1: pqhsa_decode_step_append with new_k == NULL advances every live stream's length by
                               one without writing a row - the caller's own cache write (vLLM's
                               reshape_and_cache_flash) has already stored this step's K/V.  0: the length stays. */
@@ -286,10 +289,11 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
  * are already on the device inside vLLM). */
 int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream);
 
-/* Multi-GPU: make `stream` wait until every rank's flag in this rank's flag array has reached this
- * rank's step count, i.e. until all output rows of the last step have arrived in this rank's gather
- * buffer (the buffer of parity (steps - 1) & 1).  One warp polls with a limit of about a second;
- * when it runs out, peer_seq[1] is set to 1 and the kernel returns (the context stays usable).
+/* Multi-GPU: enqueue the receiving side of the output exchange on `stream`.  One thread per flagged word of
+ * this step's parity in this rank's receive buffer waits until the word carries this rank's step count and
+ * stores its 4 bytes into peer_gather (the buffer of parity (steps - 1) & 1): when the kernel has ended, the
+ * output rows of all ranks are there.  Every wait is bounded (peer_wait_polls); when one runs out,
+ * peer_seq[1] is set to 1, the word is skipped and the kernel returns (the context stays usable).
  * Replaces the NCCL all-gather that would otherwise follow the step: the rows travel as plain
  * stores over NVLink from inside the combine kernel.  The reference has no counterpart (it runs
  * under vLLM's own tensor parallelism). */

@@ -42,7 +42,7 @@ class Params(C.Structure):
         ("k_base", C.c_void_p), ("v_base", C.c_void_p), ("block_table", C.c_void_p),
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
-        ("peer_out", C.c_void_p), ("peer_flags", C.c_void_p), ("peer_seq", C.c_void_p),
+        ("peer_out", C.c_void_p), ("peer_gather", C.c_void_p), ("peer_seq", C.c_void_p),
         ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_wait_polls", C.c_int32), ("external_append", C.c_int32),
         ("q", C.c_void_p), ("out", C.c_void_p), ("io_map", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]

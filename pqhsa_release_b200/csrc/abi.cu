@@ -53,17 +53,19 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->kcap = topk_capacity(p);
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
-  // With fewer than 96 query rows the selection of a row is shared by `parts` CTAs (a power of two): enough of
-  // them to fill the GPU, and enough that a part's candidate list (`seg` entries, a quarter more than an even
-  // share of the candidates a row can reasonably have) fits in shared memory.
+  // The selection of a row is done by one CTA when the candidates a row can reasonably have (about 1.7 K; allowed
+  // for here: 2 K + 1024) fit the 8192 that CTA holds in registers - whatever the number of rows: measured, one CTA
+  // per row beats the shared form even with 16 rows on 148 SMs.  A larger K is shared by `parts` CTAs (a power of two):
+  // enough of them to fill the GPU, and enough that a part's candidate list (`seg` entries, a quarter more than an
+  // even share of the candidates) fits in shared memory.
   {
     const size_t ccap = cap < (size_t)2 * o->kcap + 2048 ? cap : (size_t)2 * o->kcap + 2048;
     int parts = 1;
-    if (R < 96) {
+    if ((size_t)2 * o->kcap + 1024 > 8192) {
       parts = 2;
       while (parts < 16 && (R * parts < 296 || ccap * 5 / 4 > (size_t)parts * 8192)) parts *= 2;
     }
-    o->parts = parts;  // 1: enough rows to fill the GPU with one CTA per row, which then needs no candidate lists
+    o->parts = parts;
     o->seg = parts == 1 ? 8 : (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
   }
   const size_t nrec = R * (size_t)o->parts * (size_t)o->seg;
@@ -140,8 +142,8 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
       return set_error(PQHSA_E_SHAPE, "k_base / v_base must be 16-byte aligned");
   }
   if (p->peer_world > 1) {
-    if (!p->peer_out || !p->peer_flags || !p->peer_seq)
-      return set_error(PQHSA_E_NULL, "peer_out / peer_flags / peer_seq is null with peer_world > 1");
+    if (!p->peer_out || !p->peer_gather || !p->peer_seq)
+      return set_error(PQHSA_E_NULL, "peer_out / peer_gather / peer_seq is null with peer_world > 1");
     if (p->peer_rank < 0 || p->peer_rank >= p->peer_world || p->peer_world > 32)
       return set_error(PQHSA_E_SHAPE, "peer_rank %d / peer_world %d out of range", p->peer_rank, p->peer_world);
     if (p->peer_wait_polls < 0) return set_error(PQHSA_E_SHAPE, "peer_wait_polls must be non-negative");
@@ -270,7 +272,10 @@ int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream) {
 int pqhsa_wait_peers(const pqhsa_params* p, void* stream) {
   if (p == nullptr) return set_error(PQHSA_E_NULL, "params is null");
   if (p->peer_world <= 1) return PQHSA_OK;
-  if (!p->peer_flags || !p->peer_seq) return set_error(PQHSA_E_NULL, "peer_flags / peer_seq is null");
+  if (!p->peer_out || !p->peer_gather || !p->peer_seq)
+    return set_error(PQHSA_E_NULL, "peer_out / peer_gather / peer_seq is null");
+  if (p->num_streams <= 0 || (p->group != 1 && p->group != 2 && p->group != 4 && p->group != 8))
+    return set_error(PQHSA_E_SHAPE, "num_streams %d / group %d out of range", p->num_streams, p->group);
   if (p->peer_rank < 0 || p->peer_rank >= p->peer_world || p->peer_world > 32)
     return set_error(PQHSA_E_SHAPE, "peer_rank %d / peer_world %d out of range", p->peer_rank, p->peer_world);
   return launch_wait_peers(*p, (cudaStream_t)stream);

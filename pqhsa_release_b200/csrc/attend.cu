@@ -62,7 +62,6 @@ struct AttendArgs {
   const float* tail_logit;
   // output exchange between GPUs (peer_world <= 1: none)
   void* const* peer_out;
-  int32_t* const* peer_flags;
   int32_t* peer_seq;
   int32_t* combine_ticket;
   int peer_world, peer_rank;
@@ -421,6 +420,16 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
 // pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).  Thread d owns output dim d.  Everything a thread needs
 // of the first 32 partials - their (max, sum) pairs, which every thread of a warp reads from the same
 // addresses, and its own dim of their accumulators - is requested at once: one round trip, no barrier.
+// A flagged word: 8 bytes stored and loaded as one transaction (the data and the step count that says it is there).
+__device__ __forceinline__ void store_flagged(uint2* p, uint32_t data, uint32_t flag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint2 load_flagged(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 template <typename E>
 __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -466,63 +475,51 @@ __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
     if (ob >= 0) static_cast<E*>(a.out)[((size_t)ob * a.G + (row - s * a.G)) * kD + tid] = res;
   }
   if (a.peer_world > 1) {
-    // Every CTA sends its own row to every rank's gather buffer (16-byte stores into peer memory over
-    // NVLink; the buffer of this step's parity) and fences at system scope; the CTA that arrives last at
-    // the ticket then raises this rank's flag on every rank.  Nobody waits.
+    // Every CTA sends its own row to every rank as flagged words: 8-byte stores (4 bytes of the row, the step
+    // count) into peer memory over NVLink.  A word arrives whole, so the receiver needs no fence and no flag
+    // besides it, and nobody waits here.  The CTA that arrives last at the ticket counts the step.
     __shared__ __align__(16) E row_s[kD];
-    __shared__ int last_s;
     const int seq0 = a.peer_seq[0];  // steps before this one: only the last CTA changes it, after all have read it
     row_s[tid] = res;
     __syncthreads();
-    constexpr int kVecs = kD * (int)sizeof(E) / 16;  // 16-byte vectors per row
-    if (tid < kVecs) {
-      const uint4 vec = reinterpret_cast<const uint4*>(row_s)[tid];
-      const size_t at = (((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row) * kVecs + tid;
-      for (int r = 0; r < a.peer_world; ++r) reinterpret_cast<uint4*>(a.peer_out[r])[at] = vec;
-      __threadfence_system();
+    constexpr int kWords = kD * (int)sizeof(E) / 4;  // flagged words per row
+    const uint32_t* row_w = reinterpret_cast<const uint32_t*>(row_s);
+    const size_t at = (((size_t)(seq0 & 1) * a.peer_world + a.peer_rank) * a.R + row) * kWords;
+    for (int w = tid; w < kWords; w += kD) {
+      const uint32_t payload = row_w[w];
+      for (int r = 0; r < a.peer_world; ++r)
+        store_flagged(static_cast<uint2*>(a.peer_out[r]) + at + w, payload, (uint32_t)(seq0 + 1));
     }
-    __syncthreads();  // the row's stores are fenced ...
+    __syncthreads();  // every thread has read the step count
     if (tid == 0) {
-      __threadfence();  // ... before the ticket
       const int t = atomicAdd(a.combine_ticket, 1);
-      last_s = (t == (int)gridDim.x - 1);
-    }
-    __syncthreads();
-    if (last_s) {
-      if (tid == 0) {
+      if (t == (int)gridDim.x - 1) {
         a.combine_ticket[0] = 0;
         a.peer_seq[0] = seq0 + 1;
-      }
-      __threadfence_system();
-      if (tid < a.peer_world) {
-        volatile int32_t* f = a.peer_flags[tid] + a.peer_rank;
-        *f = seq0 + 1;
       }
     }
   }
 }
 
-// One warp: lane r waits for rank r's flag in this rank's flag array to reach this rank's step count.
-// The wait is bounded: when `polls` polls (about 200 ns apart) have passed the error flag is set and the
-// kernel returns.
-__global__ void __launch_bounds__(32) wait_peers_kernel(int32_t* const* peer_flags, int32_t* peer_seq, int world, int rank,
-                                                        int polls) {
-  const int lane = threadIdx.x;
-  const int target = peer_seq[0];
-  bool ok = true;
-  if (lane < world) {
-    volatile const int32_t* f = peer_flags[rank] + lane;
-    ok = false;
-    for (int it = 0; it < polls; ++it) {
-      if (*f - target >= 0) {
-        ok = true;
-        break;
-      }
-      __nanosleep(200);
+// Receiving side: one thread per flagged word of this step's parity.  It polls its word (bounded: `polls` polls
+// about 100 ns apart) until the word carries the step count, then stores the 4 bytes into the gathered rows.  When a
+// wait runs out the error flag is set, the word is skipped and the thread returns.
+__global__ void __launch_bounds__(256) wait_peers_kernel(const uint2* const* peer_out, int rank, uint32_t* gather,
+                                                         int32_t* peer_seq, long long words, int polls) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= words) return;
+  const uint2* recv = peer_out[rank];  // this rank's own receive buffer
+  const int target = peer_seq[0];  // counted by the combine kernel of this step, which ran before on this stream
+  const size_t at = (size_t)((target - 1) & 1) * (size_t)words + (size_t)i;
+  for (int it = 0; it < polls; ++it) {
+    const uint2 w = load_flagged(recv + at);
+    if ((int)w.y == target) {
+      gather[at] = w.x;
+      return;
     }
+    __nanosleep(100);
   }
-  __threadfence_system();  // the rows that preceded the flags are visible to what follows in the stream
-  if (!ok) peer_seq[1] = 1;
+  peer_seq[1] = 1;
 }
 
 template <typename E, bool MAPPED>
@@ -572,7 +569,6 @@ static int launch_attend_or_combine(const pqhsa_params& p, const pqhsa_ws_layout
   a.unit_sum = reinterpret_cast<const float*>(ws + w.unit_sum);
   a.tail_logit = reinterpret_cast<const float*>(ws + w.tail_logit);
   a.peer_out = static_cast<void* const*>(p.peer_out);
-  a.peer_flags = static_cast<int32_t* const*>(p.peer_flags);
   a.peer_seq = static_cast<int32_t*>(p.peer_seq);
   a.combine_ticket = reinterpret_cast<int32_t*>(ws + w.combine_ticket);
   a.peer_world = p.peer_world;
@@ -597,8 +593,11 @@ int launch_attend(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   return launch_attend_or_combine(p, w, false, st);
 }
 int launch_wait_peers(const pqhsa_params& p, cudaStream_t st) {
-  wait_peers_kernel<<<1, 32, 0, st>>>(static_cast<int32_t* const*>(p.peer_flags), static_cast<int32_t*>(p.peer_seq),
-                                      p.peer_world, p.peer_rank, p.peer_wait_polls > 0 ? p.peer_wait_polls : (1 << 22));
+  const size_t esz = p.dtype == PQHSA_F32 ? 4 : 2;
+  const long long words = (long long)p.peer_world * p.num_streams * p.group * (long long)(kD * esz / 4);
+  wait_peers_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint2* const*>(p.peer_out), p.peer_rank, static_cast<uint32_t*>(p.peer_gather),
+      static_cast<int32_t*>(p.peer_seq), words, p.peer_wait_polls > 0 ? p.peer_wait_polls : (1 << 22));
   return check_launch("wait_peers");
 }
 

@@ -4,14 +4,15 @@
 // leave the chip except for the ~2K candidates per row).
 //
 // The scan left one bit per (row, slot): the key's approximate logit reached the
-// row's threshold tau.  Two forms, chosen by the number of query rows R:
+// row's threshold tau.  Two forms, chosen by K:
 //
-// R >= 96 - row_select_kernel, one CTA of 1024 threads per row (end of this file):
-// the GPU is full with a CTA per row, and the row's candidates never leave the SM.
+// 2 K + 1024 <= 8192 - row_select_kernel, one CTA of 1024 threads per row (end of this
+// file): the row's candidates (about 1.7 K) stay in the CTA's registers and never
+// leave the SM.  Measured, this is the faster form even with 16 rows on 148 SMs.
 //
-// R < 96 (a shard of a multi-GPU step, a single request) - two launches with
-// `parts` CTAs per row, so that the GPU is full whatever the row count is; a CTA
-// never waits for another one (the second launch starts when the first has ended):
+// A larger K (c4: 5243 of 262144 keys) - two launches with `parts` CTAs per row,
+// each with its share of the candidates in shared memory; a CTA never waits for
+// another one (the second launch starts when the first has ended):
 //
 // cand_kernel.  The hit words of a row are dealt out to its CTAs word by word.  A
 // CTA tabulates its words (bits, first slot, list, candidates listed before) in
@@ -666,8 +667,8 @@ __global__ void __launch_bounds__(kSelThreads, 4) emit_kernel(const SelectArgs a
 }
 
 // ---- one CTA per query row --------------------------------------------------------------------------
-// With many query rows (R >= 96) a row's selection stays in one CTA of 1024 threads; the GPU is full with one CTA per
-// row, and nothing is written to or read back from global memory in between.
+// A row's selection stays in one CTA of 1024 threads, and nothing is written to or read back from global memory in
+// between.
 //   1. A thread takes 8 consecutive hit words (two 16-byte loads) and a block prefix sum says how many candidates are
 //      listed before each word.
 //   2. Candidate i belongs to the last non-empty word whose offset does not exceed i: such a word writes (its index,

@@ -47,14 +47,15 @@ def gather_context(local: torch.Tensor, out: torch.Tensor | None = None, group=N
 
 
 class PeerExchange:
-    """The output exchange without a collective call: symmetric gather buffers and flag arrays of
-    the ranks of one node, mapped into every process (``torch.distributed._symmetric_memory``), and
-    their addresses installed in a pool's parameters.  The combine kernel of every step then stores
-    its output rows into every rank's buffer and raises a flag; :meth:`wait` enqueues the bounded
-    wait for all ranks' flags.  All ranks must run the same number of steps.
+    """The output exchange without a collective call: symmetric receive buffers of the ranks of one
+    node, mapped into every process (``torch.distributed._symmetric_memory``), and their addresses
+    installed in a pool's parameters.  The combine kernel of every step then sends its output rows to
+    every rank as flagged words (8-byte stores of 4 bytes of the row and the step count);
+    :meth:`wait` enqueues the receiving kernel, which waits (bounded) for every word of the step and
+    unpacks the rows into the gathered buffer.  All ranks must run the same number of steps.
 
-    Layout of a rank's buffer: ``[2, world, R, 128]`` - parity of the step, source rank, the source
-    rank's query rows."""
+    Layout of a rank's gathered rows: ``[2, world, R, 128]`` - parity of the step, source rank, the
+    source rank's query rows."""
 
     def __init__(self, pool, group=None):
         import torch.distributed._symmetric_memory as symm
@@ -65,24 +66,22 @@ class PeerExchange:
         group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         R = pool.S * pool.G
-        self.buf = symm.empty(2, self.world, R, _lib.HEAD_DIM, dtype=pool.dtype, device=pool.device)
-        self.flags = symm.empty(max(self.world, 8), dtype=torch.int32, device=pool.device)
-        hb = symm.rendezvous(self.buf, group)
-        hf = symm.rendezvous(self.flags, group)
-        self.buf.zero_()
-        self.flags.zero_()
+        words = _lib.HEAD_DIM * torch.empty(0, dtype=pool.dtype).element_size() // 4
+        self.recv = symm.empty(2, self.world, R, words, 2, dtype=torch.int32, device=pool.device)
+        hb = symm.rendezvous(self.recv, group)
+        self.recv.zero_()
+        self.buf = torch.zeros(2, self.world, R, _lib.HEAD_DIM, dtype=pool.dtype, device=pool.device)
         self.ptr_out = torch.tensor([int(x) for x in hb.buffer_ptrs], dtype=torch.int64, device=pool.device)
-        self.ptr_flags = torch.tensor([int(x) for x in hf.buffer_ptrs], dtype=torch.int64, device=pool.device)
         self.seq = torch.zeros(2, dtype=torch.int32, device=pool.device)  # steps exchanged, error flag
         p = pool.p
-        p.peer_out, p.peer_flags, p.peer_seq = self.ptr_out.data_ptr(), self.ptr_flags.data_ptr(), self.seq.data_ptr()
+        p.peer_out, p.peer_gather, p.peer_seq = self.ptr_out.data_ptr(), self.buf.data_ptr(), self.seq.data_ptr()
         p.peer_world, p.peer_rank = self.world, self.rank
-        self._handles = (hb, hf)
+        self._handles = (hb,)
         torch.cuda.synchronize(pool.device)
         dist.barrier(group)  # nobody stores into a buffer that its owner has not cleared yet
 
     def wait(self) -> None:
-        """Make the current stream wait for the rows of the last step from every rank."""
+        """Make the current stream receive the rows of the last step from every rank."""
         import ctypes as C
 
         self._lib.call("pqhsa_wait_peers", C.byref(self.pool.p), self.pool._stream())
@@ -98,9 +97,9 @@ class PeerExchange:
 
 class LocalPeerGroup:
     """The same exchange between several pools that live in ONE process on ONE GPU (shards of a
-    layer stepped one after the other on the same stream): every pool plays a rank, the gather
-    buffers and flag arrays are ordinary device tensors.  Used to exercise the exchange protocol
-    without a second GPU; the kernels are the ones the multi-GPU path runs."""
+    layer stepped one after the other on the same stream): every pool plays a rank, the receive
+    buffers are ordinary device tensors.  Used to exercise the exchange protocol without a second
+    GPU; the kernels are the ones the multi-GPU path runs."""
 
     def __init__(self, pools, wait_polls: int = 0):
         from . import _lib
@@ -112,14 +111,14 @@ class LocalPeerGroup:
         if any(p.S * p.G != R or p.dtype != p0.dtype or p.device != p0.device for p in self.pools):
             raise ValueError("all pools of a local peer group need the same row count, dtype and device")
         dev = p0.device
+        words = _lib.HEAD_DIM * torch.empty(0, dtype=p0.dtype).element_size() // 4
+        self.recv = [torch.zeros(2, self.world, R, words, 2, dtype=torch.int32, device=dev) for _ in self.pools]
         self.bufs = [torch.zeros(2, self.world, R, _lib.HEAD_DIM, dtype=p0.dtype, device=dev) for _ in self.pools]
-        self.flags = [torch.zeros(max(self.world, 8), dtype=torch.int32, device=dev) for _ in self.pools]
         self.seqs = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in self.pools]
-        self.ptr_out = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=dev)
-        self.ptr_flags = torch.tensor([f.data_ptr() for f in self.flags], dtype=torch.int64, device=dev)
+        self.ptr_out = torch.tensor([b.data_ptr() for b in self.recv], dtype=torch.int64, device=dev)
         for r, pool in enumerate(self.pools):
             p = pool.p
-            p.peer_out, p.peer_flags, p.peer_seq = self.ptr_out.data_ptr(), self.ptr_flags.data_ptr(), self.seqs[r].data_ptr()
+            p.peer_out, p.peer_gather, p.peer_seq = self.ptr_out.data_ptr(), self.bufs[r].data_ptr(), self.seqs[r].data_ptr()
             p.peer_world, p.peer_rank, p.peer_wait_polls = self.world, r, int(wait_polls)
 
     def wait(self, rank: int) -> None:

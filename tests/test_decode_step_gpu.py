@@ -63,15 +63,21 @@ def test_batch_of_requests_and_group2():
     _check_case(case, pool)
 
 
-def test_many_query_rows_select_with_one_cta_per_row():
-    # 96 query rows and more: the selection of a row stays in one CTA (fewer rows split it over several)
+def test_selection_forms_by_k():
+    # a K whose candidates fit one CTA's registers: one CTA per row, whatever the row count
     case = make_case(B=6, Hkv=4, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
     pool, _, _ = pool_from_case(case)
     assert pool.layout.parts == 1
     info = _check_case(case, pool)
     assert int(info[:, 4].sum()) == 0
     small = make_case(B=1, Hkv=2, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
-    assert pool_from_case(small)[0].layout.parts > 1
+    assert pool_from_case(small)[0].layout.parts == 1
+    # a large K (2 K + 1024 > 8192): several CTAs per row, candidate lists in shared memory
+    big = make_case(B=1, Hkv=2, G=4, S=12000, L=64, dtype=torch.bfloat16, frac=0.32, seed=23)
+    pool, _, _ = pool_from_case(big)
+    assert pool.layout.parts > 1
+    info = _check_case(big, pool)
+    assert int(info[0, 0]) > 3584
 
 
 def test_config0_like_fp32_single_head():
