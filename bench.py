@@ -53,7 +53,21 @@ def parse_args():
     ap.add_argument("--flush", default="write+read", choices=["write+read", "write", "read", "none"],
                     help="how the L2 is flushed between timed steps")
     ap.add_argument("--stages", action="store_true", help="also print the per-stage timing table to stderr")
+    ap.add_argument("--no-sidecar", action="store_true", help="skip the second end-to-end figure (through GQASidecar)")
     return ap.parse_args()
+
+
+def profiled_traffic(kernel: str):
+    """DRAM bytes (read + written) of one launch of ``kernel`` on workload c2, from the line
+    ``dram bytes per launch: <kernel> <bytes>`` of the committed ncu summary; None if the file or the line is missing."""
+    import re
+
+    try:
+        text = (ROOT / "profiles" / "decode_step_c2_ncu_full.md").read_text()
+    except OSError:
+        return None
+    m = re.search(rf"^dram bytes per launch: {re.escape(kernel)} (\d+)\s*$", text, re.M)
+    return int(m.group(1)) if m else None
 
 
 def measured_peaks():
@@ -205,7 +219,9 @@ class StepRunner:
                 self.exchange = None
                 pool.p.peer_world = 0
         self.graph = None
-        self.launches_per_step = 7  # tables + append + encode, thresholds, scan, candidates, emit, attend + background, combine (+ the peer wait when sharded)
+        # tables + thresholds + append + encode, scan, selection (two launches when a row's selection is shared by
+        # several CTAs), attend + background, combine (+ the receiving kernel when sharded)
+        self.launches_per_step = 5 + (1 if pool.layout.parts > 1 else 0)
         pool.graph_headroom = headroom
         if use_graph:
             self._body()  # warm the lazy set-up (shared-memory opt-in, NCCL) outside the capture
@@ -237,6 +253,62 @@ class StepRunner:
         if self.exchange is not None:
             return self.exchange.result(self.steps_done)
         return self.gathered if self.gathered is not None else self.out
+
+
+def sidecar_e2e(wl, kv, qs, nks, nvs, n_ctx, steps, flush_l2, device):
+    """The same step through ``GQASidecar`` as the reference's decode runtime drives it (one sidecar for the
+    layer's requests): per step the host copies the queries and the new K/V rows from pinned memory, calls
+    ``lean_append`` and ``forward`` (one fused library call, replayed as a self-validated CUDA graph) and reads
+    the context back into pinned memory."""
+    from pqhsa_release_b200.config import paper_attention_config, paper_index_config
+    from pqhsa_release_b200.gqa_sidecar import GQASidecar
+
+    kc, vc = kv
+    B, H, G, D = wl.batch, kc.shape[1], wl.group, wl.head_dim
+    side = GQASidecar(
+        paper_index_config(num_lists=wl.num_lists),
+        paper_attention_config(scale=1.0 / math.sqrt(D), sink_tokens=wl.sink_tokens, local_window=wl.local_window,
+                               retrieval_top_fraction=wl.top_fraction, index_update_interval=1,
+                               index_update_strategy="incremental"),
+        num_query_heads=H * G, num_kv_heads=H)
+    side.build_cache(kc[:, :, : wl.context], vc[:, :, : wl.context])
+    nq = len(qs)
+    hq = [q.reshape(B, H * G, D).cpu().pin_memory() for q in qs]
+    hk = [k.reshape(B, H, D).cpu().pin_memory() for k in nks]
+    hv = [v.reshape(B, H, D).cpu().pin_memory() for v in nvs]
+    dq, dk, dv = (torch.empty_like(t[0], device=device) for t in (hq, hk, hv))
+    hout = torch.empty(B, H * G, D, dtype=wl.dtype).pin_memory()
+
+    def step(i, ev=None):
+        flush_l2()
+        if ev is not None:
+            ev[0].record()
+        dq.copy_(hq[i % nq], non_blocking=True); dk.copy_(hk[i % nq], non_blocking=True); dv.copy_(hv[i % nq], non_blocking=True)
+        if not side.lean_append(dk, dv, dq):
+            raise SystemExit("GQASidecar.lean_append refused one token per request")
+        hout.copy_(side.forward(dq), non_blocking=True)
+        if ev is not None:
+            ev[1].record()
+
+    for i in range(4):
+        step(i)
+    torch.cuda.synchronize()
+    if not bool(torch.isfinite(hout.float()).all()):
+        raise SystemExit("sidecar end-to-end check failed: non-finite context")
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for i in range(steps):
+        step(4 + i, evs[i])
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+    keys = wl.batch * wl.kv_heads * n_ctx
+    out = {"value": keys / (ms / 1e3), "unit": UNIT, "us_per_layer_step": 1e3 * ms, "steps": steps,
+           "cuda_graph_active": bool(side.cuda_graph_active),
+           "h2d_bytes_per_step": sum(t[0].numel() * t[0].element_size() for t in (hq, hk, hv)),
+           "d2h_bytes_per_step": hout.numel() * hout.element_size(),
+           "entry": "GQASidecar.lean_append + forward (copies of the inputs into the graph's static buffers included)"}
+    del side
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_b200(args):
@@ -377,6 +449,29 @@ def run_b200(args):
     h2d = hin[0].numel() * hin[0].element_size()
     d2h = hout.numel() * hout.element_size()
 
+    # ---- the latency floor of the step's launches: a graph of as many empty kernels, timed the same way ----
+    n_launch = runner.launches_per_step + (1 if runner.exchange is not None else 0)
+    floor_us = None
+    if runner.graph is not None:
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.call("pqhsa_launch_empty", n_launch, stream)
+        torch.cuda.synchronize()
+        fg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fg):
+            _lib.call("pqhsa_launch_empty", n_launch, torch.cuda.current_stream().cuda_stream)
+        nf = min(K, 50)
+        evf = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nf)]
+        for i in range(nf):
+            flush_l2()
+            evf[i][0].record(); fg.replay(); evf[i][1].record()
+        torch.cuda.synchronize()
+        floor_us = 1e3 * sum(a.elapsed_time(b) for a, b in evf) / nf
+
+    # ---- end to end through the reference-facing object: GQASidecar.lean_append + forward, host buffers ----
+    e2e_sidecar = None
+    if world == 1 and not args.no_sidecar:
+        e2e_sidecar = sidecar_e2e(wl, kv, qs, nks, nvs, n_start, min(K, 64), flush_l2, device)
+
     # ---- per-kernel durations inside a step --------------------------------
     # The five launches of a step are issued one by one with an event between them, right behind the L2
     # flush: the flush is still running while they are enqueued, so every event pair brackets exactly
@@ -418,7 +513,7 @@ def run_b200(args):
         + wl.batch * hl * wl.num_lists * wl.head_dim * e
     # dram__bytes_read.sum + dram__bytes_write.sum of one attend_kernel launch, from the committed ncu capture summary of this
     # workload under profiles/ (one GPU); no capture exists for other shapes
-    traffic = 165_806_336 if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
+    traffic = profiled_traffic("attend_kernel") if (wl.name.startswith("c2") and world == 1 and not (args.context or args.batch)) else None
     attend_s = stage_ms[3] / 1e3
     achieved = attend_bytes / attend_s / 1e9
     line = {
@@ -431,7 +526,7 @@ def run_b200(args):
             "context": wl.context, "indexed_keys_per_stream": n_start, "topk": wl.topk(), "lists": wl.num_lists,
             "kv_layout": "contiguous", "index_update": "incremental, 1 key per step",
             "parallelism": f"kv-head shard x{world}",
-            "exchange": "none" if world == 1 else ("peer stores from the combine kernel + flag wait" if runner.exchange is not None
+            "exchange": "none" if world == 1 else ("flagged-word peer stores from the combine kernel + receiving kernel" if runner.exchange is not None
                                                    else "nccl all-gather"), "l2": f"flushed between timed steps ({args.flush} of 256 MiB)",
             "cuda_graph": not args.no_graph,
         },
@@ -444,12 +539,15 @@ def run_b200(args):
         "stages_us": {n: round(1e3 * m, 2) for n, m in zip(stage_names, stage_ms)},
         "e2e": {"value": e2e_value, "unit": UNIT, "us_per_layer_step": 1e3 * e2e_ms / K,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": (runner.launches_per_step + (1 if runner.exchange is not None else 0)) * K,
+        "gpu_launches": n_launch * K,
+        "launch_floor_us": floor_us,  # a CUDA graph of as many empty kernels as the step has launches, timed the same way
         "clocks": clocks,
         "wall_s_timed_region": wall, "setup_s": setup_s,
     }
+    if e2e_sidecar is not None:
+        line["e2e_sidecar"] = e2e_sidecar
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_reference(wl, budget_s=20.0, steps=3, warmup=1)["cpu_baseline"]
+        line["cpu_baseline"] = cpu_reference(wl, budget_s=20.0, steps=20, warmup=3)["cpu_baseline"]
     if rank == 0:
         if args.stages:
             print(json.dumps(line["stages_us"]), file=sys.stderr)
@@ -640,6 +738,7 @@ def run_paged_plugin(args):
     stage_ms = [0.0] * 5
     reps = min(10, K)
     pool = engines[0].pool
+    launches = 5 + (1 if pool.layout.parts > 1 else 0)  # tables, scan, selection (one or two), attend, combine
     for r in range(reps):
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         flush.zero_(); flush_rd.sum()
@@ -673,7 +772,7 @@ def run_paged_plugin(args):
                    "contexts": ctxs if not is_c4 else ctxs[0], "indexed_keys_all_layers_and_ranks": n_keys, "lists": wl.num_lists,
                    "kv_layout": "paged: vLLM [blocks, Hkv, 16, 2D] pages, permuted block table",
                    "index_update": "deferred, flush every 256 tokens" if is_c4 else "incremental, 1 key per request-head and step",
-                   "entry": "pq_hsa_vllm runtime.pq_or_dense_forward (eager, 7 launches per layer-step)",
+                   "entry": f"pq_hsa_vllm runtime.pq_or_dense_forward (eager, {launches} launches per layer-step)",
                    "parallelism": f"kv-head shard x{world}, attention outputs stay sharded (vLLM tensor parallelism)",
                    "l2": "flushed between timed steps (write+read of 256 MiB)", "cuda_graph": False},
         "step_roofline": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / world / (total_ms / K / 1e3) / 1e9,
@@ -683,8 +782,10 @@ def run_paged_plugin(args):
         "stages_us": {n: round(1e3 * m, 2) for n, m in zip(stage_names, stage_ms)},
         "e2e": {"value": n_keys * K / (e2e_ms / 1e3), "unit": UNIT, "us_per_layer_step": 1e3 * e2e_ms / K / layers,
                 "h2d_bytes_per_step": hq.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
-        "gpu_launches": 7 * K * layers, "clocks": clocks, "setup_s": setup_s, "runtime_stats": dict(runtime.STATS),
+        "gpu_launches": launches * K * layers, "clocks": clocks, "setup_s": setup_s, "runtime_stats": dict(runtime.STATS),
     }
+    if e2e_sidecar is not None:
+        line["e2e_sidecar"] = e2e_sidecar
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from dataclasses import replace
 
@@ -716,8 +817,8 @@ def cpu_reference(wl, budget_s, steps, warmup):
     n_streams = wl.batch * wl.kv_heads
     sample = []
     t_build = time.perf_counter()
-    # at most two full-context streams: the index build dominates the sample's cost
-    for i in range(min(2, n_streams)):
+    # at most four full-context streams: the index build dominates the sample's cost
+    for i in range(min(4, n_streams)):
         k, v = workloads.mixture_kv(100_000 * 0 + i, 1, wl.context, dtype=wl.dtype)
         st = OracleStream(
             OracleIndexConfig(num_lists=wl.num_lists),
@@ -762,7 +863,9 @@ def run_reference(args):
         from dataclasses import replace
 
         wl = replace(wl, context=args.context or wl.context, batch=args.batch or wl.batch)
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    # a step of this arm is the sample's four streams (about 13 ms each at c2): the driver's step count is
+    # honoured up to 200, never fewer than 20 after at least 3 warm-up steps
+    steps, warmup = max(20, min(args.steps, 200)), max(3, min(args.warmup, 10))
     r = cpu_reference(wl, budget_s=60.0, steps=steps, warmup=warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,

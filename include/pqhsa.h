@@ -198,7 +198,8 @@ typedef struct pqhsa_ws_layout {
   size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
   size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
   size_t combine_ticket; /* int32 [1]     finished CTAs of the combine kernel (0 between launches)          */
-  int32_t parts;       /* CTAs that share the selection of one query row */
+  int32_t parts;       /* form of the selection: 1 = one CTA per query row with 8 candidates per thread, -1 = one CTA
+                          with 16 per thread (larger K), >= 2 = that many CTAs share a row (still larger K) */
   int32_t seg;         /* candidates one of them can list */
   int32_t kcap;        /* row stride of sel_* */
   int32_t tail_cap;    /* row stride of tail_logit */
@@ -288,6 +289,10 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream);
  * several microseconds before a cudaMemcpyAsync node would.  No counterpart in the reference (its inputs
  * are already on the device inside vLLM). */
 int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream);
+
+/* Launch `count` empty kernels (one warp each) on `stream`: the latency floor of a step's launches, timed by the
+ * benchmark the same way as the step itself.  No counterpart in the reference. */
+int pqhsa_launch_empty(int32_t count, void* stream);
 
 /* Multi-GPU: enqueue the receiving side of the output exchange on `stream`.  One thread per flagged word of
  * this step's parity in this rank's receive buffer waits until the word carries this rank's step count and

@@ -73,6 +73,7 @@ EXPORTS = {
     "pqhsa_attend_merge": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_copy_small": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "pqhsa_launch_empty": (C.c_int, [C.c_int32, C.c_void_p]),
     "pqhsa_wait_peers": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step_append": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_run_stage": (C.c_int, [C.POINTER(Params), C.c_int, C.c_void_p]),

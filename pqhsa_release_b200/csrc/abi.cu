@@ -54,21 +54,21 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->tail_cap = (int32_t)align_up((size_t)(p->tail_capacity > 0 ? p->tail_capacity : 8), 8);
   o->chunks = (int32_t)((p->max_full + o->kcap + kChunk - 1) / kChunk);
   // The selection of a row is done by one CTA when the candidates a row can reasonably have (about 1.7 K; allowed
-  // for here: 2 K + 1024) fit the 8192 that CTA holds in registers - whatever the number of rows: measured, one CTA
-  // per row beats the shared form even with 16 rows on 148 SMs.  A larger K is shared by `parts` CTAs (a power of two):
-  // enough of them to fill the GPU, and enough that a part's candidate list (`seg` entries, a quarter more than an
-  // even share of the candidates) fits in shared memory.
+  // for here: 2 K + 1024) fit the registers of its 1024 threads - 8 per thread (parts = 1) or 16 (parts = -1) -
+  // whatever the number of rows: measured, one CTA per row beats the shared form even with 16 rows on 148 SMs.  A
+  // still larger K is shared by `parts` CTAs (a power of two): enough of them to fill the GPU, and enough that a
+  // part's candidate list (`seg` entries, a quarter more than an even share of the candidates) fits in shared memory.
   {
     const size_t ccap = cap < (size_t)2 * o->kcap + 2048 ? cap : (size_t)2 * o->kcap + 2048;
-    int parts = 1;
-    if ((size_t)2 * o->kcap + 1024 > 8192) {
-      parts = 2;
+    const size_t want = (size_t)2 * o->kcap + 1024;
+    int parts = want <= 8192 ? 1 : (want <= 16384 ? -1 : 2);
+    if (parts == 2)
       while (parts < 16 && (R * parts < 296 || ccap * 5 / 4 > (size_t)parts * 8192)) parts *= 2;
-    }
     o->parts = parts;
-    o->seg = parts == 1 ? 8 : (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
+    o->seg = parts < 2 ? 8 : (int32_t)align_up(ccap * 5 / (4 * (size_t)parts) + 32, 8);
   }
-  const size_t nrec = R * (size_t)o->parts * (size_t)o->seg;
+  const size_t nparts = o->parts < 2 ? 1 : (size_t)o->parts;
+  const size_t nrec = R * nparts * (size_t)o->seg;
   size_t off = 0;
   auto take = [&](size_t bytes) {
     const size_t at = off;
@@ -92,8 +92,8 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->cand_key = take(nrec * sizeof(uint32_t));
   o->cand_rec = take(nrec * 4 * sizeof(int32_t));
   o->cand_bin = take(nrec * sizeof(uint16_t));
-  o->part_hist = take(R * (size_t)o->parts * (PQHSA_SELECT_BINS + 4) * sizeof(uint32_t));
-  o->part_cnt = take(R * (size_t)o->parts * sizeof(int32_t));
+  o->part_hist = take(R * nparts * (PQHSA_SELECT_BINS + 4) * sizeof(uint32_t));
+  o->part_cnt = take(R * nparts * sizeof(int32_t));
   o->sel_slot = take(R * (size_t)o->kcap * sizeof(int32_t));
   o->sel_off = take(R * (size_t)o->kcap * sizeof(int64_t));
   o->partial = take(R * (size_t)(o->chunks + kBgParts) * kPartial * sizeof(float));
@@ -267,6 +267,14 @@ int pqhsa_copy_small(void* dst, const void* src, size_t bytes, void* stream) {
   const unsigned grid = (unsigned)((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024);
   copy16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), n);
   return check_launch("copy_small");
+}
+
+__global__ void __launch_bounds__(32) empty_kernel() {}
+
+int pqhsa_launch_empty(int32_t count, void* stream) {
+  if (count < 0 || count > 64) return set_error(PQHSA_E_SHAPE, "count %d out of range", (int)count);
+  for (int i = 0; i < count; ++i) empty_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
+  return check_launch("launch_empty");
 }
 
 int pqhsa_wait_peers(const pqhsa_params* p, void* stream) {

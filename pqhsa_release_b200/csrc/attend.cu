@@ -42,7 +42,6 @@ static_assert(kAttWarps * 32 == kChunk, "one entry per lane and chunk");
 
 struct AttendArgs {
   const void* q;
-  const int32_t* io_map;  // [S] block of q / out of a stream, or null: block s
   const void* k_base;
   const void* v_base;
   KvAddr kv;
@@ -69,6 +68,9 @@ struct AttendArgs {
   unsigned long long* work_counter;  // [2]: next item, CTAs that have left; zero between launches
   int cap, ucap, tail_cap, num_lists;
   int bg_parts;  // background items per query row in this launch (1 .. kBgParts)
+  // Kept last: measured, the gather kernel compiles to 78 registers and runs 9 % faster than with this pointer
+  // next to q (same source otherwise).
+  const int32_t* io_map;  // [S] block of q / out of a stream, or null: block s
 };
 
 template <typename E> struct RawRow;  // 8 elements of a K/V row as loaded

@@ -682,11 +682,16 @@ __global__ void __launch_bounds__(kSelThreads, 4) emit_kernel(const SelectArgs a
 // More than 8192 candidates, or fewer than K (the threshold estimate failed): the same select over all N slots with the
 // keys recomputed on every pass - slow, exact, flagged.
 constexpr int kRowThreads = 1024;
-constexpr int kRowPer = 8;                          // candidates per thread held in registers
-constexpr int kRowCandCap = kRowThreads * kRowPer;  // more candidates than that select from all keys
+// Candidates per thread held in registers: 8 (up to 8192 candidates; their token positions are fetched together
+// with their codes) or, for a larger K, 16 (up to 16384; positions are fetched for the selected ones only).
+template <int PER> struct RowShape {
+  static constexpr int kPer = PER;
+  static constexpr int kCap = kRowThreads * PER;   // more candidates than that select from all keys
+  static constexpr int kIdxBits = PER == 8 ? 13 : 14;  // bits of a candidate index
+  static constexpr bool kPositionsEarly = PER == 8;
+  static_assert(kCap == 1 << kIdxBits, "candidate index bits");
+};
 constexpr int kRowWords = 8;                        // consecutive hit words per thread and round
-constexpr int kRowIdxBits = 13;                     // bits of a candidate index (kRowCandCap = 1 << 13)
-static_assert(kRowCandCap == 1 << kRowIdxBits, "candidate index bits");
 
 struct RowShared {
   float lut[kM * kC];
@@ -695,10 +700,12 @@ struct RowShared {
   int emit_count;
 };
 
-template <typename E>
+template <typename E, int PER>
 __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArgs a) {
+  using RS = RowShape<PER>;
+  constexpr int kRowPer = RS::kPer, kRowCandCap = RS::kCap, kRowIdxBits = RS::kIdxBits;
   // candidate -> (word + 1) << 13 | offset of the word's first candidate
-  __shared__ __align__(16) uint32_t owner[kRowCandCap];
+  extern __shared__ __align__(16) uint32_t owner[];  // [kRowCandCap]
   __shared__ RowShared sh;
   __shared__ RadixShared rsh;
   __shared__ RadixShared2 rsh2;
@@ -854,7 +861,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   if (!fallback) {
     // ---- 3. the candidates sit in registers, kRowPer per thread; their gathers travel four at a time ----
     uint32_t kreg[kRowPer];
-    int sreg[kRowPer], preg[kRowPer];
+    int sreg[kRowPer], preg[RS::kPositionsEarly ? kRowPer : 1];
 #pragma unroll
     for (int j0 = 0; j0 < kRowPer; j0 += 4) {
       uint32_t code[4];
@@ -865,7 +872,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         const int j = j0 + jj, i = j * kRowThreads + tid;
         kreg[j] = 0u;
         sreg[j] = -1;
-        preg[j] = 0;
+        if constexpr (RS::kPositionsEarly) preg[j] = 0;
         code[jj] = 0u;
         list[jj] = 0;
         kn[jj] = 0.f;
@@ -875,7 +882,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
           locate(i, sreg[j], list[jj], unit);
           code[jj] = __ldg(codes + sreg[j]);
           kn[jj] = to_f(norms[sreg[j]]);
-          preg[j] = __ldg(spos + sreg[j]);
+          if constexpr (RS::kPositionsEarly) preg[j] = __ldg(spos + sreg[j]);
         }
       }
 #pragma unroll
@@ -901,13 +908,14 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
     // exp-sum loses exactly the term the scan added (a tail slot's stored logit becomes -inf).
 #pragma unroll
     for (int j0 = 0; j0 < kRowPer; j0 += 4) {
-      int o[4], un[4];
+      int o[4], un[4], pos[4];
       float um[4];
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const int j = j0 + jj;
         o[jj] = -1;
         un[jj] = 0;
+        pos[jj] = 0;
         um[jj] = 0.f;
         if (j * kRowThreads >= C) continue;  // block-uniform
         const uint32_t k = kreg[j];
@@ -917,9 +925,12 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         if (m != 0u && lane == 0) base = atomicAdd(&sh.emit_count, __popc(m));
         base = __shfl_sync(0xffffffffu, base, 0) + __popc(m & ((1u << lane) - 1u));
         o[jj] = take && base < a.kcap ? base : -1;
-        if (o[jj] >= 0 && sreg[j] < n_sorted) {
-          un[jj] = ((int)(owner[j * kRowThreads + tid] >> kRowIdxBits) - 1) >> 2;
-          um[jj] = umax[un[jj]];
+        if (o[jj] >= 0) {
+          if constexpr (RS::kPositionsEarly) pos[jj] = preg[j]; else pos[jj] = __ldg(spos + sreg[j]);
+          if (sreg[j] < n_sorted) {
+            un[jj] = ((int)(owner[j * kRowThreads + tid] >> kRowIdxBits) - 1) >> 2;
+            um[jj] = umax[un[jj]];
+          }
         }
       }
 #pragma unroll
@@ -927,7 +938,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         const int j = j0 + jj;
         if (o[jj] < 0) continue;
         sel[o[jj]] = sreg[j];
-        soff[o[jj]] = a.kv.offset(req, head, preg[j]);
+        soff[o[jj]] = a.kv.offset(req, head, pos[jj]);
         if (sreg[j] < n_sorted)
           atomicAdd(a.unit_sum + (size_t)row * a.ucap + un[jj], -unit_term(key_float(kreg[j]), unit_ref(um[jj])));
         else
@@ -1014,8 +1025,19 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   a.wcap = w.parts <= 4 ? p.unit_capacity * (4 / w.parts) : ((p.unit_capacity + w.parts - 1) / w.parts) * 4;
   const size_t smem_a = (size_t)a.wcap * (3 * sizeof(uint32_t) + sizeof(uint16_t));
   const size_t smem_b = (size_t)kBoundCap * 3 * sizeof(uint32_t);
-  if (w.parts == 1) {
-    PQHSA_DISPATCH_E(p.dtype, { row_select_kernel<E><<<R, kRowThreads, 0, st>>>(a); });
+  if (w.parts == 1 || w.parts == -1) {
+    // one CTA per row: 8 candidates per thread, or 16 for a larger K (parts == -1)
+    PQHSA_DISPATCH_E(p.dtype, {
+      if (w.parts == 1) {
+        row_select_kernel<E, 8><<<R, kRowThreads, RowShape<8>::kCap * sizeof(uint32_t), st>>>(a);
+      } else {
+        auto kern = row_select_kernel<E, 16>;
+        constexpr int smem = RowShape<16>::kCap * (int)sizeof(uint32_t);
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+          return check_launch("select: shared memory opt-in");
+        kern<<<R, kRowThreads, smem, st>>>(a);
+      }
+    });
     return check_launch("select");
   }
   const unsigned grid = (unsigned)(R * w.parts);

@@ -72,12 +72,18 @@ def test_selection_forms_by_k():
     assert int(info[:, 4].sum()) == 0
     small = make_case(B=1, Hkv=2, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
     assert pool_from_case(small)[0].layout.parts == 1
-    # a large K (2 K + 1024 > 8192): several CTAs per row, candidate lists in shared memory
+    # a larger K (2 K + 1024 > 8192): still one CTA per row, 16 candidates per thread
     big = make_case(B=1, Hkv=2, G=4, S=12000, L=64, dtype=torch.bfloat16, frac=0.32, seed=23)
     pool, _, _ = pool_from_case(big)
-    assert pool.layout.parts > 1
+    assert pool.layout.parts == -1
     info = _check_case(big, pool)
-    assert int(info[0, 0]) > 3584
+    assert int(info[0, 0]) > 3584 and int(info[:, 4].sum()) == 0
+    # a still larger K (2 K + 1024 > 16384): several CTAs per row, candidate lists in shared memory
+    huge = make_case(B=1, Hkv=1, G=4, S=20000, L=64, dtype=torch.bfloat16, frac=0.42, seed=29)
+    pool, _, _ = pool_from_case(huge)
+    assert pool.layout.parts > 1
+    info = _check_case(huge, pool)
+    assert int(info[0, 0]) > 7680
 
 
 def test_config0_like_fp32_single_head():
