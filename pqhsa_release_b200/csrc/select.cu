@@ -693,6 +693,13 @@ template <int PER> struct RowShape {
 };
 constexpr int kRowWords = 8;                        // consecutive hit words per thread and round
 
+constexpr int kRowBoundary = 256;  // members of the boundary bin ranked against each other
+static_assert(kSelHist + kRowBoundary <= kRadixBins2, "the boundary members' slots sit behind the bins");
+struct RowBoundary {
+  int bin, above, members, count, tie;
+  uint32_t T, T2;
+};
+
 struct RowShared {
   float lut[kM * kC];
   float lsc[kLMax];
@@ -709,6 +716,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   __shared__ RowShared sh;
   __shared__ RadixShared rsh;
   __shared__ RadixShared2 rsh2;
+  __shared__ RowBoundary bnd;
   const int row = blockIdx.x, s = row / a.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int32_t* ri = a.row_info + (size_t)row * kRI;
@@ -738,6 +746,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
   if (tid < kM * kC) sh.lut[tid] = a.lut[(size_t)row * kM * kC + tid];
   if (tid < kLMax) sh.lsc[tid] = a.list_scores[(size_t)row * kLMax + tid];
   if (tid == 0) sh.emit_count = 0;
+  const float blo = a.row_bin[2 * row], binv = a.row_bin[2 * row + 1];  // the selection's bins (0, 0: none)
 #pragma unroll
   for (int j = 0; j < kRowPer / 4; ++j) reinterpret_cast<uint4*>(owner)[j * kRowThreads + tid] = make_uint4(0u, 0u, 0u, 0u);
 
@@ -893,14 +902,90 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
       }
     }
     if (!take_all) {
-      const int ties = block_radix_threshold_regs<kRowThreads, kRowPer>(kreg, K, rsh2, T, t);
-      if (ties != t) {  // more keys tie at the K-th value than fit (equal code, list and norm): lowest slots first
-        uint32_t tk[kRowPer];
+      // The K-th largest lies, as a rule, between the row's threshold and its upper companion (both from the sample):
+      // one histogram pass over the kSelBins bins between them (and one bin above) finds the boundary bin, whose few
+      // members are ranked against each other by (logit desc, slot asc).  No bins, or a crowded boundary bin: the
+      // block radix select over the keys.
+      bool done = false;
+      if (binv != 0.f) {  // block-uniform
+        uint32_t* hist = rsh2.hist;              // [kSelHist]
+        uint32_t* bkey = rsh.hist;               // [kRowBoundary] keys of the boundary bin's members
+        uint32_t* bslot = rsh2.hist + kSelHist;  // [kRowBoundary] ... their slots
+        for (int i = tid; i < kSelHist; i += kRowThreads) hist[i] = 0u;
+        if (tid == 0) {
+          bnd.count = 0;
+          bnd.tie = 0;
+        }
+        __syncthreads();
 #pragma unroll
-        for (int j = 0; j < kRowPer; ++j) tk[j] = (kreg[j] == T && kreg[j] != 0u) ? ~(uint32_t)sreg[j] : 0u;
-        int t2;
-        block_radix_threshold_regs<kRowThreads, kRowPer>(tk, t, rsh2, T2, t2);
-        tie_group = ties;
+        for (int j = 0; j < kRowPer; ++j)
+          if (kreg[j] != 0u) atomicAdd(&hist[cand_bin(key_float(kreg[j]), blo, binv)], 1u);
+        __syncthreads();
+        // walk from the top: thread t owns bin kSelBins - t (bins kSelBins .. 1); the last thread also bin 0
+        const uint32_t val = hist[kSelBins - tid];
+        uint32_t incl = val;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        if (lane == 31) rsh2.wtot[warp] = incl;
+        __syncthreads();
+        incl += __reduce_add_sync(0xffffffffu, lane < warp ? rsh2.wtot[lane] : 0u);
+        const uint32_t excl = incl - val, need_k = (uint32_t)K;
+        if (excl < need_k && need_k <= incl) {
+          bnd.bin = kSelBins - tid;
+          bnd.above = (int)excl;
+          bnd.members = (int)val;
+        } else if (tid == kRowThreads - 1 && incl < need_k) {
+          bnd.bin = 0;
+          bnd.above = (int)incl;
+          bnd.members = (int)hist[0];
+        }
+        __syncthreads();
+        const int bstar = bnd.bin, need = K - bnd.above, nb = bnd.members;
+        if (nb <= kRowBoundary) {  // block-uniform
+#pragma unroll
+          for (int j = 0; j < kRowPer; ++j)
+            if (kreg[j] != 0u && cand_bin(key_float(kreg[j]), blo, binv) == bstar) {
+              const int at = atomicAdd(&bnd.count, 1);
+              bkey[at] = kreg[j];
+              bslot[at] = (uint32_t)sreg[j];
+            }
+          __syncthreads();
+          if (tid < nb) {
+            const uint32_t mk = bkey[tid], ms = bslot[tid];
+            int rank = 0, eq = 0, eq_after = 0;
+            for (int i = 0; i < nb; ++i) {
+              const uint32_t ok = bkey[i], os = bslot[i];
+              rank += (ok > mk || (ok == mk && os < ms)) ? 1 : 0;
+              eq += ok == mk ? 1 : 0;
+              eq_after += (ok == mk && os > ms) ? 1 : 0;
+            }
+            if (rank == need - 1) {  // the last key taken: everything better than it goes, equal logits up to its slot
+              bnd.T = mk;
+              bnd.T2 = ~ms;
+              bnd.tie = eq_after > 0 ? eq : 0;
+            }
+          }
+          __syncthreads();
+          T = bnd.T;
+          T2 = bnd.T2;
+          tie_group = bnd.tie;
+          done = true;
+        }
+      }
+      if (!done) {
+        __syncthreads();
+        const int ties = block_radix_threshold_regs<kRowThreads, kRowPer>(kreg, K, rsh2, T, t);
+        if (ties != t) {  // more keys tie at the K-th value than fit (equal code, list and norm): lowest slots first
+          uint32_t tk[kRowPer];
+#pragma unroll
+          for (int j = 0; j < kRowPer; ++j) tk[j] = (kreg[j] == T && kreg[j] != 0u) ? ~(uint32_t)sreg[j] : 0u;
+          int t2;
+          block_radix_threshold_regs<kRowThreads, kRowPer>(tk, t, rsh2, T2, t2);
+          tie_group = ties;
+        }
       }
     }
     // Emit: a taken key gets its place in the selection (one shared-memory atomic per warp), the
