@@ -16,7 +16,7 @@ reference's K/V ring, benchmarks/e2e_pq_param_sweep.py:2912-2986, has nothing to
 
 Fast path.  ``lean_append`` only parks the step's K/V row; the ``forward`` that follows issues
 ONE fused library call (row write + incremental encode + tables + scan + selection + attention,
-seven launches), and replays it as a CUDA graph over static input / output buffers once the
+five launches), and replays it as a CUDA graph over static input / output buffers once the
 graph has validated itself: the output buffer is poisoned with NaN, the graph is replayed and
 its result compared with the eager call on the same state - the self-check of
 benchmarks/e2e_pq_param_sweep.py:6170-6201, at most three capture attempts (:7099-7107).
@@ -62,10 +62,14 @@ class _StepGraph:
                                              self.enc, 0, self.out, self.external)
 
     def _load(self, queries, keys, values, encode: int) -> None:
-        self.q.copy_(queries)
+        # a caller that filled the static buffers itself (GQASidecar.static_inputs) passes their views: nothing to copy
+        if queries.data_ptr() != self.q.data_ptr():
+            self.q.copy_(queries)
         if not self.external:
-            self.nk.copy_(keys.reshape(self.nk.shape))
-            self.nv.copy_(values.reshape(self.nv.shape))
+            if keys.data_ptr() != self.nk.data_ptr():
+                self.nk.copy_(keys.reshape(self.nk.shape))
+            if values.data_ptr() != self.nv.data_ptr():
+                self.nv.copy_(values.reshape(self.nv.shape))
         if encode != self.enc_value:
             self.enc.fill_(encode)
             self.enc_value = encode
@@ -217,6 +221,24 @@ class GQASidecar:
             done = self.engine.apply_pending_index_update()
         return self.num_kv_heads * self.engine.B if done else 0
 
+    def _graph_for(self, external: bool) -> _StepGraph:
+        eng, sg = self.engine, self._step_graph
+        if sg is None or sg.generation != eng.generation or sg.external != external:
+            sg = self._step_graph = _StepGraph(eng, external)
+        return sg
+
+    def static_inputs(self):
+        """Views of the fused step's static input buffer: ``(queries [B, Hq, D], key [B, Hkv, D], value [B, Hkv, D],
+        flat)`` where ``flat`` is the one contiguous buffer behind the three (queries, then keys, then values).  A caller
+        that writes a step's inputs there (one host-to-device copy into ``flat``) and passes these very views to
+        ``lean_append`` and ``forward`` spares the copies into the buffer.  Valid until the cache is rebuilt or restored.
+        No counterpart in the reference (its runtime copies: pq_hsa_decode_runtime.py:384-400)."""
+        if self.engine.pool is None:
+            raise RuntimeError("build_cache first")
+        sg = self._graph_for(bool(self.engine.paged and self.external_kv_write))
+        B, H, D = self.engine.B, self.engine.H, _lib.HEAD_DIM
+        return sg.q, sg.nk.view(B, H, D), sg.nv.view(B, H, D), sg.inbuf
+
     def forward(self, queries: torch.Tensor) -> torch.Tensor:
         """queries ``[B, q_heads, dim]`` -> context ``[B, q_heads, dim]`` (possibly a view of a static buffer)."""
         if queries.ndim != 3 or queries.shape[0] != max(self.engine.B, 1):
@@ -233,9 +255,7 @@ class GQASidecar:
         grow = k is not None and not eng.paged and eng.length + 1 > eng.keys.shape[2]
         if not fused or grow:
             return eng.step(queries, k, v, external_write=external)  # refresh / growth steps run eagerly
-        sg = self._step_graph
-        if sg is None or sg.generation != eng.generation or sg.external != external:
-            sg = self._step_graph = _StepGraph(eng, external)
+        sg = self._graph_for(external)
         eng.pool.check_step(not external, external, encode)
         out = sg.run(queries, k, v, encode)
         eng.pool.note_step(not external, external, encode)

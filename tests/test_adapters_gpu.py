@@ -272,6 +272,20 @@ def test_sidecar_fast_path_replays_a_validated_cuda_graph(strategy, interval):
                 for g in range(G):
                     assert_output_close(out[b_, h_ * G + g], det.output[g], dtype, f"step {step} stream {s} row {g}")
     assert fast._step_graph.attempts == 1, "the first capture must validate"
+    # the static input buffer filled by the caller: the same step without the copies into it
+    if strategy == "incremental":
+        sq, sk, sv, flat = fast.static_inputs()
+        assert flat.numel() == sq.numel() + sk.numel() + sv.numel() and sq.data_ptr() == flat.data_ptr()
+        nk = (k[:, :, 999].float() + 0.1).to(dtype).cuda()
+        nv = torch.randn(B, Hkv, 128, generator=gen).to(dtype).cuda()
+        qq = (q.float() - 0.05).to(dtype).cuda()
+        flat.copy_(torch.cat([qq.reshape(-1), nk.reshape(-1), nv.reshape(-1)]))
+        assert fast.lean_append(sk, sv, sq) and slow.lean_append(nk, nv, qq)
+        a = fast.forward(sq).clone()
+        b = slow.forward(qq)
+        torch.cuda.synchronize()
+        assert fast.cuda_graph_active and torch.equal(fast.engine.pool.state, slow.engine.pool.state)
+        assert float((a.float() - b.float()).abs().max()) <= 1e-2 * float(b.float().abs().max())
 
 
 def test_prefix_checkpoint_restores_the_index_without_a_rebuild():
