@@ -126,9 +126,6 @@ typedef struct pqhsa_params {
                               bits, list id, j) - a contiguous copy of what the threshold estimate reads, to
                               be refreshed whenever the sorted region changes; NULL = gather from the index.
                               Only read for streams with more than PQHSA_SAMPLE_KEYS sorted slots. */
-  const void *sample_start;/* int32 [S, PQHSA_MAX_LISTS + 1], required with sample: index of the first sample
-                              record of list l (records are in slot order, hence sorted by list);
-                              entry num_lists = 4096 */
 
   const void *k_base, *v_base;
   const int32_t *block_table;
@@ -175,12 +172,11 @@ typedef struct pqhsa_ws_layout {
   size_t lut;          /* float  [S, G, 8, 16]   scale * <q_m, code word>                 */
   size_t list_scores;  /* float  [S, G, 512]     scale * <q, centroid>                    */
   size_t pair_tab;     /* float  [S, G/GP, 4, 256, GP], GP = min(G, 4): byte-pair sums of lut for the scan */
-  size_t row_bin;      /* float  [R, 2]   origin (= row_tau) and 1 / width of the candidate bins of the selection */
+  size_t row_bin;      /* float  [R, 2]   origin (= row_tau) and 1 / width of the candidate bins of the selection
+                          ((size_t)-1 in a hand-made layout: no thresholds wanted)       */
   size_t row_tau;      /* float  [R]      candidate threshold on the approximate logit     */
   size_t ticket;       /* int32  [S, 2]   arrival counters of the table kernel's CTAs (0 between launches) */
-  size_t slog;         /* float  [R, PQHSA_SAMPLE_KEYS]  approximate logits of the sample keys           */
   size_t norm_pend;    /* float  [S]      norm of a key encoded in the current launch                    */
-  size_t enc_best;     /* float  [S, 16, 2]  nearest list of the key being encoded, per list CTA of the table kernel */
   size_t unit_max;     /* float  [R, unit_capacity]   per-unit max logit                   */
   size_t unit_sum;     /* float  [R, unit_capacity]   per-unit sum exp(logit - max), selected keys removed */
   size_t tail_logit;   /* float  [R, tail capacity]   logits of the unsorted tail (-inf once selected) */

@@ -38,7 +38,7 @@ class Params(C.Structure):
         ("slot_unit", C.c_void_p), ("unit_off", C.c_void_p), ("unit_list", C.c_void_p),
         ("coarse", C.c_void_p), ("codebooks", C.c_void_p), ("vmeans", C.c_void_p),
         ("vsum", C.c_void_p), ("vcnt", C.c_void_p), ("state", C.c_void_p), ("norm_max", C.c_void_p),
-        ("sample", C.c_void_p), ("sample_start", C.c_void_p),
+        ("sample", C.c_void_p),
         ("k_base", C.c_void_p), ("v_base", C.c_void_p), ("block_table", C.c_void_p),
         ("max_blocks", C.c_int32), ("block_size", C.c_int32),
         ("stride_block", C.c_int64), ("stride_head", C.c_int64), ("stride_row", C.c_int64),
@@ -54,7 +54,7 @@ class WsLayout(C.Structure):
     _fields_ = [
         ("total_bytes", C.c_size_t), ("lut", C.c_size_t), ("list_scores", C.c_size_t), ("pair_tab", C.c_size_t),
         ("row_bin", C.c_size_t),
-        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("slog", C.c_size_t), ("norm_pend", C.c_size_t), ("enc_best", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
+        ("row_tau", C.c_size_t), ("ticket", C.c_size_t), ("norm_pend", C.c_size_t), ("unit_max", C.c_size_t), ("unit_sum", C.c_size_t),
         ("tail_logit", C.c_size_t), ("row_info", C.c_size_t), ("hitmap", C.c_size_t),
         ("cand_key", C.c_size_t), ("cand_rec", C.c_size_t), ("cand_bin", C.c_size_t),
         ("part_hist", C.c_size_t), ("part_cnt", C.c_size_t),

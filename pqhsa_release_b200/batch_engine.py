@@ -148,7 +148,7 @@ class PagedBatchEngine:
     # ---- prefix checkpoints (benchmarks/e2e_pq_param_sweep.py:3358-3432, :3735-3899) -------------------
     _SNAP_SLOT = ("codes", "norms", "list_ids", "slot_pos", "slot_unit")
     _SNAP_FULL = ("unit_off", "unit_list", "coarse", "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max",
-                  "sample", "sample_start")
+                  "sample")
 
     def _checkpoint(self, slot: int, pkey, length: int) -> None:
         p = self.pool

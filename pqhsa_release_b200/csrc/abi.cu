@@ -81,9 +81,7 @@ void layout_of(const pqhsa_params* p, pqhsa_ws_layout* o) {
   o->row_bin = take(R * 2 * sizeof(float));
   o->row_tau = take(R * sizeof(float));
   o->ticket = take(2 * S * sizeof(int32_t));
-  o->slog = take(R * kSample * sizeof(float));
   o->norm_pend = take(S * sizeof(float));
-  o->enc_best = take(S * 16 * 2 * sizeof(float));
   o->unit_max = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->unit_sum = take(R * (size_t)p->unit_capacity * sizeof(float));
   o->tail_logit = take(R * (size_t)o->tail_cap * sizeof(float));
@@ -129,8 +127,6 @@ int check_params(const pqhsa_params* p, bool need_ws, bool need_kv, bool need_io
   if (!p->codes || !p->norms || !p->list_ids || !p->slot_pos || !p->slot_unit || !p->unit_off || !p->unit_list ||
       !p->coarse || !p->codebooks || !p->vmeans || !p->state || !p->norm_max)
     return set_error(PQHSA_E_NULL, "an index pool pointer is null");
-  if (p->sample != nullptr && p->sample_start == nullptr)
-    return set_error(PQHSA_E_NULL, "sample needs sample_start");
   if (need_kv) {
     if (!p->k_base || !p->v_base) return set_error(PQHSA_E_NULL, "k_base / v_base is null");
     if (p->block_table != nullptr && (p->block_size <= 0 || p->max_blocks <= 0))

@@ -417,11 +417,6 @@ __global__ void __launch_bounds__(kAttThreads, 6) attend_kernel(const AttendArgs
   }
 }
 
-// One CTA per query row folds the row's partials (exact chunks + background) into the output row:
-// out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M)  (pq_attend_reduce_mw,
-// pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).  Thread d owns output dim d.  Everything a thread needs
-// of the first 32 partials - their (max, sum) pairs, which every thread of a warp reads from the same
-// addresses, and its own dim of their accumulators - is requested at once: one round trip, no barrier.
 // A flagged word: 8 bytes stored and loaded as one transaction (the data and the step count that says it is there).
 __device__ __forceinline__ void store_flagged(uint2* p, uint32_t data, uint32_t flag) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
@@ -432,42 +427,47 @@ __device__ __forceinline__ uint2 load_flagged(const uint2* p) {
   return v;
 }
 
+// One CTA per query row folds the row's partials (exact chunks + background) into the output row:
+// out = sum_p acc_p 2^(m_p - M) / sum_p l_p 2^(m_p - M)  (pq_attend_reduce_mw,
+// pq_hsa/kernels/cuda/pq_fused_h20.cu:2244-2402).  Thread d owns output dim d.  Everything a thread needs
+// of 32 partials - their (max, sum) pairs, which every thread of a warp reads from the same
+// addresses, and its own dim of their accumulators - is requested at once: one round trip per 32 partials, no barrier.
 template <typename E>
 __global__ void __launch_bounds__(kD) combine_kernel(const AttendArgs a) {
   const int row = blockIdx.x, tid = threadIdx.x;
   const int slots = a.chunks + a.bg_parts;  // <= kD, checked with the parameters; empty chunks carry (-inf, 0)
   const float* pp = a.partial + (size_t)row * (a.chunks + kBgParts) * kPartial;
-  constexpr int kFirst = 32;
-  float m[kFirst], l[kFirst], v[kFirst];
+  // 32 partials at a time, all of a batch requested at once (one round trip per batch; c2 has 27 partials per row,
+  // a row of 5243 selected keys 47); the batches are folded into a running (max, sum, acc)
+  constexpr int kBatch = 32;
+  float M = kNegInf, L = 0.f, A = 0.f;
+  for (int p0 = 0; p0 < slots; p0 += kBatch) {
+    float m[kBatch], l[kBatch], v[kBatch];
 #pragma unroll
-  for (int p = 0; p < kFirst; ++p) {
-    m[p] = kNegInf;
-    l[p] = 0.f;
-    v[p] = 0.f;
-    if (p < slots) {
-      m[p] = __ldcg(pp + (size_t)p * kPartial);
-      l[p] = __ldcg(pp + (size_t)p * kPartial + 1);
-      v[p] = __ldcg(pp + (size_t)p * kPartial + 2 + tid);
+    for (int p = 0; p < kBatch; ++p) {
+      m[p] = kNegInf;
+      l[p] = 0.f;
+      v[p] = 0.f;
+      if (p0 + p < slots) {
+        m[p] = __ldcg(pp + (size_t)(p0 + p) * kPartial);
+        l[p] = __ldcg(pp + (size_t)(p0 + p) * kPartial + 1);
+        v[p] = __ldcg(pp + (size_t)(p0 + p) * kPartial + 2 + tid);
+      }
     }
-  }
-  float M = m[0];
+    float Mb = m[0];
 #pragma unroll
-  for (int p = 1; p < kFirst; ++p) M = fmaxf(M, m[p]);
-  float L = 0.f, A = 0.f;
+    for (int p = 1; p < kBatch; ++p) Mb = fmaxf(Mb, m[p]);
+    if (Mb == kNegInf) continue;  // a batch of empty chunks
+    const float Mn = fmaxf(M, Mb);
+    const float fo = (M == kNegInf) ? 0.f : ex2(M - Mn);
+    L *= fo;
+    A *= fo;
 #pragma unroll
-  for (int p = 0; p < kFirst; ++p) {
-    const float f = (m[p] == kNegInf) ? 0.f : ex2(m[p] - M);
-    L = fmaf(l[p], f, L);
-    A = fmaf(v[p], f, A);
-  }
-  for (int p = kFirst; p < slots; ++p) {  // long rows: the remaining partials one by one
-    const float mp = __ldcg(pp + (size_t)p * kPartial);
-    if (mp == kNegInf) continue;
-    const float lp = __ldcg(pp + (size_t)p * kPartial + 1), vp = __ldcg(pp + (size_t)p * kPartial + 2 + tid);
-    const float Mn = fmaxf(M, mp);
-    const float fo = (M == kNegInf) ? 0.f : ex2(M - Mn), fn = ex2(mp - Mn);
-    L = L * fo + lp * fn;
-    A = A * fo + vp * fn;
+    for (int p = 0; p < kBatch; ++p) {
+      const float f = (m[p] == kNegInf) ? 0.f : ex2(m[p] - Mn);
+      L = fmaf(l[p], f, L);
+      A = fmaf(v[p], f, A);
+    }
     M = Mn;
   }
   const E res = from_f<E>(A / fmaxf(L, 1.17549435e-38f));

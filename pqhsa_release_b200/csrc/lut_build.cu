@@ -62,8 +62,7 @@ struct LutArgs {
   const void* norms;
   const uint16_t* list_ids;
   const int4* sample;  // [S, kSample] (code, norm as float bits, list, slot) of the stratified sample, or null
-  const int32_t* sample_start;  // [S, kLMax + 1] first sample record of every list
-  float* slog;         // [R, kSample] logits of the sample keys, or null: no threshold wanted
+  int want_tau;        // 1: thresholds wanted
   float* norm_max_rw;
   float* lut;
   float* pair_tab;  // [S, G / GP, 4, 256, GP] byte-pair sums of the tables for the scan, GP = min(G, 4); or null
@@ -71,7 +70,6 @@ struct LutArgs {
   float* row_bin;
   float* row_tau;
   int32_t* ticket;
-  float2* enc_best;  // [S, 16] nearest list of the key being encoded among each list CTA's lists: (distance, list as int bits)
   int num_lists, cap, G;
   float scale;
   double top_fraction;
@@ -417,7 +415,7 @@ __global__ void __launch_bounds__(kLutThreads, 2) lut_build_kernel(const LutArgs
     const int share = ((a.num_lists + G - 1) / G + kLutWarps - 1) / kLutWarps * kLutWarps;  // rows per CTA, whole warps
     const int l_begin = min(j * share, a.num_lists), l_end = min(l_begin + share, a.num_lists);
     const int nmy = (l_end - l_begin + R::kLPS - 1) / R::kLPS;
-    const bool want_tau = a.slog != nullptr && a.sample != nullptr;
+    const bool want_tau = a.want_tau != 0 && a.sample != nullptr;
     const int4* sample = a.sample + (size_t)s * kSample;
     const int total = nmy + (want_tau ? R::kSampleChunks : 0);
     auto issue = [&](int c) {  // one group per call, empty or not: the waits count groups
@@ -645,10 +643,9 @@ static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const
   a.lut = reinterpret_cast<float*>(ws + w.lut);
   a.pair_tab = w.pair_tab == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.pair_tab);
   a.list_scores = reinterpret_cast<float*>(ws + w.list_scores);
-  a.row_bin = reinterpret_cast<float*>(ws + w.row_bin);
+  a.row_bin = w.row_bin == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.row_bin);
   a.row_tau = reinterpret_cast<float*>(ws + w.row_tau);
   a.ticket = reinterpret_cast<int32_t*>(ws + w.ticket);
-  a.enc_best = w.enc_best == (size_t)-1 ? nullptr : reinterpret_cast<float2*>(ws + w.enc_best);
   a.num_lists = p.num_lists;
   a.cap = p.slot_capacity;
   a.G = p.group;
@@ -657,8 +654,7 @@ static void fill_lut_args(const pqhsa_params& p, const pqhsa_ws_layout& w, const
   a.topk_fixed = p.topk_fixed;
   a.margin = p.select_margin;
   a.sample = static_cast<const int4*>(p.sample);
-  a.sample_start = static_cast<const int32_t*>(p.sample_start);
-  a.slog = w.slog == (size_t)-1 ? nullptr : reinterpret_cast<float*>(ws + w.slog);
+  a.want_tau = w.row_bin == (size_t)-1 ? 0 : 1;
   a.norm_max_rw = static_cast<float*>(p.norm_max);
   a.k_base = const_cast<void*>(p.k_base);
   a.v_base = const_cast<void*>(p.v_base);
@@ -693,7 +689,7 @@ static int launch_lut_build_t(const pqhsa_params& p, LutArgs& a, cudaStream_t st
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kern, (const LutArgs)a) != cudaSuccess) return check_launch("lut_build");
   if (int rc = check_launch("lut_build")) return rc;
-  if (a.slog == nullptr || a.sample != nullptr) return PQHSA_OK;  // no threshold wanted, or placed by the first kernel
+  if (!a.want_tau || a.sample != nullptr) return PQHSA_OK;  // no threshold wanted, or placed by the first kernel
   tau_kernel<E><<<p.num_streams * p.group, kLutThreads, 0, st>>>(a);
   return check_launch("tau");
 }

@@ -83,11 +83,9 @@ extern "C" int pqhsa_scan_scores_static(const pqhsa_params* p, float* scores, vo
   w.total_bytes = kStaticBytes;
   w.lut = kOffLut;
   w.pair_tab = (size_t)-1;  // only the full scan reads pair tables
-  w.slog = (size_t)-1;      // ... and thresholds
   w.norm_pend = (size_t)-1;
-  w.enc_best = (size_t)-1;
   w.list_scores = kOffListScores;
-  w.row_bin = kOffRowBin;
+  w.row_bin = (size_t)-1;  // ... and thresholds
   w.row_tau = kOffRowTau;
   w.ticket = kOffTicket;
   w.row_info = kOffRowInfo;

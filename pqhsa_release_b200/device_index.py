@@ -136,7 +136,6 @@ class DeviceIndexPool:
         self.state = torch.zeros(S, _lib.STATE_INTS, dtype=torch.int32, device=dev)
         # contiguous copy of the slots the threshold estimate samples: (code, norm bits, list, slot)
         self.sample = torch.zeros(S, _lib.SAMPLE_KEYS, 4, dtype=torch.int32, device=dev)
-        self.sample_start = torch.zeros(S, _lib.MAX_LISTS + 1, dtype=torch.int32, device=dev)
         # host mirrors of the device counters (every update is deterministic)
         self.h_sorted = np.zeros(S, dtype=np.int64)
         self.h_tail = np.zeros(S, dtype=np.int64)
@@ -157,7 +156,7 @@ class DeviceIndexPool:
         p.hist_inv_width = 0.0 if hist_width is None else float(1.0 / hist_width)
         p.select_margin = float(select_margin)
         for name in ("codes", "norms", "list_ids", "slot_pos", "slot_unit", "unit_off", "unit_list", "coarse",
-                     "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max", "sample", "sample_start"):
+                     "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max", "sample"):
             setattr(p, name, getattr(self, name).data_ptr())
         self.p = p
         self.layout = WsLayout()
@@ -229,9 +228,6 @@ class DeviceIndexPool:
         rec[:, 1] = self.norms[s][j].float().view(torch.int32)
         rec[:, 2] = self.list_ids[s][j].to(torch.int32) & 0xFFFF
         rec[:, 3] = j.to(torch.int32)
-        # first record of every list (records are in slot order = sorted by list)
-        lists = torch.arange(_lib.MAX_LISTS + 1, device=self.device, dtype=torch.int32)
-        self.sample_start[s] = torch.searchsorted(rec[:, 2].contiguous(), lists).to(torch.int32)
 
     def export_stream(self, s: int) -> dict[str, torch.Tensor]:
         """Slots of stream ``s`` back in token order (for tests and state dicts)."""

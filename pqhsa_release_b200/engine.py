@@ -372,7 +372,7 @@ class PoolAttention:
     # ---- prefix checkpoint (benchmarks/e2e_pq_param_sweep.py:3358-3432, :3735-3899) ---------------------
     _SNAP_SLOT = ("codes", "norms", "list_ids", "slot_pos", "slot_unit")
     _SNAP_FULL = ("unit_off", "unit_list", "coarse", "codebooks", "vmeans", "vsum", "vcnt", "state", "norm_max",
-                  "sample", "sample_start")
+                  "sample")
 
     def snapshot(self) -> dict:
         """Device-side copy of everything the index holds (slot arrays up to the longest stream, tables,
