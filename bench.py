@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(workloads.WORKLOADS) + ["encode_bulk"])
     ap.add_argument("--context", type=int, default=None, help="override the context length (debugging)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (debugging)")
     ap.add_argument("--layers", type=int, default=None, help="layers of workload c4 (default 80)")
@@ -876,11 +876,67 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_encode_bulk(args):
+    """``--workload encode_bulk``: the bulk encode kernel (the pass that ends an index build or a codebook-moving
+    refresh: every key assigned to its nearest list and PQ-encoded) on seeded synthetic keys of the c2 index size,
+    and whole ``build_index_batch`` / ``online_refresh_batch`` calls around it.  One JSON line of its own."""
+    from pqhsa_release_b200.config import paper_index_config
+    from pqhsa_release_b200.index_build import build_index_batch, encode_bulk, online_refresh_batch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    streams, keys, lists, dt = (args.batch or 4) * 8, (args.context or 131072) - 132, 512, torch.bfloat16
+    iters = max(3, min(args.steps, 20))
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn(streams, keys, 128, device="cuda", generator=gen).to(dt)
+    coarse = torch.nn.functional.normalize(torch.randn(streams, lists, 128, device="cuda", generator=gen), dim=-1).to(dt)
+    books = (0.1 * torch.randn(streams, 8, 16, 16, device="cuda", generator=gen)).to(dt)
+    for _ in range(max(args.warmup, 1)):
+        encode_bulk(k, coarse, books)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(iters):
+        encode_bulk(k, coarse, books)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / iters
+    del k, coarse, books
+    cfg = paper_index_config(num_lists=lists)
+    kk = torch.randn(streams, keys + 256, 128, device="cuda").to(dt)
+    vv = torch.randn(streams, keys + 256, 128, device="cuda").to(dt)
+    build_index_batch(kk[:, :4096], vv[:, :4096], cfg)  # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    built = build_index_batch(kk[:, :keys], vv[:, :keys], cfg)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    cur = [{"coarse": b.coarse_centroids, "codebooks": b.codebooks} for b in built]
+    online_refresh_batch(kk, vv, cur, 256, cfg)
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    pairs = streams * keys * lists * 128
+    fp32_issue = 148 * 128 * 1.965e9 / 2  # subtract + fma per pair: nominal, there is no measured fp32 peak
+    print(json.dumps({
+        "metric": "index_encode_keys_per_s", "value": streams * keys / (ms / 1e3), "unit": "keys/s", "n_gpus": 1,
+        "steps": iters, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "encode_bulk: index build / refresh pass at the c2 index size", "streams": streams,
+                   "keys_per_stream": keys, "lists": lists, "element": "bf16"},
+        "roofline": {"bound": "fp32 issue (nominal)", "achieved": pairs / (ms / 1e3) / 1e12, "peak": fp32_issue / 1e12,
+                     "unit": "T subtract-fma pairs/s", "frac": pairs / (ms / 1e3) / fp32_issue, "traffic": None},
+        "build_index_batch_ms": (t1 - t0) * 1e3, "online_refresh_batch_ms": (t2 - t1) * 1e3,
+        "note": "whole calls: wall clock around a device synchronise",
+    }))
+
+
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
     elif a.workload in ("c3", "c4"):
         run_paged_plugin(a)
+    elif a.workload == "encode_bulk":
+        run_encode_bulk(a)
     else:
         run_b200(a)

@@ -233,59 +233,3 @@ def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list
         )
         for i in range(s)
     ]
-
-
-def _time_encode_bulk(streams: int, keys: int, lists: int, iters: int, dtype: torch.dtype) -> float:
-    """Milliseconds per ``encode_bulk`` call on seeded synthetic keys (CUDA events, after one warm-up)."""
-    gen = torch.Generator(device="cuda").manual_seed(0)
-    k = torch.randn(streams, keys, 128, device="cuda", generator=gen).to(dtype)
-    coarse = torch.nn.functional.normalize(torch.randn(streams, lists, 128, device="cuda", generator=gen), dim=-1).to(dtype)
-    books = (0.1 * torch.randn(streams, 8, 16, 16, device="cuda", generator=gen)).to(dtype)
-    encode_bulk(k, coarse, books)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record()
-    for _ in range(iters):
-        encode_bulk(k, coarse, books)
-    stop.record()
-    torch.cuda.synchronize()
-    return start.elapsed_time(stop) / iters
-
-
-if __name__ == "__main__":
-    import argparse
-
-    ap = argparse.ArgumentParser(description="time the bulk encode kernel on synthetic keys")
-    ap.add_argument("--streams", type=int, default=32)
-    ap.add_argument("--keys", type=int, default=130940)
-    ap.add_argument("--lists", type=int, default=512)
-    ap.add_argument("--iters", type=int, default=5)
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"])
-    ap.add_argument("--build", action="store_true", help="also time a whole build_index_batch and a refresh")
-    ns = ap.parse_args()
-    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[ns.dtype]
-    if ns.build:
-        import time
-
-        from .config import paper_index_config
-
-        cfg = paper_index_config(num_lists=ns.lists)
-        kk = torch.randn(ns.streams, ns.keys + 256, 128, device="cuda").to(dt)
-        vv = torch.randn(ns.streams, ns.keys + 256, 128, device="cuda").to(dt)
-        build_index_batch(kk[:, :4096], vv[:, :4096], cfg)  # warm-up
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        built = build_index_batch(kk[:, : ns.keys], vv[:, : ns.keys], cfg)
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        cur = [{"coarse": b.coarse_centroids, "codebooks": b.codebooks} for b in built]
-        online_refresh_batch(kk, vv, cur, 256, cfg)
-        torch.cuda.synchronize()
-        t2 = time.perf_counter()
-        print(f"build_index_batch streams={ns.streams} keys={ns.keys}: {(t1 - t0) * 1e3:.0f} ms; "
-              f"online_refresh_batch (+256 keys): {(t2 - t1) * 1e3:.0f} ms (wall clock around a device synchronise)")
-        del kk, vv, built, cur
-    ms = _time_encode_bulk(ns.streams, ns.keys, ns.lists, ns.iters, dt)
-    pairs = ns.streams * ns.keys * ns.lists * 128
-    print(f"encode_bulk streams={ns.streams} keys={ns.keys} lists={ns.lists} {ns.dtype}: {ms:.3f} ms/call, "
-          f"{ns.streams * ns.keys / ms / 1e3:.1f} M keys/s, {pairs / ms / 1e9:.2f} T subtract-fma pairs/s")
