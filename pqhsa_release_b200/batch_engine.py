@@ -4,7 +4,7 @@ The reference's vLLM runtime keeps one sidecar per (layer, request) and loops th
 decode step in Python (benchmarks/vllm_backend/pq_hsa_batch_decode.py:383-432: per request an
 append launch, a graph replay and a context copy).  Here a layer owns one ``DeviceIndexPool``
 whose streams are (request slot, KV head) pairs; a decode step of any number of requests with
-any mix of context lengths is ONE fused library call - seven launches, the result written
+any mix of context lengths is ONE fused library call - five launches, the result written
 straight into vLLM's output tensor:
 
 * a request keeps its slot for life, whatever row of the batch it sits in at a given step: the

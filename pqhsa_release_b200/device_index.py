@@ -363,7 +363,7 @@ class DeviceIndexPool:
 
     def decode_step_append(self, q: torch.Tensor, new_k: torch.Tensor | None, new_v: torch.Tensor | None,
                            encode: int = 0, out: torch.Tensor | None = None, external: bool = False) -> torch.Tensor:
-        """append_kv(new_k, new_v) + append_encode(encode) + decode_step(q) as one call of seven
+        """append_kv(new_k, new_v) + append_encode(encode) + decode_step(q) as one call of five
         launches (the first kernel does the append, the encode and the tables side by side).
         ``external`` (with new_k None): the caller already stored this step's rows in the cache;
         every live stream's length advances by one."""

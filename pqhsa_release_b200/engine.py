@@ -326,7 +326,7 @@ class PoolAttention:
              out: torch.Tensor | None = None, *, external_write: bool = False) -> torch.Tensor:
         """``append(keys, values)`` followed by ``forward(queries)`` as one fused library call (token row
         write, incremental encode of the keys that leave the local window, tables, scan, selection,
-        attention: seven launches), with the bookkeeping of :meth:`append`.  ``external_write``: the
+        attention: five launches), with the bookkeeping of :meth:`append`.  ``external_write``: the
         caller's own cache write already stored the row (vLLM's pages), only the length advances."""
         if self.pool is None:
             raise RuntimeError("build_cache must be called first")
