@@ -549,8 +549,8 @@ class OracleStream:
         centroids and the code words by one EMA step (benchmarks/e2e_pq_param_sweep.py:3173-3220, PQ part
         :2454-2513), then ONLY those keys are assigned and encoded against the moved codebooks (:3222-3256) -
         old list ids and codes stay - and the value means are merged count-weighted (:3259-3281).
-        PARITY UNPINNED for this method: the reference code needs CUDA tensors (:3049-3054), so no fixture of
-        the reference itself could be generated; it follows the cited lines in fp32."""
+        Pinned by tests/golden/golden_flush_incremental.npz: the reference's own method run on CPU tensors
+        (tests/golden/make_golden.py, ``production_flush``), which this reproduces bit for bit."""
         if not self.deferred_pending:
             return False
         self.deferred_pending = False

@@ -144,6 +144,74 @@ def adapter_state(ref_root: str) -> None:
     print("adapter state bytes", (HERE / "golden_adapter_state.pt").stat().st_size)
 
 
+FLUSH_CASE = dict(seed=91, heads=2, context=1400, appends=37, lists=48, interval=32)
+
+
+def flush_inputs():
+    """(keys [H, S + U, D], values) in fp32 holding bf16-representable values."""
+    c = FLUSH_CASE
+    kk, vv = workloads.mixture_kv(c["seed"], c["heads"], c["context"] + c["appends"], dtype=torch.bfloat16, components=16)
+    return kk.float(), vv.float()
+
+
+def production_flush(ref_root: str) -> None:
+    """``golden_flush_incremental.npz``: the PRODUCTION deferred flush of the reference
+    (``GQAIVFPQDecodeAttentionAdapter._apply_pending_batched`` with PQ_HSA_INCREMENTAL_FLUSH=1,
+    benchmarks/e2e_pq_param_sweep.py:3021-3344) run on CPU tensors.  The method itself has no device test;
+    what keeps it off the CPU in the reference is that only the CUDA decode path fills the shared K/V
+    buffers it reads.  Here the adapter is built by the reference's own CPU path (one stream per head),
+    tokens are appended until the deferred update is pending, and the shared buffers are then set to the
+    very K/V rows the streams hold - after which the unmodified method runs.  ``datasets`` is not
+    installed in the build container and is stubbed for the import of the benchmark module (nothing on
+    this path calls it)."""
+    import types
+
+    sys.path.insert(0, ref_root)
+    if "datasets" not in sys.modules:
+        stub = types.ModuleType("datasets")
+        stub.load_dataset = lambda *a, **k: None
+        sys.modules["datasets"] = stub
+    os.environ["PQ_HSA_INCREMENTAL_FLUSH"] = "1"
+    from benchmarks.e2e_pq_param_sweep import GQAIVFPQDecodeAttentionAdapter
+    from pq_hsa.attention.sparse_attention import SparseAttentionConfig
+    from pq_hsa.index.ivfpq import IVFPQConfig
+
+    c = FLUSH_CASE
+    H, S, U = c["heads"], c["context"], c["appends"]
+    K, V = flush_inputs()
+    ic = IVFPQConfig(num_lists=c["lists"], nprobe=64, num_subspaces=8, num_bits=4, residual=True, coarse_max_iter=1,
+                     pq_max_iter=2, pack_codes=True, topk_block_size=1024, kernel_backend="torch", rotation="none",
+                     direction_normalize=True, seed=0)
+    ac = SparseAttentionConfig(sink_tokens=4, local_window=128, retrieval_top_fraction=0.05, exact_rerank=True,
+                               mode="hybrid", hybrid_value_mode="centroid", hybrid_topk_source="all_pq",
+                               hybrid_denominator_source="all_pq", index_update_interval=c["interval"],
+                               index_update_strategy="deferred", collect_attention_details=False)
+    ad = GQAIVFPQDecodeAttentionAdapter(ic, ac, num_query_heads=2 * H, num_key_value_heads=H)
+    ad.build_cache(K[None, :, :S], V[None, :, :S])
+    for t in range(U):
+        ad.append(K[None, :, S + t], V[None, :, S + t])
+    caches = [s.cache for s in ad._streams]
+    assert all(bool(x._deferred_index_update_pending) for x in caches)
+    ad._shared_base_keys, ad._shared_base_vals, ad._shared_base_fallback = K.clone(), V.clone(), False
+    for h, x in enumerate(caches):
+        x._key_buf, x._val_buf = ad._shared_base_keys[h], ad._shared_base_vals[h]
+    old_n = int(caches[0].index.num_vectors)
+    assert ad._apply_pending_batched() == H, "the batched flush refused its preconditions"
+    out = {"input_checksum": np.float64(checksum(K, V)), "old_indexed": np.int64(old_n)}
+    for h, x in enumerate(caches):
+        ix = x.index
+        out[f"packed_codes_{h}"] = ix.packed_codes.numpy().copy()
+        out[f"list_ids_{h}"] = ix.list_ids.to(torch.int32).numpy().copy()
+        out[f"key_norms_{h}"] = ix.key_norms.numpy().copy()
+        out[f"coarse_{h}"] = ix.coarse_centroids.numpy().copy()
+        out[f"codebooks_{h}"] = ix.pq.codebooks.numpy().copy()
+        out[f"value_means_{h}"] = x.retrieval_value_centroids.numpy().copy()
+    np.savez_compressed(HERE / "golden_flush_incremental.npz", **out)
+    print("production flush: indexed", old_n, "->", int(caches[0].index.num_vectors), "bytes",
+          (HERE / "golden_flush_incremental.npz").stat().st_size)
+
+
 if __name__ == "__main__":
     adapter_state(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])
+    production_flush(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])
     main(sys.argv[1] if len(sys.argv) > 1 else os.environ["PQHSA_REFERENCE"])  # a checkout of the reference

@@ -106,3 +106,37 @@ def test_topk_count_is_ceil_in_double():
     assert resolve_topk(130940, 0.02) == 2619
     assert resolve_topk(100, 1.0) == 100
     assert resolve_topk(5, None, 100) == 5
+
+
+def test_production_flush_is_bit_exact():
+    """The oracle's restatement of the production deferred flush (codebook EMA over the keys that left the
+    local window, only those keys encoded, count-weighted value means: benchmarks/e2e_pq_param_sweep.py:3021-3344)
+    against what the reference's own method produced on the same inputs (tests/golden/make_golden.py,
+    ``production_flush``): every index tensor of every head, bit for bit."""
+    from make_golden import FLUSH_CASE, flush_inputs
+
+    from oracle.pqhsa_oracle import OracleAttentionConfig, OracleIndexConfig, OracleStream
+
+    g = np.load(HERE / "golden" / "golden_flush_incremental.npz")
+    K, V = flush_inputs()
+    assert checksum(K, V) == pytest.approx(float(g["input_checksum"]), rel=1e-12)
+    c = FLUSH_CASE
+    S, U = c["context"], c["appends"]
+    for h in range(c["heads"]):
+        st = OracleStream(
+            OracleIndexConfig(num_lists=c["lists"]),
+            OracleAttentionConfig(sink_tokens=4, local_window=128, retrieval_top_fraction=0.05,
+                                  index_update_interval=c["interval"], index_update_strategy="deferred"),
+        ).build_cache(K[h, :S], V[h, :S])
+        assert st.index.list_ids.numel() == int(g["old_indexed"])
+        for t in range(U):
+            st.append(K[h, S + t], V[h, S + t])
+        assert st.deferred_pending and st.apply_pending_incremental_flush()
+        ix = st.index
+        assert ix.list_ids.numel() == int(g["old_indexed"]) + U
+        assert np.array_equal(ix.packed.numpy(), g[f"packed_codes_{h}"])
+        assert np.array_equal(ix.list_ids.numpy(), g[f"list_ids_{h}"])
+        assert np.array_equal(ix.norms.numpy(), g[f"key_norms_{h}"])
+        assert np.array_equal(ix.coarse.numpy(), g[f"coarse_{h}"])
+        assert np.array_equal(ix.codebooks.numpy(), g[f"codebooks_{h}"])
+        assert np.array_equal(st.value_means.numpy(), g[f"value_means_{h}"])
