@@ -127,7 +127,7 @@ __device__ __forceinline__ void enc_best_of_cta(float& bd, int& bl, EncodeShared
 template <typename E, int THREADS>
 __device__ __forceinline__ void enc_nearest_list(const E* __restrict__ coarse, int l_begin, int l_end, int nl,
                                                  EncodeShared<THREADS>& sh, float& out_d, int& out_l) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   const int sub = tid & 3, grp = tid >> 2;  // groups of 4 lanes
   constexpr int kGroups = THREADS / 4;
   constexpr int kVecs = 32 * (int)sizeof(E) / 16;  // 16-byte vectors per 32 dims

@@ -57,8 +57,6 @@ constexpr int kBoundCap = kSelThreads * kBoundPer;  // boundary keys resolved in
 constexpr int kSelWords = 8;                        // hit words a thread holds at a time
 constexpr int kSelBatch = 8;                        // candidates a thread holds at a time
 constexpr int kSelVecs = 4;                         // 8-candidate bin vectors a thread holds at a time
-constexpr int kSlotBits = 22;                       // a list entry is slot | list << 22
-constexpr uint32_t kSlotMask = (1u << kSlotBits) - 1u;
 
 struct SelectArgs {
   const uint32_t* codes;
