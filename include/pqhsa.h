@@ -31,6 +31,7 @@ extern "C" {
 #define PQHSA_HEAD_DIM 128
 #define PQHSA_MAX_LISTS 512
 #define PQHSA_UNIT_KEYS 128     /* a scan unit = at most this many slots of one list */
+#define PQHSA_COMPACT_MAX_TAIL 4096 /* tail slots per stream one pqhsa_compact call can fold in */
 #define PQHSA_SAMPLE_KEYS 4096  /* keys scored per stream to place the candidate threshold */
 #define PQHSA_HIST_BINS 2048    /* resolution of the sample histogram */
 #define PQHSA_SELECT_BINS 1024  /* candidate bins between the threshold and its upper companion; one more above */
@@ -299,6 +300,15 @@ int pqhsa_launch_empty(int32_t count, void* stream);
  * stores over NVLink from inside the combine kernel.  The reference has no counterpart (it runs
  * under vLLM's own tensor parallelism). */
 int pqhsa_wait_peers(const pqhsa_params* p, void* stream);
+
+/* Fold every stream's unsorted tail back into its list-sorted region, on the device and in place: the keys of a
+ * list stay together in token order (the layout a stable sort by list gives), the scan units, the slots' unit
+ * ids, the sample records and the counters N_SORTED / N_TAIL / N_UNITS are rebuilt.  One CTA per stream, no
+ * scratch memory, no host round trip.  Streams with an empty tail are left alone.  A stream whose tail is longer
+ * than PQHSA_COMPACT_MAX_TAIL (or whose units would not fit unit_capacity) is left as it is and `*error` (device
+ * int32, caller-owned, not cleared by the call) is set to 1.  Replaces the snapshot rebuild after a flush
+ * (benchmarks/e2e_pq_param_sweep.py:4163-4363: stable argsort over all list ids). */
+int pqhsa_compact(const pqhsa_params* p, int32_t* error, void* stream);
 
 /* Write one new K/V row per stream into the cache at position seq_len and bump
  * seq_len (contiguous or paged addressing as above).  new_k/new_v: E [S, 128].

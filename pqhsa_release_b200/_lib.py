@@ -11,6 +11,7 @@ from pathlib import Path
 
 ABI_VERSION = 4
 SUBSPACES, CODES, HEAD_DIM, MAX_LISTS, UNIT_KEYS, SAMPLE_KEYS, HIST_BINS = 8, 16, 128, 512, 128, 4096, 2048
+COMPACT_MAX_TAIL = 4096
 STATE_INTS, ROW_INFO_INTS = 8, 8
 ST_N_SORTED, ST_N_TAIL, ST_SEQ_LEN, ST_N_UNITS, ST_N_LISTS, ST_REQ, ST_KV_HEAD = range(7)
 RI_K, RI_N, RI_NCAND, RI_NSEL, RI_FALLBACK, RI_TIES = range(6)
@@ -77,6 +78,7 @@ EXPORTS = {
     "pqhsa_wait_peers": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "pqhsa_decode_step_append": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_run_stage": (C.c_int, [C.POINTER(Params), C.c_int, C.c_void_p]),
+    "pqhsa_compact": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_append_kv": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p]),
     "pqhsa_append_encode": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p]),
     "pqhsa_encode_bulk": (

@@ -302,6 +302,13 @@ int pqhsa_run_stage(const pqhsa_params* p, int stage, void* stream) {
   }
 }
 
+int pqhsa_compact(const pqhsa_params* p, int32_t* error, void* stream) {
+  if (int rc = check_params(p, false, false, false)) return rc;
+  if (!error) return set_error(PQHSA_E_NULL, "error flag is null");
+  if (!p->slot_unit || !p->unit_off || !p->unit_list) return set_error(PQHSA_E_NULL, "unit arrays are null");
+  return launch_compact(*p, error, (cudaStream_t)stream);
+}
+
 int pqhsa_append_kv(const pqhsa_params* p, const void* new_k, const void* new_v, void* stream) {
   if (int rc = check_params(p, false, true, false)) return rc;
   if (!new_k || !new_v) return set_error(PQHSA_E_NULL, "new_k / new_v is null");

@@ -49,6 +49,7 @@ int launch_merge(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t s
 int launch_wait_peers(const pqhsa_params& p, cudaStream_t st);
 int launch_append_kv(const pqhsa_params& p, const void* k, const void* v, cudaStream_t st);
 int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni, cudaStream_t st);
+int launch_compact(const pqhsa_params& p, int32_t* error, cudaStream_t st);
 int launch_encode_bulk(const void* keys, long long stream_stride, int streams, int n, int dtype, const void* coarse,
                        int num_lists, const void* codebooks, uint32_t* codes, void* norms, uint16_t* list_ids,
                        cudaStream_t st);

@@ -166,6 +166,7 @@ class DeviceIndexPool:
         p.workspace_bytes = int(self.layout.total_bytes)
         self._kv_keepalive = None
         self.graph_headroom = 0
+        self._compact_error = None
 
     # ---- loading ---------------------------------------------------------
     def load_stream(self, s: int, idx: StreamIndexTensors | None, *, seq_len: int, req: int, kv_head: int) -> None:
@@ -458,9 +459,26 @@ class DeviceIndexPool:
         self.h_tail += cnt
 
     def compact(self) -> None:
-        """Merge every stream's tail into its list-sorted region (re-sort by list,
-        rebuild the scan units).  The analogue of the reference's snapshot refresh
-        after a flush (benchmarks/e2e_pq_param_sweep.py:4163-4363)."""
+        """Merge every stream's tail into its list-sorted region and rebuild the scan units: one
+        kernel over all streams, in place, no host round trip (``pqhsa_compact``).  The analogue of the
+        reference's snapshot refresh after a flush (benchmarks/e2e_pq_param_sweep.py:4163-4363)."""
+        if int(self.h_tail.max()) == 0:
+            return
+        if int(self.h_tail.max()) > _lib.COMPACT_MAX_TAIL:
+            self._compact_by_sort()
+            return
+        if self._compact_error is None:
+            self._compact_error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        _lib.call("pqhsa_compact", C.byref(self.p), self._compact_error.data_ptr(), self._stream())
+        self.h_sorted += self.h_tail
+        self.h_tail[:] = 0
+
+    def compact_failed(self) -> bool:
+        """True if a ``compact`` left a stream as it was (never with a pool built by this class)."""
+        return self._compact_error is not None and bool(int(self._compact_error.item()) != 0)
+
+    def _compact_by_sort(self) -> None:
+        """``compact`` for tails too long for the kernel: a stable sort by (list, token position) per stream."""
         for s in range(self.S):
             if self.h_tail[s] == 0:
                 continue

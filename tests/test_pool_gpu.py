@@ -264,3 +264,62 @@ def test_paged_ragged_batch_64_decode_steps():
     b, n = 1, ctxs[1] + steps
     t = torch.arange(ctxs[1], n, device=dev)
     assert bool((kv_cache[0, table[b, t // bs].long(), t % bs].float().abs().sum(-1) > 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_compact_kernel_equals_the_stable_sort(dtype):
+    """pqhsa_compact folds the tails of all streams into their sorted regions in place, without a sort; the
+    layout must be the one a stable sort by (list, token position) gives - every index array, the scan units,
+    the slots' unit ids, the sample records and the counters, bit for bit - for ragged streams, a stream with
+    an empty tail, and tails of different lengths (one longer than a chunk of 1024)."""
+    import copy
+
+    from pqhsa_release_b200 import _lib
+
+    case = make_case(B=3, Hkv=2, G=2, S=6200, L=48, dtype=dtype, seed=37, interval=1, strategy="incremental",
+                     contexts=[6200, 4300, 5000])
+    pool, kc, vc = pool_from_case(case, tail_capacity=2048, extra_slots=2200)
+    gen = torch.Generator().manual_seed(9)
+    S = pool.S
+    # tails of 1500, 700, 0, 40, 1100 and 1 keys: append rows for everybody, encode per-stream counts
+    want = [1500, 700, 0, 40, 1100, 1]
+    steps = max(want)
+    for t in range(steps):
+        nk = torch.randn(S, 128, generator=gen).to(dtype).cuda()
+        nv = torch.randn(S, 128, generator=gen).to(dtype).cuda()
+        pool.append_kv(nk, nv)
+    for s0 in range(0, steps, 500):
+        pool.append_encode([max(0, min(500, w - s0)) for w in want])
+    torch.cuda.synchronize()
+    assert pool.h_tail.tolist() == want
+    # the same pool compacted by the sort
+    ref = copy.copy(pool)
+    for name in ("codes", "norms", "list_ids", "slot_pos", "slot_unit", "unit_off", "unit_list", "state", "sample"):
+        setattr(ref, name, getattr(pool, name).clone())
+    ref.h_sorted, ref.h_tail = pool.h_sorted.copy(), pool.h_tail.copy()
+    ref._compact_by_sort()
+    pool.compact()
+    torch.cuda.synchronize()
+    assert not pool.compact_failed()
+    assert pool.h_tail.tolist() == [0] * S and pool.h_sorted.tolist() == ref.h_sorted.tolist()
+    assert torch.equal(pool.state, ref.state)
+    for s in range(S):
+        n = int(pool.h_sorted[s])
+        u = int(pool.state[s, _lib.ST_N_UNITS])
+        for name in ("codes", "norms", "list_ids", "slot_pos", "slot_unit"):
+            assert torch.equal(getattr(pool, name)[s, :n], getattr(ref, name)[s, :n]), f"stream {s}: {name}"
+        assert torch.equal(pool.unit_off[s, : u + 1], ref.unit_off[s, : u + 1]), f"stream {s}: unit_off"
+        assert torch.equal(pool.unit_list[s, :u], ref.unit_list[s, :u]), f"stream {s}: unit_list"
+        if n > _lib.SAMPLE_KEYS:
+            assert torch.equal(pool.sample[s], ref.sample[s]), f"stream {s}: sample records"
+    # the rest of the appended keys, a second compaction, and the step on the compacted pool against the
+    # same pool before the compaction (the selection is exact either way)
+    for s0 in range(0, steps, 500):
+        pool.append_encode([max(0, min(500, (steps - w) - s0)) for w in want])
+    q = case.queries.cuda().reshape(S, case.G, 128).contiguous()
+    before = pool.decode_step(q).float().cpu()
+    pool.compact()
+    after = pool.decode_step(q).float().cpu()
+    torch.cuda.synchronize()
+    assert not pool.compact_failed() and int(pool.h_tail.max()) == 0
+    assert float((before - after).abs().max()) <= 2e-2 * float(before.abs().max())
