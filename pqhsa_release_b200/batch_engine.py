@@ -118,6 +118,22 @@ class PagedBatchEngine:
         self.free.append(slot)
         self.stats["evictions"] += 1
 
+    def _rollback(self, slot: int, length: int) -> None:
+        """The request keeps its first ``length`` tokens (benchmarks/vllm_backend/pq_hsa_multi_query.py:30-45: the
+        rejected tail of a speculative step disappears).  Only called when the index does not cover a dropped token:
+        the pages are read in place and appended tokens touch nothing but the counters, so the counters go back and
+        that is all.  ``stats["rollbacks"]`` counts the tokens dropped."""
+        drop = int(self.length[slot]) - length
+        if drop <= 0:
+            return
+        st = list(self._streams(slot))
+        self.length[slot] = length
+        self.pending[slot] = max(int(self.pending[slot]) - drop, 0)
+        self.since_flush[slot] = max(int(self.since_flush[slot]) - drop, 0)
+        self.pool.state[st[0] : st[-1] + 1, _lib.ST_SEQ_LEN] = length
+        self.pool.h_seq[st] = length
+        self.stats["rollbacks"] = self.stats.get("rollbacks", 0) + drop
+
     def _install(self, slot: int, row: int, length: int, pkey) -> None:
         """Index of a request that is new to the layer (or jumped): restored from the prefix checkpoint of the
         same prompt, else built from its pages.  ``length`` counts this step's token, which is in the pages."""
@@ -237,10 +253,13 @@ class PagedBatchEngine:
 
     # ---- one decode step of the layer ---------------------------------------------------------------
     def step(self, query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, req_keys: list,
-             seq_lens: list[int], output: torch.Tensor, prompt_keys: list | None = None) -> torch.Tensor:
+             seq_lens: list[int], output: torch.Tensor, prompt_keys: list | None = None,
+             hold_flush: bool = False) -> torch.Tensor:
         """query / output: ``[T, Hq, 128]`` contiguous, one token per request, row i = request ``req_keys[i]`` of
         ``seq_lens[i]`` tokens (this step's token included and already stored in the pages).  Writes the context
-        into ``output`` and returns it."""
+        into ``output`` and returns it.  A request whose length went BACK since its last step (speculative tokens
+        were rejected) keeps its index as long as the index does not cover a dropped token.  ``hold_flush``: no
+        deferred flush after this step (the step's token is not verified yet)."""
         T = len(req_keys)
         if T > self.max_requests:
             raise RuntimeError(f"{T} requests in the step, the layer's pool holds {self.max_requests}")
@@ -270,6 +289,9 @@ class PagedBatchEngine:
             self._h_io[st.start : st.stop] = np.arange(i * self.H, (i + 1) * self.H)
             self._h_req[st.start : st.stop] = i
             prev, prev_indexed = int(self.length[slot]), int(self.indexed_length[slot])
+            if prev >= length and prev_indexed <= length - 1 and prev > 0:
+                self._rollback(slot, length - 1)
+                prev = length - 1
             s0, old_r = self._bounds(max(prev, 0), prev_indexed)
             _, r = self._bounds(length, length)
             sequential = prev + 1 == length
@@ -310,7 +332,7 @@ class PagedBatchEngine:
         self.stats["steps"] += 1
         self.stats["launch_calls"] += 1
         # deferred policy: a request flushes once flush_every tokens have gathered since its last update
-        if self.acfg.index_update_strategy == "deferred" and self.flush_every > 0:
+        if self.acfg.index_update_strategy == "deferred" and self.flush_every > 0 and not hold_flush:
             for key in req_keys:
                 slot = self.slots[key]
                 if self.since_flush[slot] >= self.flush_every:

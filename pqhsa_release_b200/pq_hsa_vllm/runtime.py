@@ -132,7 +132,9 @@ def should_pq_decode(attn_metadata) -> bool:
     if getattr(attn_metadata, "use_cascade", False):
         return reject("cascade")
     if int(getattr(attn_metadata, "max_query_len", 0)) != 1:
-        return reject("max_query_len!=1")
+        if not multi_query_enabled():
+            return reject("max_query_len!=1")
+        return should_pq_decode_mq(attn_metadata)
     seq_lens = getattr(attn_metadata, "seq_lens", None)
     if seq_lens is None:
         return reject("no_seq_lens")
@@ -154,6 +156,41 @@ def should_pq_decode(attn_metadata) -> bool:
     # (benchmarks/vllm_backend/paged_kv_fa.py:15-27)
     if int(getattr(attn_metadata, "max_seq_len", 0)) < min_pq_seq():
         return reject("seq_too_short")
+    return True
+
+
+def multi_query_enabled() -> bool:
+    """PQ_HSA_MULTI_QUERY=1 (default 0): speculative-decoding steps of one request take the PQ path
+    (benchmarks/vllm_backend/pq_hsa_multi_query.py:1-12)."""
+    return os.environ.get("PQ_HSA_MULTI_QUERY", "0") == "1"
+
+
+def should_pq_decode_mq(attn_metadata) -> bool:
+    """Admission of a step with ``T = max_query_len > 1`` query tokens (pq_hsa_multi_query.py:112-160): one
+    request, T within PQ_HSA_MQ_MAX, every token of the step a query token, the committed context long enough,
+    and not a prefill chunk (a chunk starts inside the prompt; a speculative step starts after it)."""
+    seq_lens = getattr(attn_metadata, "seq_lens", None)
+    if seq_lens is None or int(seq_lens.shape[0]) != 1:
+        return reject("mq_num_reqs!=1")
+    T = int(getattr(attn_metadata, "max_query_len", 0))
+    if T < 1 or T > int(os.environ.get("PQ_HSA_MQ_MAX", "8")):
+        return reject("mq_query_len_out_of_range")
+    if int(getattr(attn_metadata, "num_actual_tokens", 0)) != T:
+        return reject("mq_num_actual_tokens!=T")
+    context = batch_seq_lens(attn_metadata)[0] - T
+    if context < min_pq_seq():
+        return reject("seq_too_short")
+    runner = getattr(attn_metadata, "_pq_runner", None)
+    req_ids = getattr(getattr(runner, "input_batch", None), "req_ids", None) if runner is not None else None
+    request = runner.requests.get(req_ids[0]) if req_ids and req_ids[0] is not None and hasattr(runner, "requests") else None
+    if request is None:
+        return reject("mq_no_request")  # without the request a prefill chunk cannot be told from a speculative step
+    prompt = getattr(request, "num_prompt_tokens", None)
+    if prompt is None:
+        ids = getattr(request, "prompt_token_ids", None)
+        prompt = None if ids is None else len(ids)
+    if prompt is None or context < int(prompt):
+        return reject("mq_prefill_chunk")
     return True
 
 
@@ -221,6 +258,8 @@ def run_pq_decode(impl, layer, query, key, value, kv_cache, attn_metadata, outpu
     (pq_hsa_decode_runtime.py:719-787 + :492-716; batch: pq_hsa_batch_decode.py:383-432)."""
     import torch
 
+    if int(getattr(attn_metadata, "max_query_len", 1)) > 1:
+        return run_pq_decode_mq(impl, layer, query, key, value, kv_cache, attn_metadata, output)
     lens = batch_seq_lens(attn_metadata)
     num_reqs = len(lens)
     if any(n < min_pq_seq() for n in lens):
@@ -242,6 +281,46 @@ def run_pq_decode(impl, layer, query, key, value, kv_cache, attn_metadata, outpu
     for k in ("builds", "flushes", "restores", "evictions"):
         STATS[k] += eng.stats[k] - before[k]
     STATS["pq_steps"] += 1
+    return output
+
+
+def run_pq_decode_mq(impl, layer, query, key, value, kv_cache, attn_metadata, output):
+    """A speculative-decoding step of one request: T query tokens at the consecutive positions C .. C + T - 1
+    (pq_hsa_multi_query.py:14-60).  Causality by sequential replay, as there: for j < T the request advances by
+    token C + j (already in the pages) and query j attends with the steady path's sink / local / retrieval
+    semantics - T fused library calls.  Where the reference checkpoints the sidecar before the step and restores
+    it when drafts are rejected, nothing needs saving here: the pages are read in place and an appended token
+    changes only the counters, so the engine takes the request's length back when the next step starts at a
+    lower position (``PagedBatchEngine._rollback``).  No deferred flush runs on an unverified token: the first
+    token of a step is the one the previous step committed, the flush check happens there."""
+    import torch
+
+    T = int(attn_metadata.max_query_len)
+    total = batch_seq_lens(attn_metadata)[0]
+    context = total - T
+    if context < min_pq_seq():
+        raise RuntimeError("request too short for the PQ path")
+    write_step_kv(key, value, kv_cache, attn_metadata)
+    eng = layer_engine(impl, layer, kv_cache, attn_metadata)
+    table = attn_metadata.block_table
+    if table.dtype != torch.int32 or not table.is_contiguous():
+        table = table.to(torch.int32).contiguous()
+    q = query[:T].reshape(T, impl.num_heads, -1).contiguous()
+    direct = output.is_contiguous() and output.dtype == q.dtype and output[:T].numel() == q.numel()
+    out = output[:T].view(q.shape) if direct else torch.empty_like(q)
+    keys = batch_req_keys(attn_metadata, 1)
+    pkeys = prefix_keys(attn_metadata, [total])
+    before = dict(eng.stats)
+    for j in range(T):
+        eng.step(q[j : j + 1], kv_cache, table, keys, [context + j + 1], out[j : j + 1], pkeys if j == 0 else None,
+                 hold_flush=j > 0)
+    if not direct:
+        output[:T].copy_(out.reshape(output[:T].shape))
+    for k in ("builds", "flushes", "restores", "evictions"):
+        STATS[k] += eng.stats[k] - before[k]
+    STATS["pq_steps"] += 1
+    STATS["mq_steps"] = STATS.get("mq_steps", 0) + 1
+    STATS["mq_tokens"] = STATS.get("mq_tokens", 0) + T
     return output
 
 

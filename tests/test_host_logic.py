@@ -233,3 +233,34 @@ def test_reference_checkpoint_layout_is_understood_on_the_host():
     bad = dict(att, leading_shape=(2, 2))
     with pytest.raises(ValueError):
         reference_attention_state(bad, device="cpu")
+
+
+def test_multi_query_admission(monkeypatch):
+    """benchmarks/vllm_backend/pq_hsa_multi_query.py:112-160: a step with several query tokens is taken only with
+    PQ_HSA_MULTI_QUERY=1, for one request, within PQ_HSA_MQ_MAX, when it starts after the prompt."""
+    from types import SimpleNamespace as NS
+
+    import torch
+
+    from pqhsa_release_b200.pq_hsa_vllm import runtime
+
+    runtime.reset()
+    monkeypatch.setenv("PQ_HSA_ENABLE", "1")
+    monkeypatch.delenv("PQ_HSA_BATCH", raising=False)
+    runner = NS(input_batch=NS(req_ids=["r"]), requests={"r": NS(prompt_token_ids=[0] * 900, num_prompt_tokens=900)})
+
+    def md(total, T, n=1):
+        lens = torch.tensor([total] * n, dtype=torch.int32)
+        return NS(use_cascade=False, max_query_len=T, num_actual_tokens=T * n, seq_lens=lens, seq_lens_cpu=lens,
+                  max_seq_len=total, _pq_runner=runner)
+
+    monkeypatch.delenv("PQ_HSA_MULTI_QUERY", raising=False)
+    assert not runtime.should_pq_decode(md(1000, 3))
+    monkeypatch.setenv("PQ_HSA_MULTI_QUERY", "1")
+    assert runtime.should_pq_decode(md(1000, 3))
+    assert not runtime.should_pq_decode(md(1000, 9)), "more query tokens than PQ_HSA_MQ_MAX"
+    assert not runtime.should_pq_decode(md(902, 3)), "the step starts inside the prompt: a prefill chunk"
+    assert not runtime.should_pq_decode(md(1000, 3, n=2)), "one request only"
+    runner.requests.clear()
+    assert not runtime.should_pq_decode(md(1000, 3)), "no request object: a chunk cannot be told from a speculative step"
+    assert runtime.rejects()["mq_prefill_chunk"] == 1 and runtime.rejects()["mq_no_request"] == 1

@@ -215,3 +215,93 @@ def test_steps_the_pq_path_does_not_take_go_to_the_original_forward(monkeypatch)
     runtime.pq_or_dense_forward(original, NS(scale=1.0, num_heads=HQ, num_kv_heads=HKV), object(), None, None, None, None,
                                 bad, output=out)
     assert calls[-1] == "dense" and runtime.STATS["fallbacks"] == 1
+
+
+@pytest.mark.parametrize("layout", ["5d", "4d"])
+def test_speculative_steps_replay_in_order_and_roll_back(layout, monkeypatch):
+    """PQ_HSA_MULTI_QUERY=1: a step of one request carries T = 3 query tokens at consecutive positions (the token
+    the last step committed + two drafts).  Query j must see the prefix and the step's tokens up to its own
+    (benchmarks/vllm_backend/pq_hsa_multi_query.py:14-60) - checked against the oracle holding the engine's index
+    at every length - and after verification only 1 + a tokens survive: the next step starts at a lower position,
+    overwrites the rejected rows in the pages, and the engine takes the length back without rebuilding anything.
+    Single-token steps in between follow the same rule.  Deferred flushes run on committed tokens only."""
+    from pqhsa_release_b200.pq_hsa_vllm import runtime
+
+    for k, v in {"PQ_HSA_MULTI_QUERY": "1", "PQ_HSA_TOP_FRAC": str(FRAC), "PQ_HSA_NUM_LISTS": "64",
+                 "PQ_HSA_FLUSH_INTERVAL": "8", "PQ_HSA_MAX_REQUESTS": "1", "PQ_HSA_MAX_CONTEXT": "8192",
+                 "PQ_HSA_ENABLE": "1", "PQ_HSA_UPD_STRATEGY": "deferred", "PQ_HSA_FALLBACK": "0"}.items():
+        monkeypatch.setenv(k, v)
+    monkeypatch.delenv("PQ_HSA_BATCH", raising=False)
+    runtime.reset()
+    dtype = torch.bfloat16
+    pages = Pages(layout)
+    k0, v0 = workloads.mixture_kv(411, HKV, 3000, dtype=dtype, components=16)
+    qbase = workloads.planted_queries(977, k0, G)
+    pages.add_request("A", k0, v0)
+    runner = NS(input_batch=NS(req_ids=["A"]), requests={"A": NS(prompt_token_ids=[1, 2, 3], num_prompt_tokens=2990)})
+    impl = NS(scale=1.0 / D ** 0.5, num_heads=HQ, num_kv_heads=HKV, kv_cache_dtype="auto")
+    layer = object()
+
+    def original(*a, **kw):
+        raise AssertionError("the step fell through to the dense path: " + str(runtime.rejects()))
+
+    gen = torch.Generator().manual_seed(5)
+
+    def run_step(T):
+        """Append T tokens at the request's current length and run the hook; returns (queries, outputs, C)."""
+        C = pages.len["A"]
+        nk = torch.randn(T, HKV, D, generator=gen).to(dtype)
+        nv = torch.randn(T, HKV, D, generator=gen).to(dtype)
+        for j in range(T):
+            pages.append("A", nk[j], nv[j], write=(layout == "4d"))
+        b = pages.blocks["A"]
+        table = torch.zeros(1, pages.max_blocks, dtype=torch.int32)
+        table[0, : len(b)] = torch.tensor(b, dtype=torch.int32)
+        slots = [b[(C + j) // BS] * BS + (C + j) % BS for j in range(T)]
+        lens = torch.tensor([C + T], dtype=torch.int32)
+        md = NS(use_cascade=False, max_query_len=T, num_actual_tokens=T, seq_lens=lens.cuda(), seq_lens_cpu=lens,
+                max_seq_len=C + T, block_table=table.cuda(), slot_mapping=torch.tensor(slots, dtype=torch.long, device="cuda"),
+                _pq_runner=runner)
+        q = torch.stack([(qbase.float() * (1 + 0.01 * ((C + j) % 7))).to(dtype) for j in range(T)]).cuda()   # [T, Hq, D]
+        out = torch.zeros(T, HQ * D, dtype=dtype, device="cuda")
+        res = runtime.pq_or_dense_forward(original, impl, layer, q, nk.cuda(), nv.cuda(), pages.kv, md, output=out)
+        torch.cuda.synchronize()
+        assert res is out
+        return q, out.view(T, HQ, D).float().cpu(), C
+
+    def check(q, o, C, T):
+        eng = runtime._LAYERS[id(layer)]
+        full_len = pages.len["A"]
+        for j in range(T):
+            pages.len["A"] = C + j + 1                     # the oracle of query j sees the tokens up to its own
+            for h in range(HKV):
+                st = _oracle(eng, pages, "A", h)
+                st.keys, st.values = st.keys[: C + j + 1], st.values[: C + j + 1]
+                det = st.forward_detail(q[j, h * G : (h + 1) * G].float().cpu())
+                for g in range(G):
+                    assert_output_close(o[j, h * G + g], det.output[g], dtype, f"context {C} token {j} head {h * G + g}", l2_bar=3e-3)
+        pages.len["A"] = full_len
+
+    def keep(C, kept):
+        """Verification keeps `kept` of the step's tokens: the request is C + kept tokens long."""
+        pages.len["A"] = C + kept
+        pages.k["A"], pages.v["A"] = pages.k["A"][:, : C + kept], pages.v["A"][:, : C + kept]
+
+    q, o, C = run_step(1)                                  # a plain decode step installs the request
+    check(q, o, C, 1)
+    eng = runtime._LAYERS[id(layer)]
+    compared = 0
+    for it, kept in enumerate([3, 1, 2, 1, 3, 2, 1, 1, 2, 3, 1, 2]):
+        T = 1 if it in (4, 9) else 3                       # single-token steps in between
+        flushes = eng.stats["flushes"]
+        q, o, C = run_step(T)
+        assert bool(torch.isfinite(o).all())
+        if eng.stats["flushes"] == flushes:                # a flush inside the step changes the index under the later queries
+            check(q, o, C, T)
+            compared += 1
+        keep(C, min(kept, T))
+    s = runtime.STATS
+    assert s["dense_steps"] == 0 and s["fallbacks"] == 0 and s["builds"] == 1, "rejections never rebuild the index"
+    assert s["mq_steps"] == 10 and s["mq_tokens"] == 30
+    assert eng.stats["rollbacks"] >= 10 and eng.stats["flushes"] >= 1 and compared >= 6
+    assert s["kv_writes"] == (13 if layout == "5d" else 0)
