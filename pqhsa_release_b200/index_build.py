@@ -121,9 +121,11 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
     if n == 0:
         raise ValueError("cannot build IVF-PQ index with zero keys")
     dtype = keys.dtype
-    kf = keys.float()
-    norms = torch.linalg.vector_norm(kf, dim=-1).to(dtype).clamp_min(cfg.eps)
-    unit = kf / norms.float().unsqueeze(-1)
+    # fp32 working copies are made one at a time and reused in place (directions, then residuals; the values only
+    # at the end): three of them alive at once at the most, against [S, N, 128] inputs
+    unit = keys.to(torch.float32, copy=True)  # a copy also for fp32 keys: it is overwritten below
+    norms = torch.linalg.vector_norm(unit, dim=-1).to(dtype).clamp_min(cfg.eps)
+    unit.div_(norms.float().unsqueeze(-1))
     lists = min(cfg.num_lists, n)
     on_gpu = keys.is_cuda and d == 128 and cfg.num_subspaces == 8 and cfg.num_bits == 4
     if on_gpu:
@@ -135,7 +137,8 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
         _, lid, norms = encode_bulk(keys, coarse, no_books)
     else:
         coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps)
-    resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
+    resid = unit.sub_(torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d)))  # the directions are not needed again
+    del unit
     m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
     books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
     words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
@@ -149,6 +152,7 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
             words |= d2.argmin(dim=-1) << (4 * j)
     if on_gpu:
         words, _, _ = encode_bulk(keys, coarse, books)  # same lists as above: the kernel is deterministic
+    del resid
     vf = values.float()
     vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
     vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
