@@ -339,6 +339,40 @@ int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_strea
                       const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
                       uint16_t* list_ids, void* stream);
 
+/* The same with the lists given: list_ids u16 [num_streams, n] is read (a key's list from an earlier pass against the
+ * same coarse centroids), the nearest-list search is skipped, and codes and norms come out as pqhsa_encode_bulk
+ * writes them for those lists.  The index build uses it for its last pass, once the code words are trained
+ * (pq_hsa/index/ivfpq.py:275-348: the lists are fixed before the code words are). */
+int pqhsa_encode_bulk_assigned(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                               const void* coarse, int32_t num_lists, const void* codebooks, const uint16_t* list_ids,
+                               uint32_t* codes, void* norms, void* stream);
+
+/* The Lloyd steps of the index build (pq_hsa/index/kmeans.py:195-224; code words: pq_hsa/index/pq.py:81-94) and
+ * the per-list value sums (pq_hsa/attention/kv_cache.py:688-728), with results that do not depend on the order in
+ * which thread blocks run.  The reference's update is `index_add_(0, assignments, vectors)`: on a CPU one fp32
+ * addition per key and column in the order of the keys; the two calls below give exactly those sums.
+ *
+ * pqhsa_cluster_order: stable counting sort.  ids u16 [num_sets, n] hold a cluster id below k (1..PQHSA_MAX_LISTS)
+ * per key; writes order int32 [num_sets, n] (order[j] = the key at place j when the keys are sorted by cluster and,
+ * inside a cluster, by index) and start int32 [num_sets, k + 1] (first place of every cluster; start[k] = n).
+ *
+ * pqhsa_cluster_sums: rows E [num_streams][n] of row_stride elements (stream_stride elements from one stream's
+ * first row to the next's); key set t = g * num_streams + s (g < groups) sums columns [g * width, (g + 1) * width)
+ * of stream s's rows by the clusters of order / start [groups * num_streams, ...]; width divides 128.  Writes sums
+ * float [groups * num_streams, k, width], every element the rows added one by one in the order of the keys. */
+int pqhsa_cluster_order(const uint16_t* ids, int32_t num_sets, int32_t n, int32_t k, int32_t* order, int32_t* start,
+                        void* stream);
+int pqhsa_cluster_sums(const void* rows, int32_t dtype, int64_t stream_stride, int32_t row_stride, int32_t width,
+                       int32_t num_streams, int32_t groups, int32_t n, int32_t k, const int32_t* order,
+                       const int32_t* start, float* sums, void* stream);
+
+/* The assignment of the code-word training: rows float [num_streams, n, 128] (residuals; stream_stride floats between
+ * streams, 16-byte aligned), books float [num_streams, 8, 16, 16]; writes ids u16 [8, num_streams, n], the nearest
+ * code word of every key in every subspace as argmin_c (|c|^2 - 2 x.c) (pq_hsa/index/kmeans.py:108-131), the first
+ * minimum on ties. */
+int pqhsa_subspace_assign(const float* rows, int64_t stream_stride, const float* books, int32_t num_streams, int32_t n,
+                          uint16_t* ids, void* stream);
+
 /* Test / inspection entry: approximate logits (scale * estimated q.k) of every
  * slot, float [R, cap], same arithmetic as the scan.  Counterpart of
  * score_packed_4bit_lut_multihead_list_bias

@@ -86,6 +86,18 @@ EXPORTS = {
         [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
          C.c_void_p, C.c_void_p, C.c_void_p],
     ),
+    "pqhsa_cluster_order": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "pqhsa_cluster_sums": (
+        C.c_int,
+        [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+         C.c_void_p, C.c_void_p, C.c_void_p],
+    ),
+    "pqhsa_subspace_assign": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "pqhsa_encode_bulk_assigned": (
+        C.c_int,
+        [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+         C.c_void_p, C.c_void_p, C.c_void_p],
+    ),
     "pqhsa_scan_scores": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_scan_scores_static": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p]),
     "pqhsa_topk_radix": (

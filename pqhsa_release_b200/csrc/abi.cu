@@ -323,9 +323,9 @@ int pqhsa_append_encode(const pqhsa_params* p, const int32_t* enc_count, int32_t
   return launch_append_encode(*p, enc_count, uniform_count, (cudaStream_t)stream);
 }
 
-int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
-                      const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
-                      uint16_t* list_ids, void* stream) {
+static int encode_bulk_checked(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                               const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
+                               uint16_t* list_ids, bool lists_given, void* stream) {
   if (!keys || !coarse || !codebooks || !codes || !norms || !list_ids) return set_error(PQHSA_E_NULL, "null argument");
   if (dtype < PQHSA_F32 || dtype > PQHSA_F16) return set_error(PQHSA_E_DTYPE, "unknown dtype %d", dtype);
   if (num_streams <= 0 || num_streams > 65535) return set_error(PQHSA_E_SHAPE, "num_streams must be in 1..65535");
@@ -336,7 +336,53 @@ int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_strea
     return set_error(PQHSA_E_SHAPE, "keys, coarse and codebooks must be 16-byte aligned");
   if (n == 0) return PQHSA_OK;
   return launch_encode_bulk(keys, stream_stride, num_streams, n, dtype, coarse, num_lists, codebooks, codes, norms,
-                            list_ids, (cudaStream_t)stream);
+                            list_ids, lists_given, (cudaStream_t)stream);
+}
+
+int pqhsa_encode_bulk(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                      const void* coarse, int32_t num_lists, const void* codebooks, uint32_t* codes, void* norms,
+                      uint16_t* list_ids, void* stream) {
+  return encode_bulk_checked(keys, stream_stride, num_streams, n, dtype, coarse, num_lists, codebooks, codes, norms,
+                             list_ids, false, stream);
+}
+
+int pqhsa_encode_bulk_assigned(const void* keys, int64_t stream_stride, int32_t num_streams, int32_t n, int32_t dtype,
+                               const void* coarse, int32_t num_lists, const void* codebooks, const uint16_t* list_ids,
+                               uint32_t* codes, void* norms, void* stream) {
+  return encode_bulk_checked(keys, stream_stride, num_streams, n, dtype, coarse, num_lists, codebooks, codes, norms,
+                             const_cast<uint16_t*>(list_ids), true, stream);
+}
+
+int pqhsa_cluster_order(const uint16_t* ids, int32_t num_sets, int32_t n, int32_t k, int32_t* order, int32_t* start,
+                        void* stream) {
+  if (!ids || !order || !start) return set_error(PQHSA_E_NULL, "null argument");
+  if (num_sets <= 0 || n < 0) return set_error(PQHSA_E_SHAPE, "need num_sets > 0 and n >= 0");
+  if (k < 1 || k > kLMax) return set_error(PQHSA_E_SHAPE, "k must be in 1..%d, got %d", kLMax, k);
+  return launch_cluster_order(ids, num_sets, n, k, order, start, (cudaStream_t)stream);
+}
+
+int pqhsa_cluster_sums(const void* rows, int32_t dtype, int64_t stream_stride, int32_t row_stride, int32_t width,
+                       int32_t num_streams, int32_t groups, int32_t n, int32_t k, const int32_t* order,
+                       const int32_t* start, float* sums, void* stream) {
+  if (!rows || !order || !start || !sums) return set_error(PQHSA_E_NULL, "null argument");
+  if (dtype < PQHSA_F32 || dtype > PQHSA_F16) return set_error(PQHSA_E_DTYPE, "unknown dtype %d", dtype);
+  if (width < 1 || width > 128 || 128 % width) return set_error(PQHSA_E_SHAPE, "width must divide 128, got %d", width);
+  if (num_streams <= 0 || groups <= 0 || (int64_t)num_streams * groups > 65535)
+    return set_error(PQHSA_E_SHAPE, "need 1 <= num_streams * groups <= 65535");
+  if (n < 0 || k < 1 || row_stride < groups * width || stream_stride < (int64_t)n * row_stride)
+    return set_error(PQHSA_E_SHAPE, "need n >= 0, k >= 1, row_stride >= groups * width, stream_stride >= n * row_stride");
+  return launch_cluster_sums(rows, dtype, stream_stride, row_stride, width, num_streams, groups, n, k, order, start, sums,
+                             (cudaStream_t)stream);
+}
+
+int pqhsa_subspace_assign(const float* rows, int64_t stream_stride, const float* books, int32_t num_streams, int32_t n,
+                          uint16_t* ids, void* stream) {
+  if (!rows || !books || !ids) return set_error(PQHSA_E_NULL, "null argument");
+  if (num_streams <= 0 || num_streams > 65535) return set_error(PQHSA_E_SHAPE, "num_streams must be in 1..65535");
+  if (n < 0 || stream_stride < (int64_t)n * kD) return set_error(PQHSA_E_SHAPE, "need n >= 0 and stream_stride >= n * %d", kD);
+  if (((uintptr_t)rows & 15) || (stream_stride & 3)) return set_error(PQHSA_E_SHAPE, "rows must be 16-byte aligned");
+  if (n == 0) return PQHSA_OK;
+  return launch_subspace_assign(rows, stream_stride, books, num_streams, n, ids, (cudaStream_t)stream);
 }
 
 int pqhsa_scan_scores(const pqhsa_params* p, float* scores, void* stream) {

@@ -52,9 +52,15 @@ int launch_append_encode(const pqhsa_params& p, const int32_t* cnt, int32_t uni,
 int launch_compact(const pqhsa_params& p, int32_t* error, cudaStream_t st);
 int launch_encode_bulk(const void* keys, long long stream_stride, int streams, int n, int dtype, const void* coarse,
                        int num_lists, const void* codebooks, uint32_t* codes, void* norms, uint16_t* list_ids,
-                       cudaStream_t st);
+                       bool lists_given, cudaStream_t st);
 int launch_topk(const float* scores, int rows, int n, int64_t stride, int k, int32_t* oi, float* ov,
                 cudaStream_t st);
+int launch_cluster_order(const uint16_t* ids, int sets, int n, int k, int32_t* order, int32_t* start, cudaStream_t st);
+int launch_cluster_sums(const void* rows, int dtype, long long stream_stride, int row_stride, int width, int streams,
+                        int groups, int n, int k, const int32_t* order, const int32_t* start, float* sums,
+                        cudaStream_t st);
+int launch_subspace_assign(const float* rows, long long stream_stride, const float* books, int streams, int n,
+                           uint16_t* ids, cudaStream_t st);
 
 #define PQHSA_DISPATCH_E(dtype, ...)                                   \
   switch (dtype) {                                                     \
@@ -271,6 +277,30 @@ __device__ __forceinline__ StreamGeom stream_geom(const int32_t* st, int sink) {
   g.retr_end = g.sink_end + g.n_sorted + g.n_tail;
   g.full = g.sink_end + max(g.seq_len - g.retr_end, 0);
   return g;
+}
+
+// Exclusive prefix sum over the 1024 threads of a CTA (thread t holds value t; threads with nothing pass 0); all
+// threads call.  Returns the exclusive sum; *total = the sum of all.  wtot: 32 ints of shared memory.
+__device__ __forceinline__ int block_exscan(int v, int* wtot, int* total) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int x = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += x;
+  }
+  __syncthreads();  // wtot of an earlier call has been read
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  int w = wtot[lane];  // 32 warps
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int x = __shfl_up_sync(0xffffffffu, w, o);
+    if (lane >= o) w += x;
+  }
+  *total = __shfl_sync(0xffffffffu, w, 31);
+  const int before = __shfl_sync(0xffffffffu, w, warp) - __shfl_sync(0xffffffffu, incl, 31);
+  return before + incl - v;
 }
 
 #endif  // __CUDACC__

@@ -48,30 +48,6 @@ struct CompactShared {
   int total_units;
 };
 
-// Exclusive prefix sum of v over the first kLMax threads of the CTA (thread t holds list t's value); all threads
-// call, threads >= kLMax pass 0.  Returns the exclusive sum; *total = the sum of all.
-__device__ __forceinline__ int block_exscan(int v, int* wtot, int* total) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int incl = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int x = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += x;
-  }
-  __syncthreads();  // wtot of an earlier call has been read
-  if (lane == 31) wtot[warp] = incl;
-  __syncthreads();
-  int w = wtot[lane];  // 32 warps
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int x = __shfl_up_sync(0xffffffffu, w, o);
-    if (lane >= o) w += x;
-  }
-  *total = __shfl_sync(0xffffffffu, w, 31);
-  const int before = __shfl_sync(0xffffffffu, w, warp) - __shfl_sync(0xffffffffu, incl, 31);
-  return before + incl - v;
-}
-
 template <typename E>
 __global__ void __launch_bounds__(kCompThreads) compact_kernel(const CompactArgs a) {
   extern __shared__ __align__(16) unsigned char comp_smem[];

@@ -14,6 +14,9 @@
 // memory, dimension-major, while the stream's centroids pass through a second shared tile 64
 // lists at a time.  A thread owns a 4-key x 8-list block of distances, so three 16-byte
 // shared loads feed 32 subtract-fma pairs.
+//
+// GIVEN: the lists are an input (the caller kept them from an earlier pass against the same centroids, as the index
+// build does once its code words are trained); the search is skipped and only norm, residual and code remain.
 #include "common.cuh"
 
 namespace pqhsa {
@@ -31,7 +34,7 @@ struct BulkArgs {
   const void* codebooks;
   uint32_t* codes;
   void* norms;
-  uint16_t* list_ids;
+  uint16_t* list_ids;  // written, or read when the lists are given
   int n, num_lists;
 };
 
@@ -65,7 +68,7 @@ __device__ __forceinline__ void load_tile_transposed(const E* src, int row0, int
 
 // NJ = blocks of 4 lists per thread.  A warp spans 16 / NJ threads along the lists of a tile and
 // 2 NJ threads along the keys; a thread owns 4 keys x 4 NJ lists; a CTA takes 64 NJ keys.
-template <typename E, int NJ>
+template <typename E, int NJ, bool GIVEN>
 __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const BulkArgs a) {
   constexpr int kBulkKeys = 64 * NJ;
   constexpr int kTx = 16 / NJ;  // threads of a warp along the lists
@@ -100,6 +103,10 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
     }
   }
 
+  if constexpr (GIVEN) {
+    if (tid < kBulkKeys)
+      list_sh[tid] = key0 + tid < a.n ? min((int)a.list_ids[(size_t)s * a.n + key0 + tid], a.num_lists - 1) : 0;
+  } else {
   // ---- nearest list
   const int tx = lane % kTx, ty = warp * (32 / kTx) + lane / kTx;  // lists 4 tx (+ 4 kTx jb) .., keys 4 ty ..
   float bd[4];
@@ -177,7 +184,8 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
     }
     if (tx == 0) list_sh[4 * ty + i] = bl[i];
   }
-  __syncthreads();
+  }
+  __syncthreads();  // the lists and (lists given: no tile loop before this) the directions are in place
 
   // ---- residuals in place of the directions, code words into the centroid tile
   // lane -> key: the shared accesses touch 32 banks; the centroid rows come from L2
@@ -242,13 +250,13 @@ __global__ void __launch_bounds__(kBulkThreads, 2) encode_bulk_kernel(const Bulk
     const size_t o = (size_t)s * a.n + key0 + tid;
     a.codes[o] = code_sh[tid];
     static_cast<E*>(a.norms)[o] = from_f<E>(nrm_sh[tid]);
-    a.list_ids[o] = (uint16_t)list_sh[tid];
+    if constexpr (!GIVEN) a.list_ids[o] = (uint16_t)list_sh[tid];
   }
 }
 
 int launch_encode_bulk(const void* keys, long long stream_stride, int streams, int n, int dtype, const void* coarse,
                        int num_lists, const void* codebooks, uint32_t* codes, void* norms, uint16_t* list_ids,
-                       cudaStream_t st) {
+                       bool lists_given, cudaStream_t st) {
   BulkArgs a;
   a.keys = keys;
   a.stream_stride = stream_stride;
@@ -264,7 +272,7 @@ int launch_encode_bulk(const void* keys, long long stream_stride, int streams, i
   const dim3 grid((n + kKeys - 1) / kKeys, streams);
   constexpr int kSmem = kD * (kKeys + kBulkLists) * (int)sizeof(float);  // above the default limit
   PQHSA_DISPATCH_E(dtype, {
-    auto kern = encode_bulk_kernel<E, NJ>;
+    auto kern = lists_given ? encode_bulk_kernel<E, NJ, true> : encode_bulk_kernel<E, NJ, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return check_launch("encode_bulk: shared memory opt-in");
     kern<<<grid, kBulkThreads, kSmem, st>>>(a);

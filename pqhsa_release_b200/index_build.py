@@ -9,10 +9,14 @@ nearest-code-word encoding (:97-115) and the per-list value means
 CPU generator with the reference's seeds, so the same rows are drawn as in the
 reference's CPU build.
 
-This is set-up work outside the per-step path.  The k-means training steps are
-torch tensor operations on the device; the pass that assigns and encodes every key
-against the finished centroids and code words - the bulk of the arithmetic - is one
-CUDA kernel (``encode_bulk`` -> ``pqhsa_encode_bulk``) when the tensors are on a GPU.
+This is set-up work outside the per-step path.  With the tensors on a GPU every pass
+over the keys is a CUDA kernel: the assignment against the coarse centroids and the
+final encoding (``encode_bulk`` -> ``pqhsa_encode_bulk``), the assignment of the
+code-word training (``pqhsa_subspace_assign``) and the sums of the Lloyd steps and of
+the values per list (``cluster_sums`` -> ``pqhsa_cluster_order`` + ``pqhsa_cluster_sums``:
+rows added in the order of the keys, so a build gives the same bits every time it runs).
+What stays in torch works on [streams, clusters, width] tensors: dividing by the counts,
+re-seeding empty clusters, rounding to the storage type.
 """
 
 from __future__ import annotations
@@ -23,14 +27,18 @@ from .config import IVFPQConfig, validate_index_config
 from .device_index import StreamIndexTensors, codes_to_words, words_to_codes  # noqa: F401
 
 
-def encode_bulk(keys: torch.Tensor, coarse: torch.Tensor, codebooks: torch.Tensor):
+def encode_bulk(keys: torch.Tensor, coarse: torch.Tensor, codebooks: torch.Tensor, raw: bool = False,
+                lists: torch.Tensor | None = None):
     """Assign and encode every key on the GPU with fixed codebooks (``pqhsa_encode_bulk``).
 
     keys [S, N, 128] (rows contiguous; streams may be strided views of a cache), coarse
     [S, L, 128], codebooks [S, 8, 16, 16], all of the keys' dtype.  Returns
     ``(words int64 [S, N], list ids int64 [S, N], norms [S, N] in the keys' dtype)``: what
     ``IVFPQIndex.add`` (pq_hsa/index/ivfpq.py:598-645) computes for the batch, in the
-    incremental encoder's arithmetic."""
+    incremental encoder's arithmetic.  ``raw``: words and list ids as the kernel wrote them
+    (int32 / int16 holding unsigned bit patterns).  ``lists`` (int16 [S, N], raw ids of an
+    earlier call with the same ``coarse``): the nearest-list search is skipped
+    (``pqhsa_encode_bulk_assigned``)."""
     from . import _lib
     from .device_index import _DTYPE_CODE
 
@@ -51,17 +59,81 @@ def encode_bulk(keys: torch.Tensor, coarse: torch.Tensor, codebooks: torch.Tenso
         raise ValueError("codebooks must be [streams, 8, 16, 16]")
     words = torch.empty(s, n, dtype=torch.int32, device=keys.device)
     norms = torch.empty(s, n, dtype=keys.dtype, device=keys.device)
+    if lists is not None:
+        if lists.dtype != torch.int16 or tuple(lists.shape) != (s, n) or lists.device != keys.device:
+            raise ValueError("lists must be int16 [streams, N] on the keys' device")
+        lids = lists.contiguous()
+    else:
+        lids = torch.empty(s, n, dtype=torch.int16, device=keys.device)  # u16 bit patterns
     if n == 0:
-        return words.long(), torch.empty(s, 0, dtype=torch.long, device=keys.device), norms
-    lids = torch.empty(s, n, dtype=torch.int16, device=keys.device)  # u16 bit patterns
+        return (words, lids, norms) if raw else (words.long(), lids.long(), norms)
     stride = keys.stride(0) if s > 1 else max(n * 128, 1)
     with torch.cuda.device(keys.device):
-        _lib.call(
-            "pqhsa_encode_bulk", keys.data_ptr(), stride, s, n, _DTYPE_CODE[keys.dtype], coarse.data_ptr(),
-            coarse.shape[1], codebooks.data_ptr(), words.data_ptr(), norms.data_ptr(), lids.data_ptr(),
-            torch.cuda.current_stream(keys.device).cuda_stream,
-        )
-    return words.long() & 0xFFFFFFFF, lids.long() & 0xFFFF, norms
+        st = torch.cuda.current_stream(keys.device).cuda_stream
+        if lists is None:
+            _lib.call("pqhsa_encode_bulk", keys.data_ptr(), stride, s, n, _DTYPE_CODE[keys.dtype], coarse.data_ptr(),
+                      coarse.shape[1], codebooks.data_ptr(), words.data_ptr(), norms.data_ptr(), lids.data_ptr(), st)
+        else:
+            _lib.call("pqhsa_encode_bulk_assigned", keys.data_ptr(), stride, s, n, _DTYPE_CODE[keys.dtype],
+                      coarse.data_ptr(), coarse.shape[1], codebooks.data_ptr(), lids.data_ptr(), words.data_ptr(),
+                      norms.data_ptr(), st)
+    if raw:
+        return words, lids, norms
+    return words.long() & 0xFFFFFFFF, _u16(lids), norms
+
+
+def _u16(t: torch.Tensor) -> torch.Tensor:
+    """int16 tensor holding u16 bit patterns -> int64 values."""
+    return t.long() & 0xFFFF
+
+
+def cluster_sums(rows: torch.Tensor, ids: torch.Tensor, k: int, width: int = 128, groups: int = 1):
+    """Per-cluster sums of rows, added in the order of the keys (``index_add_`` on one CPU thread, bit for bit).
+
+    rows [S, N, R] (fp32 / bf16 / fp16; rows contiguous, streams may be strided), ids int16 [groups * S, N] with
+    u16 cluster ids below k: key set g * S + s sums columns [g * width, (g + 1) * width) of stream s.  Returns
+    ``(sums fp32 [groups * S, k, width], counts int32 [groups * S, k])``."""
+    from . import _lib
+    from .device_index import _DTYPE_CODE
+
+    if not rows.is_cuda:
+        raise RuntimeError("cluster_sums needs CUDA tensors: there is no CPU path")
+    s, n, r = rows.shape
+    if n and (rows.stride(2) != 1 or rows.stride(1) != r or (s > 1 and rows.stride(0) < n * r)):
+        rows = rows.contiguous()
+    ids = ids.contiguous()
+    if ids.dtype != torch.int16 or tuple(ids.shape) != (groups * s, n):
+        raise ValueError("ids must be int16 [groups * streams, N]")
+    sets = groups * s
+    if n == 0:
+        return (torch.zeros(sets, k, width, dtype=torch.float32, device=rows.device),
+                torch.zeros(sets, k, dtype=torch.int32, device=rows.device))
+    order = torch.empty(sets, n, dtype=torch.int32, device=rows.device)
+    start = torch.empty(sets, k + 1, dtype=torch.int32, device=rows.device)
+    sums = torch.empty(sets, k, width, dtype=torch.float32, device=rows.device)
+    stride = rows.stride(0) if s > 1 else max(n * r, 1)
+    with torch.cuda.device(rows.device):
+        st = torch.cuda.current_stream(rows.device).cuda_stream
+        _lib.call("pqhsa_cluster_order", ids.data_ptr(), sets, n, k, order.data_ptr(), start.data_ptr(), st)
+        _lib.call("pqhsa_cluster_sums", rows.data_ptr(), _DTYPE_CODE[rows.dtype], stride, r, width, s, groups, n, k,
+                  order.data_ptr(), start.data_ptr(), sums.data_ptr(), st)
+    return sums, start[:, 1:] - start[:, :-1]
+
+
+def subspace_assign(resid: torch.Tensor, books: torch.Tensor) -> torch.Tensor:
+    """Nearest code word of every residual in every subspace (``pqhsa_subspace_assign``): resid fp32 [S, N, 128],
+    books fp32 [S, 8, 16, 16] -> int16 [8, S, N]."""
+    from . import _lib
+
+    if not resid.is_cuda or resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise ValueError("resid must be a contiguous fp32 CUDA tensor")
+    s, n, _ = resid.shape
+    books = books.float().contiguous()
+    ids = torch.empty(8, s, n, dtype=torch.int16, device=resid.device)
+    with torch.cuda.device(resid.device):
+        _lib.call("pqhsa_subspace_assign", resid.data_ptr(), max(n * 128, 4), books.data_ptr(), s, n, ids.data_ptr(),
+                  torch.cuda.current_stream(resid.device).cuda_stream)
+    return ids
 
 
 def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Tensor:
@@ -77,11 +149,13 @@ def _assign(x: torch.Tensor, cent: torch.Tensor, chunk: int = 16384) -> torch.Te
 
 
 def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.dtype, eps: float,
-            final_assign: bool = True, assign_fn=None):
+            final_assign: bool = True, step_fn=None, after_launch=None):
     """Batched seeded Lloyd iterations.  x [S, N, d] fp32 -> (centroids [S, k, d]
     holding values representable in ``store_dtype``, assignments [S, N]; None when
     ``final_assign`` is off and the caller assigns with the finished centroids itself).
-    ``assign_fn(centroids) -> [S, N]`` replaces the torch assignment of the Lloyd steps."""
+    ``step_fn(centroids) -> (sums [S, k, d], counts [S, k])`` replaces the torch assignment
+    and scatter of a Lloyd step (the kernels, on a GPU); ``after_launch()`` runs once, behind the
+    first step's launches and before the host waits for them (host work that can overlap)."""
     s, n, d = x.shape
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
@@ -91,11 +165,18 @@ def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.d
         rows = torch.cat([torch.arange(n), torch.randint(0, n, (k - n,), generator=gen)])
     cent = x[:, rows.to(x.device)].to(store_dtype).float()
     for _ in range(iters):
-        a = _assign(x, cent) if assign_fn is None else assign_fn(cent)
-        sums = torch.zeros(s, k, d, dtype=torch.float32, device=x.device)
-        sums.scatter_add_(1, a.unsqueeze(-1).expand(-1, -1, d), x)
-        cnt = torch.zeros(s, k, dtype=torch.float32, device=x.device)
-        cnt.scatter_add_(1, a, torch.ones_like(a, dtype=torch.float32))
+        if step_fn is None:
+            a = _assign(x, cent)
+            sums = torch.zeros(s, k, d, dtype=torch.float32, device=x.device)
+            sums.scatter_add_(1, a.unsqueeze(-1).expand(-1, -1, d), x)
+            cnt = torch.zeros(s, k, dtype=torch.float32, device=x.device)
+            cnt.scatter_add_(1, a, torch.ones_like(a, dtype=torch.float32))
+        else:
+            sums, cnt = step_fn(cent)
+            cnt = cnt.float()
+            if after_launch is not None:
+                after_launch()
+                after_launch = None
         live = cnt > 0
         new = sums / cnt.clamp_min(eps).unsqueeze(-1)
         dead = (~live).sum(dim=1).tolist()
@@ -107,6 +188,65 @@ def _kmeans(x: torch.Tensor, k: int, iters: int, seed: int, store_dtype: torch.d
                     new[i, ~live[i]] = x[i, repl]
         cent = new.to(store_dtype).float()
     return cent, (_assign(x, cent) if final_assign else None)
+
+
+def _draw_code_word_rows(n: int, seed: int):
+    """The initial rows of the 8 code-word trainings (subspace m: a CPU generator seeded seed + 10000 + m, as
+    pq_hsa/index/pq.py:81-94 seeds them) and the generators, which later draw the replacements of empty clusters.
+    About a millisecond of host time per subspace at 128K keys."""
+    gens, rows = [], []
+    for j in range(8):
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(seed + 10_000 + j)
+        if n >= 16:
+            rows.append(torch.randperm(n, generator=gen)[:16])
+        else:
+            rows.append(torch.cat([torch.arange(n), torch.randint(0, n, (16 - n,), generator=gen)]))
+        gens.append(gen)
+    return gens, rows
+
+
+def _train_code_words(resid: torch.Tensor, iters: int, seed: int, store_dtype: torch.dtype, eps: float, drawn=None):
+    """The 8 seeded code-word trainings of pq_hsa/index/pq.py:81-94 as one batch on the GPU.  resid fp32
+    [S, N, 128] -> code words fp32 [S, 8, 16, 16] holding values representable in ``store_dtype``.  Every
+    subspace keeps its own generator, so the rows it draws are those of its own sequential run.  ``drawn``: the
+    result of :func:`_draw_code_word_rows` when the caller made it earlier."""
+    s, n, d = resid.shape
+    m, k, sub = 8, 16, 16
+    gens, rows = drawn if drawn is not None else _draw_code_word_rows(n, seed)
+    first = [resid[:, rows[j].to(resid.device), j * sub : (j + 1) * sub] for j in range(m)]
+    cent = torch.stack(first, dim=1).to(store_dtype).float()  # [S, 8, 16, 16]
+    for _ in range(iters):
+        ids = subspace_assign(resid, cent)
+        sums, cnt = cluster_sums(resid, ids.view(m * s, n), k, width=sub, groups=m)
+        sums = sums.view(m, s, k, sub).transpose(0, 1)
+        cnt = cnt.view(m, s, k).transpose(0, 1).float()
+        live = cnt > 0
+        new = sums / cnt.clamp_min(eps).unsqueeze(-1)
+        dead = (~live).sum(dim=2).tolist()  # [S][8]
+        for j in range(m):
+            for i in range(s):
+                if dead[i][j]:
+                    repl = torch.randint(0, n, (dead[i][j],), generator=gens[j]).to(resid.device)
+                    new[i, j, ~live[i, j]] = resid[i, repl, j * sub : (j + 1) * sub]
+        cent = new.to(store_dtype).float()
+    return cent
+
+
+def _value_summaries(values: torch.Tensor, lid: torch.Tensor, lid_raw, lists: int):
+    """Per-list value sums, counts and means (pq_hsa/attention/kv_cache.py:688-728): the kernels on a GPU (the
+    values are read in their own dtype and widened on the way), torch scatters elsewhere."""
+    s, n, d = values.shape
+    if lid_raw is not None:
+        vsum, cnt = cluster_sums(values, lid_raw, lists)
+        vcnt = cnt.float()
+    else:
+        vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=values.device)
+        vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), values.float())
+        vcnt = torch.zeros(s, lists, dtype=torch.float32, device=values.device)
+        vcnt.scatter_add_(1, lid, torch.ones_like(lid, dtype=torch.float32))
+    vmean = torch.where(vcnt.unsqueeze(-1) > 0, vsum / vcnt.clamp_min(1).unsqueeze(-1), torch.zeros_like(vsum))
+    return vsum, vcnt, vmean
 
 
 @torch.no_grad()
@@ -128,37 +268,38 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
     unit.div_(norms.float().unsqueeze(-1))
     lists = min(cfg.num_lists, n)
     on_gpu = keys.is_cuda and d == 128 and cfg.num_subspaces == 8 and cfg.num_bits == 4
+    m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
+    lid_raw = None
     if on_gpu:
-        # every assignment against the coarse centroids - the Lloyd steps' and the final one - by the
-        # kernel (the code words are not known yet: their half of the result is ignored)
+        # every assignment against the coarse centroids - the Lloyd steps' and the final one - by the bulk
+        # encode kernel (the code words are not known yet: their half of the result is ignored), the sums of
+        # a step by the ordered-sum kernels
         no_books = torch.zeros(s, 8, 16, 16, dtype=dtype, device=keys.device)
+        drawn = []  # the code-word trainings' random rows are drawn on the host while the first step runs on the device
         coarse, _ = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps, final_assign=False,
-                            assign_fn=lambda cent: encode_bulk(keys, cent, no_books)[1])
-        _, lid, norms = encode_bulk(keys, coarse, no_books)
+                            step_fn=lambda cent: cluster_sums(unit, encode_bulk(keys, cent, no_books, raw=True)[1], lists),
+                            after_launch=lambda: drawn.append(_draw_code_word_rows(n, cfg.seed)))
+        _, lid_raw, norms = encode_bulk(keys, coarse, no_books, raw=True)
+        lid = _u16(lid_raw)
     else:
         coarse, lid = _kmeans(unit, lists, cfg.coarse_max_iter, cfg.seed, dtype, cfg.eps)
     resid = unit.sub_(torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d)))  # the directions are not needed again
     del unit
-    m, sub, ncodes = cfg.num_subspaces, d // cfg.num_subspaces, 1 << cfg.num_bits
-    books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
-    words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
-    for j in range(m):
-        chunk = resid[:, :, j * sub : (j + 1) * sub].contiguous()
-        books[:, j], _ = _kmeans(chunk, ncodes, cfg.pq_max_iter, cfg.seed + 10_000 + j, dtype, cfg.eps,
-                                 final_assign=False)
-        if not on_gpu:
+    if on_gpu:
+        books = _train_code_words(resid, cfg.pq_max_iter, cfg.seed, dtype, cfg.eps, drawn[0] if drawn else None)
+        words, _, _ = encode_bulk(keys, coarse, books, lists=lid_raw)  # the lists found above: no second search
+    else:
+        books = torch.empty(s, m, ncodes, sub, dtype=torch.float32, device=keys.device)
+        words = torch.zeros(s, n, dtype=torch.int64, device=keys.device)
+        for j in range(m):
+            chunk = resid[:, :, j * sub : (j + 1) * sub].contiguous()
+            books[:, j], _ = _kmeans(chunk, ncodes, cfg.pq_max_iter, cfg.seed + 10_000 + j, dtype, cfg.eps,
+                                     final_assign=False)
             # encode with true squared distances (torch.cdist's small-size path)
             d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
             words |= d2.argmin(dim=-1) << (4 * j)
-    if on_gpu:
-        words, _, _ = encode_bulk(keys, coarse, books)  # same lists as above: the kernel is deterministic
     del resid
-    vf = values.float()
-    vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
-    vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
-    vcnt = torch.zeros(s, lists, dtype=torch.float32, device=keys.device)
-    vcnt.scatter_add_(1, lid, torch.ones_like(lid, dtype=torch.float32))
-    vmean = torch.where(vcnt.unsqueeze(-1) > 0, vsum / vcnt.clamp_min(1).unsqueeze(-1), torch.zeros_like(vsum))
+    vsum, vcnt, vmean = _value_summaries(values, lid, lid_raw, lists)
     out = []
     for i in range(s):
         out.append(
@@ -213,8 +354,10 @@ def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list
         chunk = ures[:, :, j * sub : (j + 1) * sub].contiguous()
         books[:, j] = ema(books[:, j], chunk, _assign(chunk, books[:, j]))
     books = books.to(dtype).float()
+    lid_raw = None
     if keys.is_cuda and d == 128 and m == 8 and cfg.num_bits == 4:
-        words, lid, norms = encode_bulk(keys, coarse, books)
+        words, lid_raw, norms = encode_bulk(keys, coarse, books, raw=True)
+        words, lid = words.long() & 0xFFFFFFFF, _u16(lid_raw)
     else:
         lid = _assign(unit, coarse)
         resid = unit - torch.gather(coarse, 1, lid.unsqueeze(-1).expand(-1, -1, d))
@@ -223,12 +366,7 @@ def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list
             chunk = resid[:, :, j * sub : (j + 1) * sub]
             d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
             words |= d2.argmin(dim=-1) << (4 * j)
-    vf = values.float()
-    vsum = torch.zeros(s, lists, d, dtype=torch.float32, device=keys.device)
-    vsum.scatter_add_(1, lid.unsqueeze(-1).expand(-1, -1, d), vf)
-    vcnt = torch.zeros(s, lists, dtype=torch.float32, device=keys.device)
-    vcnt.scatter_add_(1, lid, torch.ones_like(lid, dtype=torch.float32))
-    vmean = torch.where(vcnt.unsqueeze(-1) > 0, vsum / vcnt.clamp_min(1).unsqueeze(-1), torch.zeros_like(vsum))
+    vsum, vcnt, vmean = _value_summaries(values, lid, lid_raw, lists)
     return [
         StreamIndexTensors(
             packed_codes=words_to_codes(words[i]), list_ids=lid[i], key_norms=norms[i],

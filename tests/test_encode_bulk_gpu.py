@@ -133,6 +133,23 @@ def test_device_build_and_refresh_use_the_kernel_and_stay_close_to_the_cpu_build
         assert float((a.packed_codes != b.packed_codes.cpu()).any(dim=1).float().mean()) <= 0.05
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bulk_encode_with_given_lists_equals_the_full_pass(dtype):
+    """pqhsa_encode_bulk_assigned: with the lists of an earlier pass as an input the codes and norms are those of
+    the full pass, bit for bit (the index build's last pass skips the nearest-list search this way)."""
+    from pqhsa_release_b200.index_build import encode_bulk
+
+    gen = torch.Generator().manual_seed(21)
+    keys = torch.randn(2, 1500, 128, generator=gen).to(dtype).cuda()
+    coarse = torch.nn.functional.normalize(torch.randn(2, 77, 128, generator=gen), dim=-1).to(dtype).cuda()
+    books = (0.1 * torch.randn(2, 8, 16, 16, generator=gen)).to(dtype).cuda()
+    words, lids, norms = encode_bulk(keys, coarse, books, raw=True)
+    w2, l2, n2 = encode_bulk(keys, coarse, books, raw=True, lists=lids.clone())
+    assert torch.equal(w2, words) and torch.equal(l2, lids) and torch.equal(n2, norms)
+    with pytest.raises(ValueError):
+        encode_bulk(keys, coarse, books, lists=lids[:, :10])
+
+
 def test_bulk_encode_argument_errors():
     from pqhsa_release_b200 import _lib
     from pqhsa_release_b200.index_build import encode_bulk
