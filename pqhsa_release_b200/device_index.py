@@ -61,8 +61,19 @@ def list_sorted_layout(list_ids: torch.Tensor, num_lists: int):
     Returns (perm, unit_off [U+1], unit_list [U])."""
     ids = list_ids.to(torch.int64)
     n = ids.numel()
-    perm = torch.argsort(ids, stable=True)
-    counts = torch.bincount(ids, minlength=num_lists)
+    if ids.is_cuda and n and 0 < num_lists <= _lib.MAX_LISTS:
+        # the counting sort of the index build's kernels: the same stable order, and the lists' sizes with it
+        raw = ids.to(torch.int16).contiguous()  # u16 bit patterns
+        order = torch.empty(n, dtype=torch.int32, device=ids.device)
+        start = torch.empty(num_lists + 1, dtype=torch.int32, device=ids.device)
+        with torch.cuda.device(ids.device):
+            _lib.call("pqhsa_cluster_order", raw.data_ptr(), 1, n, num_lists, order.data_ptr(), start.data_ptr(),
+                      torch.cuda.current_stream(ids.device).cuda_stream)
+        perm = order.long()
+        counts = (start[1:] - start[:-1]).long()
+    else:
+        perm = torch.argsort(ids, stable=True)
+        counts = torch.bincount(ids, minlength=num_lists)
     off = torch.zeros(num_lists + 1, dtype=torch.int64, device=ids.device)
     off[1:] = torch.cumsum(counts, 0)
     per = (counts + _lib.UNIT_KEYS - 1) // _lib.UNIT_KEYS
