@@ -153,7 +153,11 @@ template <typename E> struct ScanRing {
   static constexpr int kDepth = 2;  // units per warp in the ring: one being scored, one in flight
 };
 
-template <typename E, int G, int T>
+// ALIGNED: few streams (at most a warp's worth and a quarter of the grid): every CTA works inside ONE stream, so it
+// pays for one set of tables, list scores and headers; stream s gets 1 + floor(units_s * (grid - streams) / units)
+// CTAs, which split its units evenly.  Every warp works the split out for itself from the counters (no barrier).
+// Otherwise: equal shares of the global unit sequence, a CTA may run across stream boundaries.
+template <typename E, int G, int T, bool ALIGNED>
 __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
   using PS = PairShape<G>;
   using RG = ScanRing<E>;
@@ -180,59 +184,8 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
     return u > 0 ? u + kSegCost : 0;
   };
 
-  // total number of units (all streams), one load per thread
-  long long part = 0;
-  for (int s = tid; s < a.S; s += T) part += units_of(s);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-  if (lane == 0) s_red[warp] = part;
-  __syncthreads();
-  long long total = 0;
-#pragma unroll
-  for (int w = 0; w < W; ++w) total += s_red[w];
-  // this CTA's share [g0, g1) of the global unit sequence
-  const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
-  if (g0 >= g1) return;
-
-  long long carry = 0;  // global index of the first unit of stream `base`
-  for (int base = 0; base < a.S && carry < g1; base += T) {
-    // exclusive prefix of the unit counts of streams base .. base + T - 1
-    const int ut = base + tid < a.S ? units_of(base + tid) : 0;
-    int incl = ut;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    __syncthreads();  // s_red, s_pref, s_ut, s_first of the previous round are no longer read
-    if (lane == 31) s_red[warp] = incl;
-    if (tid == 0) s_first = 0;
-    __syncthreads();
-    int woff = 0, ctot = 0;
-#pragma unroll
-    for (int w = 0; w < W; ++w) {
-      const int v = (int)s_red[w];
-      woff += w < warp ? v : 0;
-      ctot += v;
-    }
-    const int excl = woff + incl - ut;
-    s_pref[tid] = excl;
-    s_ut[tid] = ut;
-    if (ut > 0 && carry + excl <= g0 && g0 < carry + excl + ut) s_first = tid;  // the stream holding g0
-    __syncthreads();
-    if (carry + ctot > g0) {
-      const int tend = min(T, a.S - base);
-      for (int t = s_first; t < tend; ++t) {
-        const long long sb = carry + s_pref[t];
-        const int len = s_ut[t];  // units + kSegCost
-        if (sb >= g1) break;
-        if (len == 0 || sb + len <= g0) continue;
-        const int s = base + t;
-        const int u_tot = len - kSegCost;
-        const int u0 = max((int)((sb > g0 ? sb : g0) - sb) - kSegCost, 0);
-        const int u1 = max((int)((sb + len < g1 ? sb + len : g1) - sb) - kSegCost, 0);
-        if (u0 >= u1) continue;
-
+  // ---- the units [u0, u1) of stream s (u_tot units in all) ----
+  auto scan_stream = [&](const int s, const int u0, const int u1, const int u_tot) {
         const int32_t* st = a.state + (size_t)s * kST;
         const int n_sorted = st[PQHSA_ST_N_SORTED], n_tail = st[PQHSA_ST_N_TAIL], n_units = st[PQHSA_ST_N_UNITS];
         const uint32_t* codes = a.codes + (size_t)s * a.cap;
@@ -432,9 +385,91 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
             cp_async_wait<0>();
           }
         }
+  };
+
+  if constexpr (ALIGNED) {
+    int cost = 0;  // lane s: units of stream s
+    if (lane < a.S) {
+      const int32_t* st = a.state + (size_t)lane * kST;
+      cost = st[PQHSA_ST_N_UNITS] + (st[PQHSA_ST_N_TAIL] + kUnit - 1) / kUnit;
+    }
+    const int total = (int)__reduce_add_sync(0xffffffffu, (unsigned)cost);
+    const int live = __popc(__ballot_sync(0xffffffffu, cost > 0));
+    if (total == 0) return;
+    const int ctas = cost > 0 ? 1 + (int)((long long)cost * ((int)gridDim.x - live) / total) : 0;
+    int incl = ctas;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int b = blockIdx.x;
+    const unsigned owner = __ballot_sync(0xffffffffu, incl - ctas <= b && b < incl);
+    if (owner == 0u) return;  // a spare CTA
+    const int s = __ffs(owner) - 1;
+    const int j = b - __shfl_sync(0xffffffffu, incl - ctas, s), n = __shfl_sync(0xffffffffu, ctas, s);
+    const int c = __shfl_sync(0xffffffffu, cost, s);
+    const int u0 = (int)((long long)c * j / n), u1 = (int)((long long)c * (j + 1) / n);
+    if (u0 < u1) scan_stream(s, u0, u1, c);
+  } else {
+  // total number of units (all streams), one load per thread
+  long long part = 0;
+  for (int s = tid; s < a.S; s += T) part += units_of(s);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) s_red[warp] = part;
+  __syncthreads();
+  long long total = 0;
+#pragma unroll
+  for (int w = 0; w < W; ++w) total += s_red[w];
+  // this CTA's share [g0, g1) of the global unit sequence
+  const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
+  if (g0 >= g1) return;
+
+  long long carry = 0;  // global index of the first unit of stream `base`
+  for (int base = 0; base < a.S && carry < g1; base += T) {
+    // exclusive prefix of the unit counts of streams base .. base + T - 1
+    const int ut = base + tid < a.S ? units_of(base + tid) : 0;
+    int incl = ut;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    __syncthreads();  // s_red, s_pref, s_ut, s_first of the previous round are no longer read
+    if (lane == 31) s_red[warp] = incl;
+    if (tid == 0) s_first = 0;
+    __syncthreads();
+    int woff = 0, ctot = 0;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const int v = (int)s_red[w];
+      woff += w < warp ? v : 0;
+      ctot += v;
+    }
+    const int excl = woff + incl - ut;
+    s_pref[tid] = excl;
+    s_ut[tid] = ut;
+    if (ut > 0 && carry + excl <= g0 && g0 < carry + excl + ut) s_first = tid;  // the stream holding g0
+    __syncthreads();
+    if (carry + ctot > g0) {
+      const int tend = min(T, a.S - base);
+      for (int t = s_first; t < tend; ++t) {
+        const long long sb = carry + s_pref[t];
+        const int len = s_ut[t];  // units + kSegCost
+        if (sb >= g1) break;
+        if (len == 0 || sb + len <= g0) continue;
+        const int s = base + t;
+        const int u_tot = len - kSegCost;
+        const int u0 = max((int)((sb > g0 ? sb : g0) - sb) - kSegCost, 0);
+        const int u1 = max((int)((sb + len < g1 ? sb + len : g1) - sb) - kSegCost, 0);
+        if (u0 >= u1) continue;
+
+        scan_stream(s, u0, u1, u_tot);
       }
     }
     carry += ctot;
+  }
   }
 }
 
@@ -462,16 +497,17 @@ __global__ void __launch_bounds__(256) scan_dump_kernel(const ScanArgs a) {
 
 template <typename E, int G, int T>
 static int launch_scan_t(const pqhsa_params& p, const ScanArgs& a, cudaStream_t st) {
-  using PS = PairShape<G>;
-  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kLMax * PS::GP * sizeof(float) + (size_t)kHdr * sizeof(int4) +
-                      (size_t)(T / 32) * ScanRing<E>::kDepth * ScanRing<E>::kStageBytes;
-  auto kern = scan_kernel<E, G, T>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return check_launch("scan: shared memory opt-in");
   const long long units_hi = (long long)p.num_streams * (p.num_lists + p.max_slots / kUnit + 2);
   long long ctas = sm_count();
   if (ctas > units_hi) ctas = units_hi;
   if (ctas < 1) ctas = 1;
+  const bool aligned = p.num_streams <= 32 && 4LL * p.num_streams <= ctas;
+  using PS = PairShape<G>;
+  const size_t smem = PS::kFloats * sizeof(float) + (size_t)kLMax * PS::GP * sizeof(float) + (size_t)kHdr * sizeof(int4) +
+                      (size_t)(T / 32) * ScanRing<E>::kDepth * ScanRing<E>::kStageBytes;
+  auto kern = aligned ? scan_kernel<E, G, T, true> : scan_kernel<E, G, T, false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return check_launch("scan: shared memory opt-in");
   kern<<<(unsigned)ctas, T, smem, st>>>(a);
   return check_launch("scan");
 }
