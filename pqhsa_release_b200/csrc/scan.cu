@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(T, 1) scan_kernel(const ScanArgs a) {
           // GP-float vectors (conflict-free stores); the REP threads of an entry read the same vector.
           {
             const float* src = a.pair_tab + (size_t)(s * PS::NP + pass) * (4 * 256 * GP);
-#pragma unroll 4
+#pragma unroll
             for (int i = tid; i < 4 * 256 * PS::REP; i += T) {
               const int e = i / PS::REP;
               if constexpr (GP == 4) {
