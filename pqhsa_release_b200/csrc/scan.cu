@@ -8,9 +8,13 @@
 //
 // Work split.  The sorted region of a stream is cut into units of at most 128
 // consecutive slots of ONE list, so the list score is a warp-uniform register
-// and the per-list log-sum-exp is a warp reduction with no atomics.  All units
-// of all streams form one global sequence; a persistent grid (one CTA per SM)
-// takes equal shares of it, so ragged contexts balance by themselves.  Inside a
+// and the per-list log-sum-exp is a warp reduction with no atomics.  A persistent
+// grid (one CTA per SM) shares the units out.  With few streams every CTA stays
+// inside one stream (a stream's CTAs split its units evenly), because entering a
+// stream - 128 KB of tables, list scores, headers - costs about as much as 40
+// units of scanning.  With many streams all units of all streams form one global
+// sequence and the CTAs take equal shares of it, so ragged contexts balance by
+// themselves and a CTA may run across stream boundaries.  Inside a
 // stream the sequence is a stride permutation of the units, so every CTA gets
 // units from all over the stream (lists with many candidates do not pile up on one
 // CTA).  The unit headers of a share are staged in shared memory; a warp takes one
