@@ -50,9 +50,9 @@ def codes_to_words(packed: torch.Tensor) -> torch.Tensor:
 
 
 def words_to_codes(words: torch.Tensor) -> torch.Tensor:
-    """Inverse of :func:`codes_to_words`."""
+    """Inverse of :func:`codes_to_words`: integer [..., N] -> uint8 [..., N, 4]."""
     w = words.to(torch.int64) & 0xFFFFFFFF
-    return torch.stack([(w >> (8 * i)) & 0xFF for i in range(4)], dim=1).to(torch.uint8)
+    return torch.stack([(w >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)
 
 
 def list_sorted_layout(list_ids: torch.Tensor, num_lists: int):

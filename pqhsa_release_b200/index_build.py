@@ -233,6 +233,19 @@ def _train_code_words(resid: torch.Tensor, iters: int, seed: int, store_dtype: t
     return cent
 
 
+def _per_stream(words, lid, norms, coarse, books, vmean, vsum, vcnt, dtype) -> list[StreamIndexTensors]:
+    """The batch's results as one record per stream; the conversions run once on the batch, the records hold views."""
+    codes = words_to_codes(words)
+    coarse, books, vmean, vcnt = coarse.to(dtype), books.to(dtype), vmean.to(dtype), vcnt.to(torch.int32)
+    return [
+        StreamIndexTensors(
+            packed_codes=codes[i], list_ids=lid[i], key_norms=norms[i], coarse_centroids=coarse[i], codebooks=books[i],
+            value_means=vmean[i], value_sums=vsum[i], value_counts=vcnt[i],
+        )
+        for i in range(words.shape[0])
+    ]
+
+
 def _value_summaries(values: torch.Tensor, lid: torch.Tensor, lid_raw, lists: int):
     """Per-list value sums, counts and means (pq_hsa/attention/kv_cache.py:688-728): the kernels on a GPU (the
     values are read in their own dtype and widened on the way), torch scatters elsewhere."""
@@ -300,21 +313,7 @@ def build_index_batch(keys: torch.Tensor, values: torch.Tensor, cfg: IVFPQConfig
             words |= d2.argmin(dim=-1) << (4 * j)
     del resid
     vsum, vcnt, vmean = _value_summaries(values, lid, lid_raw, lists)
-    out = []
-    for i in range(s):
-        out.append(
-            StreamIndexTensors(
-                packed_codes=words_to_codes(words[i]),
-                list_ids=lid[i],
-                key_norms=norms[i],
-                coarse_centroids=coarse[i].to(dtype),
-                codebooks=books[i].to(dtype),
-                value_means=vmean[i].to(dtype),
-                value_sums=vsum[i],
-                value_counts=vcnt[i].to(torch.int32),
-            )
-        )
-    return out
+    return _per_stream(words, lid, norms, coarse, books, vmean, vsum, vcnt, dtype)
 
 
 @torch.no_grad()
@@ -367,11 +366,4 @@ def online_refresh_batch(keys: torch.Tensor, values: torch.Tensor, current: list
             d2 = ((chunk.unsqueeze(2) - books[:, j].unsqueeze(1)) ** 2).sum(-1)
             words |= d2.argmin(dim=-1) << (4 * j)
     vsum, vcnt, vmean = _value_summaries(values, lid, lid_raw, lists)
-    return [
-        StreamIndexTensors(
-            packed_codes=words_to_codes(words[i]), list_ids=lid[i], key_norms=norms[i],
-            coarse_centroids=coarse[i].to(dtype), codebooks=books[i].to(dtype), value_means=vmean[i].to(dtype),
-            value_sums=vsum[i], value_counts=vcnt[i].to(torch.int32),
-        )
-        for i in range(s)
-    ]
+    return _per_stream(words, lid, norms, coarse, books, vmean, vsum, vcnt, dtype)
