@@ -682,12 +682,17 @@ __global__ void __launch_bounds__(kSelThreads, 4) emit_kernel(const SelectArgs a
 constexpr int kRowThreads = 1024;
 // Candidates per thread held in registers: 8 (up to 8192 candidates; their token positions are fetched together
 // with their codes) or, for a larger K, 16 (up to 16384; positions are fetched for the selected ones only).
-template <int PER> struct RowShape {
+// THREADS: 1024, or 512 for rows with at most 4096 candidates when there are more rows than SMs - two CTAs fit an SM
+// then, and the rows' latency chains overlap instead of queueing in waves.
+template <int PER, int THREADS> struct RowShape {
   static constexpr int kPer = PER;
-  static constexpr int kCap = kRowThreads * PER;   // more candidates than that select from all keys
-  static constexpr int kIdxBits = PER == 8 ? 13 : 14;  // bits of a candidate index
+  static constexpr int kCap = THREADS * PER;   // more candidates than that select from all keys
+  static constexpr int kIdxBits = (PER == 8 ? 13 : 14) - (THREADS == 512 ? 1 : 0);  // bits of a candidate index
   static constexpr bool kPositionsEarly = PER == 8;
+  static constexpr int kBinsPer = kSelBins / THREADS;  // histogram bins a thread walks
+  static_assert(THREADS == 1024 || THREADS == 512, "thread count");
   static_assert(kCap == 1 << kIdxBits, "candidate index bits");
+  static_assert(kBinsPer * THREADS == kSelBins, "bins per thread");
 };
 constexpr int kRowWords = 8;                        // consecutive hit words per thread and round
 
@@ -705,9 +710,10 @@ struct RowShared {
   int emit_count;
 };
 
-template <typename E, int PER>
-__global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArgs a) {
-  using RS = RowShape<PER>;
+template <typename E, int PER, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS) row_select_kernel(const SelectArgs a) {
+  using RS = RowShape<PER, THREADS>;
+  constexpr int kRowThreads = THREADS;  // shadows the default above
   constexpr int kRowPer = RS::kPer, kRowCandCap = RS::kCap, kRowIdxBits = RS::kIdxBits;
   // candidate -> (word + 1) << 13 | offset of the word's first candidate
   extern __shared__ __align__(16) uint32_t owner[];  // [kRowCandCap]
@@ -777,7 +783,7 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
     __syncthreads();  // the previous round's totals have been read; first round: the array is clear
     if (lane == 31) sh.wtot[warp] = incl;
     __syncthreads();
-    int wt = sh.wtot[lane];  // 32 warps: every warp scans the 32 totals
+    int wt = lane < kRowThreads / 32 ? sh.wtot[lane] : 0;  // every warp scans the warps' totals
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, wt, o);
@@ -919,8 +925,15 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         for (int j = 0; j < kRowPer; ++j)
           if (kreg[j] != 0u) atomicAdd(&hist[cand_bin(key_float(kreg[j]), blo, binv)], 1u);
         __syncthreads();
-        // walk from the top: thread t owns bin kSelBins - t (bins kSelBins .. 1); the last thread also bin 0
-        const uint32_t val = hist[kSelBins - tid];
+        // walk from the top: thread t owns the bins kSelBins - t * kBinsPer downwards (all threads: bins kSelBins .. 1);
+        // the last thread also bin 0
+        constexpr int kBinsPer = RS::kBinsPer;
+        uint32_t bv[kBinsPer], val = 0u;
+#pragma unroll
+        for (int b = 0; b < kBinsPer; ++b) {
+          bv[b] = hist[kSelBins - tid * kBinsPer - b];
+          val += bv[b];
+        }
         uint32_t incl = val;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -930,12 +943,18 @@ __global__ void __launch_bounds__(kRowThreads) row_select_kernel(const SelectArg
         if (lane == 31) rsh2.wtot[warp] = incl;
         __syncthreads();
         incl += __reduce_add_sync(0xffffffffu, lane < warp ? rsh2.wtot[lane] : 0u);
-        const uint32_t excl = incl - val, need_k = (uint32_t)K;
-        if (excl < need_k && need_k <= incl) {
-          bnd.bin = kSelBins - tid;
-          bnd.above = (int)excl;
-          bnd.members = (int)val;
-        } else if (tid == kRowThreads - 1 && incl < need_k) {
+        const uint32_t need_k = (uint32_t)K;
+        uint32_t run = incl - val;  // candidates in the bins above this thread's
+#pragma unroll
+        for (int b = 0; b < kBinsPer; ++b) {
+          if (run < need_k && need_k <= run + bv[b]) {
+            bnd.bin = kSelBins - tid * kBinsPer - b;
+            bnd.above = (int)run;
+            bnd.members = (int)bv[b];
+          }
+          run += bv[b];
+        }
+        if (tid == kRowThreads - 1 && incl < need_k) {
           bnd.bin = 0;
           bnd.above = (int)incl;
           bnd.members = (int)hist[0];
@@ -1111,11 +1130,14 @@ int launch_select(const pqhsa_params& p, const pqhsa_ws_layout& w, cudaStream_t 
   if (w.parts == 1 || w.parts == -1) {
     // one CTA per row: 8 candidates per thread, or 16 for a larger K (parts == -1)
     PQHSA_DISPATCH_E(p.dtype, {
-      if (w.parts == 1) {
-        row_select_kernel<E, 8><<<R, kRowThreads, RowShape<8>::kCap * sizeof(uint32_t), st>>>(a);
+      if (w.parts == 1 && R > sm_count() && 2 * w.kcap + 1024 <= RowShape<8, 512>::kCap) {
+        // more rows than SMs and few candidates per row: half-size CTAs, two to an SM
+        row_select_kernel<E, 8, 512><<<R, 512, RowShape<8, 512>::kCap * sizeof(uint32_t), st>>>(a);
+      } else if (w.parts == 1) {
+        row_select_kernel<E, 8, kRowThreads><<<R, kRowThreads, RowShape<8, kRowThreads>::kCap * sizeof(uint32_t), st>>>(a);
       } else {
-        auto kern = row_select_kernel<E, 16>;
-        constexpr int smem = RowShape<16>::kCap * (int)sizeof(uint32_t);
+        auto kern = row_select_kernel<E, 16, kRowThreads>;
+        constexpr int smem = RowShape<16, kRowThreads>::kCap * (int)sizeof(uint32_t);
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
           return check_launch("select: shared memory opt-in");
         kern<<<R, kRowThreads, smem, st>>>(a);

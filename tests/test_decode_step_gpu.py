@@ -72,6 +72,13 @@ def test_selection_forms_by_k():
     assert int(info[:, 4].sum()) == 0
     small = make_case(B=1, Hkv=2, G=4, S=5200, L=64, dtype=torch.bfloat16, seed=19)
     assert pool_from_case(small)[0].layout.parts == 1
+    # more rows than SMs and at most 4096 candidates per row: CTAs of 512 threads, two to an SM
+    many = make_case(B=10, Hkv=4, G=4, S=3000, L=64, dtype=torch.bfloat16, seed=37)
+    pool, _, _ = pool_from_case(many)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert pool.layout.parts == 1 and pool.S * pool.G > sms and 2 * pool.layout.kcap + 1024 <= 4096
+    info = _check_case(many, pool)
+    assert int(info[:, 4].sum()) == 0
     # a larger K (2 K + 1024 > 8192): still one CTA per row, 16 candidates per thread
     big = make_case(B=1, Hkv=2, G=4, S=12000, L=64, dtype=torch.bfloat16, frac=0.32, seed=23)
     pool, _, _ = pool_from_case(big)
