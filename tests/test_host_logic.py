@@ -91,6 +91,24 @@ def test_batched_index_build_equals_the_oracle_build():
         assert torch.equal(res[i].value_counts.float(), vc)
 
 
+def test_device_build_draws_the_rows_of_the_sequential_trainings():
+    """The batched code-word training of the device-side build seeds subspace m like the per-subspace k-means of
+    the CPU build (seed + 10000 + m, pq_hsa/index/pq.py:81-94): same initial rows, and a generator per subspace
+    that continues where that k-means' generator would."""
+    from pqhsa_release_b200.index_build import _draw_code_word_rows
+
+    gens, rows = _draw_code_word_rows(300, 7)
+    assert len(gens) == 8 and len(rows) == 8
+    for m in range(8):
+        ref = torch.Generator().manual_seed(7 + 10_000 + m)
+        assert torch.equal(rows[m], torch.randperm(300, generator=ref)[:16])
+        assert torch.equal(torch.randint(0, 300, (5,), generator=gens[m]), torch.randint(0, 300, (5,), generator=ref))
+    _, few = _draw_code_word_rows(9, 7)  # fewer keys than code words: every key, then random repeats
+    for m in range(8):
+        ref = torch.Generator().manual_seed(7 + 10_000 + m)
+        assert torch.equal(few[m], torch.cat([torch.arange(9), torch.randint(0, 9, (7,), generator=ref)]))
+
+
 def test_online_refresh_equals_the_oracle_refresh():
     g = torch.Generator().manual_seed(2)
     k = torch.randn(1, 1800, 128, generator=g)
