@@ -74,8 +74,7 @@ __global__ void __launch_bounds__(kOrdThreads) cluster_order_kernel(const uint16
 
 // Sums of the rows of every cluster, added in the order of the keys.  rows: E [streams][n] rows of row_stride
 // elements; key set t = group * streams + stream sums the columns [group * width, (group + 1) * width) of its
-// stream's rows.  128 threads: 128 / width clusters per CTA, a thread per column.  The loads of 16 rows and the places
-// of the next 16 are in flight together; the additions stay one after the other.
+// stream's rows.  128 threads: 128 / width clusters per CTA, a thread per column.
 template <typename E>
 __global__ void __launch_bounds__(128) cluster_sums_kernel(const E* __restrict__ rows, long long stream_stride,
                                                             int row_stride, int width, int streams, int n, int k,
@@ -90,23 +89,40 @@ __global__ void __launch_bounds__(128) cluster_sums_kernel(const E* __restrict__
   const int p1 = start[(size_t)t * (k + 1) + c + 1];
   int p = start[(size_t)t * (k + 1) + c];
   float acc = 0.f;
-  constexpr int U = 16;
+  // Batches of U rows, two batches of row loads and the places of a third in flight; the additions stay one after
+  // the other.  A chain is latency-bound (one thread per cluster and column), so what counts is loads in flight.
+  constexpr int U = 32;
+  const int nb = (p1 - p) / U;
   int idx[U];
-  if (p + U <= p1) {
+  E v[U];
+  if (nb > 0) {
 #pragma unroll
     for (int u = 0; u < U; ++u) idx[u] = ord[p + u];
-  }
-  for (; p + U <= p1; p += U) {
-    E v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) v[u] = base[(size_t)idx[u] * row_stride];
-    if (p + 2 * U <= p1) {  // the next batch's places travel while this batch's rows do
+    if (nb > 1) {
 #pragma unroll
       for (int u = 0; u < U; ++u) idx[u] = ord[p + U + u];
     }
+  }
+  for (int bt = 0; bt < nb; ++bt) {
+    E w[U];
+    if (bt + 1 < nb) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) w[u] = base[(size_t)idx[u] * row_stride];
+    }
+    if (bt + 2 < nb) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) idx[u] = ord[p + (bt + 2) * U + u];
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) acc = __fadd_rn(acc, to_f(v[u]));
+    if (bt + 1 < nb) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = w[u];
+    }
   }
+  p += nb * U;
   for (; p < p1; ++p) acc = __fadd_rn(acc, to_f(base[(size_t)ord[p] * row_stride]));
   sums[((size_t)t * k + c) * width + col] = acc;
 }
