@@ -195,8 +195,9 @@ typedef struct pqhsa_ws_layout {
   size_t row_ticket;   /* int32  [R]      finished items of the attend kernel per row (0 between launches) */
   size_t work_counter; /* uint64 [2]      work distribution of the attend kernel (0 between launches)      */
   size_t combine_ticket; /* int32 [1]     finished CTAs of the combine kernel (0 between launches)          */
-  int32_t parts;       /* form of the selection: 1 = one CTA per query row with 8 candidates per thread, -1 = one CTA
-                          with 16 per thread (larger K), >= 2 = that many CTAs share a row (still larger K) */
+  int32_t parts;       /* form of the selection: 1 = one CTA per query row with 8 candidates per thread (1024 threads;
+                          512, two CTAs to an SM, when there are more rows than SMs and 2 kcap + 1024 <= 4096), -1 = one
+                          CTA with 16 per thread (larger K), >= 2 = that many CTAs share a row (still larger K) */
   int32_t seg;         /* candidates one of them can list */
   int32_t kcap;        /* row stride of sel_* */
   int32_t tail_cap;    /* row stride of tail_logit */
